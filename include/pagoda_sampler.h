@@ -1,0 +1,145 @@
+/*
+ * pagoda_sampler.h -- C ABI of the B200 (sm_100a) backend for pagoda's per-step
+ * logits -> token chain.
+ *
+ * The reference runs this chain on the host, one sequence at a time, inside
+ * Engine::advance_with_logits (pagoda/src/engine.rs:1286-1327): sanity check ->
+ * penalties -> grammar mask -> EOS fix -> Sampler::sample.  The reference has no
+ * FFI today; these entry points are what a `pagoda-sampler-sys` crate would bind so
+ * that the per-sequence loop at pagoda/src/engine.rs:511-544 becomes one batched
+ * call.  Every function returns an int: 0 on success, a negative pgs_error
+ * otherwise; nothing throws or aborts across the boundary.  There is no CPU
+ * fallback: without a CUDA device pgs_create fails.
+ *
+ * Plain pointers and sizes only.  All calls on one handle must come from one thread
+ * at a time (the reference samples on its single actor thread,
+ * pagoda/src/engine.rs:1396); a handle may move between threads.
+ */
+#ifndef PAGODA_SAMPLER_H
+#define PAGODA_SAMPLER_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define PGS_ABI_VERSION 1
+
+#if defined(__GNUC__)
+#define PGS_API __attribute__((visibility("default")))
+#else
+#define PGS_API
+#endif
+
+typedef struct pgs_handle pgs_handle;
+
+enum pgs_error {
+    PGS_OK = 0,
+    PGS_ERR_INVALID = -1,  /* bad argument (message in pgs_last_error) */
+    PGS_ERR_CUDA = -2,     /* a CUDA call failed */
+    PGS_ERR_NOMEM = -3,
+    PGS_ERR_LIMIT = -4,    /* rows / vocab / history beyond what pgs_create was sized for */
+    PGS_ERR_TIMEOUT = -5   /* a bounded device-side wait ran out (peer exchange) */
+};
+
+/* Per-row outcome.  Maps onto the reference's per-request finish reasons so that a
+ * bad row never affects its batch-mates (pagoda/tests/fault_tests.rs:63-82). */
+enum pgs_row_status {
+    PGS_ROW_OK = 0,
+    PGS_ROW_NONFINITE = 1, /* logits_sane failed (engine.rs:1278-1295) -> FinishReason::Fault */
+    PGS_ROW_DEAD = 2,      /* grammar state is a dead end (engine.rs:1299-1303) -> Stop, no token */
+    PGS_ROW_EMPTY = 3,     /* nothing finite left after masking; token 0, as sampler.rs:59-70 returns */
+    PGS_ROW_BAD_PARAM = 4  /* non-finite parameter, bad mask table/state, history too long */
+};
+
+enum pgs_mem { PGS_MEM_DEVICE = 0, PGS_MEM_HOST = 1 };
+enum pgs_dtype { PGS_F32 = 0, PGS_BF16 = 1 };
+
+/* Replaces Sampler::new / Engine's ownership of the sampler (sampler.rs:16-18,
+ * engine.rs:96,202).  Sizes the device workspace once; later calls never allocate
+ * unless a host-resident batch first needs its staging buffer. */
+PGS_API int pgs_create(int device_ordinal, uint32_t max_rows, uint32_t max_vocab,
+               uint32_t max_history_per_row, pgs_handle **out);
+PGS_API int pgs_destroy(pgs_handle *h);
+/* Message for the last failing call on this handle (or on creation when h == NULL). */
+PGS_API const char *pgs_last_error(const pgs_handle *h);
+
+/* Grammar bitmask tables.  Replaces the per-step allowed-byte vector that
+ * Grammar::allowed_bytes builds and mask_logits applies (grammar.rs:52-65, :73-85):
+ * the host tabulates its grammar into states, uploads one bitmask of
+ * `words_per_state` u32 words per state once, and then names (table, state) per row.
+ * Token i is kept iff bit (i & 31) of word (i >> 5) is set.  state_flags (may be NULL):
+ * bit 0 = the partial output is already complete (drives the EOS fix of
+ * engine.rs:1307-1312), bit 1 = dead end. */
+PGS_API int pgs_mask_table_upload(pgs_handle *h, uint32_t n_states, uint32_t words_per_state,
+                          const uint32_t *host_words, const uint8_t *state_flags,
+                          int32_t *table_id);
+PGS_API int pgs_mask_table_free(pgs_handle *h, int32_t table_id);
+
+/* One decode step for a batch of rows.  Per-row arrays may be NULL (defaults in
+ * brackets, the reference's SamplingParams::default(), spec.rs:90-105). */
+typedef struct pgs_batch_desc {
+    uint32_t struct_size;         /* sizeof(pgs_batch_desc) */
+    uint32_t rows;
+    uint32_t vocab;
+    uint32_t logits_dtype;        /* pgs_dtype; bf16 is upcast exactly, then the same math */
+    uint64_t row_stride;          /* elements between consecutive rows (>= vocab) */
+    const void *logits;           /* [rows x row_stride], read only */
+    uint32_t logits_mem;          /* pgs_mem: where `logits` lives */
+    uint32_t aux_mem;             /* pgs_mem: where every other array below lives */
+
+    const float *temperature;     /* [0.0] below 1e-5 -> greedy (sampler.rs:29) */
+    const uint32_t *top_k;        /* [0] 0 or >= vocab disables (sampler.rs:117) */
+    const float *top_p;           /* [1.0] >= 1 disables (sampler.rs:131) */
+    const float *frequency_penalty; /* [0.0] engine.rs:1553-1573 */
+    const float *presence_penalty;  /* [0.0] */
+    const float *repetition_penalty;/* [1.0] extension: logit > 0 ? logit / r : logit * r */
+    const uint32_t *hist_offsets; /* CSR over generated token ids, rows + 1 entries (NULL = none) */
+    const uint32_t *hist_ids;     /* ids >= vocab are skipped (engine.rs:1562) */
+    const int32_t *mask_table;    /* per row table id, < 0 = no grammar (NULL = none) */
+    const int32_t *mask_state;    /* per row state inside that table */
+    int32_t eos_token_id;         /* < 0: none */
+    uint32_t reserved0;
+    const float *uniform;         /* per row rng.next_f32() (rng.rs:28-30); only read for rows that draw */
+
+    uint32_t *token;              /* out, required */
+    int32_t *status;              /* out, required: pgs_row_status */
+    uint8_t *drew;                /* out, optional: 1 iff the row consumed its uniform (sampler.rs:43-46) */
+
+    /* optional diagnostics for parity checks (NULL to skip) */
+    uint32_t *argmax;             /* argmax of the processed logits, lowest id on ties */
+    float *row_max;               /* max over finite processed logits */
+    float *sumexp;                /* the f32 left-fold sum of temperature_softmax */
+    float *total;                 /* sample_categorical's total */
+    uint32_t *n_kept;             /* entries with probability > 0 after top-k / top-p */
+    uint32_t dump_cap;            /* per row capacity of the two arrays below */
+    uint32_t reserved1;
+    uint32_t *dump_ids;           /* [rows x dump_cap] kept ids, ascending */
+    float *dump_probs;            /* [rows x dump_cap] their probabilities */
+} pgs_batch_desc;
+
+/* Replaces the loop body apply_penalties -> mask_logits -> Sampler::sample
+ * (engine.rs:1296-1314) for every row at once.  Returns after the outputs are
+ * readable by the host. */
+PGS_API int pgs_sample_batch(pgs_handle *h, const pgs_batch_desc *desc);
+/* Same, enqueued on `cuda_stream` (a cudaStream_t; NULL = the handle's own stream)
+ * without waiting.  Every array must be device memory. */
+PGS_API int pgs_sample_batch_async(pgs_handle *h, const pgs_batch_desc *desc, void *cuda_stream);
+
+/* Counters since creation (for the engine's /stats): rows sampled, rows faulted, algorithmic
+ * bytes touched. */
+typedef struct pgs_counters {
+    uint64_t calls, rows, rows_faulted, bytes;
+    uint64_t kernel_launches;
+} pgs_counters;
+PGS_API int pgs_get_counters(const pgs_handle *h, pgs_counters *out);
+
+/* The handle's stream as a cudaStream_t, for callers that time or order work on it. */
+PGS_API void *pgs_stream(pgs_handle *h);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

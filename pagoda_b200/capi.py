@@ -1,0 +1,274 @@
+"""ctypes binding of include/pagoda_sampler.h.
+
+Host arrays (numpy) go through the host-memory side of the ABI; CUDA tensors (torch) are passed
+as raw device pointers.  torch is only used for device memory and streams.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+from dataclasses import dataclass
+from typing import Optional
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+
+PGS_F32, PGS_BF16 = 0, 1
+MEM_DEVICE, MEM_HOST = 0, 1
+ROW_OK, ROW_NONFINITE, ROW_DEAD, ROW_EMPTY, ROW_BAD_PARAM = 0, 1, 2, 3, 4
+
+EXPORTS = ["pgs_create", "pgs_destroy", "pgs_last_error", "pgs_mask_table_upload", "pgs_mask_table_free",
+           "pgs_sample_batch", "pgs_sample_batch_async", "pgs_get_counters", "pgs_stream"]
+
+
+class SamplerError(RuntimeError):
+    def __init__(self, code: int, msg: str):
+        super().__init__(f"pgs error {code}: {msg}")
+        self.code = code
+
+
+class BatchDesc(C.Structure):
+    _fields_ = [
+        ("struct_size", C.c_uint32), ("rows", C.c_uint32), ("vocab", C.c_uint32), ("logits_dtype", C.c_uint32),
+        ("row_stride", C.c_uint64), ("logits", C.c_void_p), ("logits_mem", C.c_uint32), ("aux_mem", C.c_uint32),
+        ("temperature", C.c_void_p), ("top_k", C.c_void_p), ("top_p", C.c_void_p),
+        ("frequency_penalty", C.c_void_p), ("presence_penalty", C.c_void_p), ("repetition_penalty", C.c_void_p),
+        ("hist_offsets", C.c_void_p), ("hist_ids", C.c_void_p),
+        ("mask_table", C.c_void_p), ("mask_state", C.c_void_p),
+        ("eos_token_id", C.c_int32), ("reserved0", C.c_uint32), ("uniform", C.c_void_p),
+        ("token", C.c_void_p), ("status", C.c_void_p), ("drew", C.c_void_p),
+        ("argmax", C.c_void_p), ("row_max", C.c_void_p), ("sumexp", C.c_void_p), ("total", C.c_void_p),
+        ("n_kept", C.c_void_p), ("dump_cap", C.c_uint32), ("reserved1", C.c_uint32),
+        ("dump_ids", C.c_void_p), ("dump_probs", C.c_void_p),
+    ]
+
+
+class Counters(C.Structure):
+    _fields_ = [("calls", C.c_uint64), ("rows", C.c_uint64), ("rows_faulted", C.c_uint64), ("bytes", C.c_uint64),
+                ("kernel_launches", C.c_uint64)]
+
+
+def lib_path() -> str:
+    return os.path.join(_HERE, "libpagoda_sampler.so")
+
+
+_lib = None
+
+
+def load_library():
+    """dlopen the built library and declare its signatures. Raises if it has not been built."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    path = lib_path()
+    if not os.path.exists(path):
+        raise SamplerError(-2, f"{path} is missing: build it with `python -m pagoda_b200.build` "
+                               "(there is no CPU fallback)")
+    L = C.CDLL(path)
+    L.pgs_create.argtypes = [C.c_int, C.c_uint32, C.c_uint32, C.c_uint32, C.POINTER(C.c_void_p)]
+    L.pgs_destroy.argtypes = [C.c_void_p]
+    L.pgs_last_error.restype = C.c_char_p
+    L.pgs_last_error.argtypes = [C.c_void_p]
+    L.pgs_mask_table_upload.argtypes = [C.c_void_p, C.c_uint32, C.c_uint32, C.c_void_p, C.c_void_p,
+                                        C.POINTER(C.c_int32)]
+    L.pgs_mask_table_free.argtypes = [C.c_void_p, C.c_int32]
+    L.pgs_sample_batch.argtypes = [C.c_void_p, C.POINTER(BatchDesc)]
+    L.pgs_sample_batch_async.argtypes = [C.c_void_p, C.POINTER(BatchDesc), C.c_void_p]
+    L.pgs_get_counters.argtypes = [C.c_void_p, C.POINTER(Counters)]
+    L.pgs_stream.restype = C.c_void_p
+    L.pgs_stream.argtypes = [C.c_void_p]
+    _lib = L
+    return L
+
+
+def _is_torch(x) -> bool:
+    return x is not None and type(x).__module__.startswith("torch")
+
+
+@dataclass
+class BatchResult:
+    token: np.ndarray
+    status: np.ndarray
+    drew: np.ndarray
+    argmax: Optional[np.ndarray] = None
+    row_max: Optional[np.ndarray] = None
+    sumexp: Optional[np.ndarray] = None
+    total: Optional[np.ndarray] = None
+    n_kept: Optional[np.ndarray] = None
+    dump_ids: Optional[np.ndarray] = None
+    dump_probs: Optional[np.ndarray] = None
+
+    def kept(self, row: int):
+        n = min(int(self.n_kept[row]), self.dump_ids.shape[1])
+        return self.dump_ids[row, :n], self.dump_probs[row, :n]
+
+
+class Sampler:
+    """One device-side sampler backend (a `pgs_handle`)."""
+
+    def __init__(self, device: int = 0, max_rows: int = 256, max_vocab: int = 262144, max_history: int = 4096):
+        self._lib = load_library()
+        self._h = C.c_void_p()
+        rc = self._lib.pgs_create(device, max_rows, max_vocab, max_history, C.byref(self._h))
+        if rc != 0:
+            raise SamplerError(rc, self._lib.pgs_last_error(None).decode())
+        self.device = device
+        self.max_rows, self.max_vocab, self.max_history = max_rows, max_vocab, max_history
+
+    def close(self):
+        if getattr(self, "_h", None):
+            self._lib.pgs_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def _check(self, rc: int):
+        if rc != 0:
+            raise SamplerError(rc, self._lib.pgs_last_error(self._h).decode())
+
+    @property
+    def stream_ptr(self) -> int:
+        return self._lib.pgs_stream(self._h)
+
+    def counters(self) -> dict:
+        c = Counters()
+        self._check(self._lib.pgs_get_counters(self._h, C.byref(c)))
+        return {k: getattr(c, k) for k, _ in Counters._fields_}
+
+    def upload_mask_table(self, words, state_flags=None) -> int:
+        words = np.ascontiguousarray(words, dtype=np.uint32)
+        assert words.ndim == 2
+        flags = None if state_flags is None else np.ascontiguousarray(state_flags, dtype=np.uint8)
+        tid = C.c_int32(-1)
+        self._check(self._lib.pgs_mask_table_upload(
+            self._h, words.shape[0], words.shape[1], words.ctypes.data,
+            None if flags is None else flags.ctypes.data, C.byref(tid)))
+        return tid.value
+
+    def free_mask_table(self, table_id: int):
+        self._check(self._lib.pgs_mask_table_free(self._h, table_id))
+
+    # ------------------------------------------------------------------ host-resident batch
+    def sample_batch(self, logits, temperature=None, top_k=None, top_p=None, frequency_penalty=None,
+                     presence_penalty=None, repetition_penalty=None, hist_offsets=None, hist_ids=None,
+                     mask_table=None, mask_state=None, eos_token_id=-1, uniform=None, diagnostics=False,
+                     dump_cap=0, row_stride=None, vocab=None) -> BatchResult:
+        """`logits`: numpy [rows, vocab] float32, or uint16 holding bf16 bit patterns; or a CUDA
+        torch tensor (float32 / bfloat16), in which case only the per-row arrays are staged."""
+        keep = []
+        d = BatchDesc()
+        d.struct_size = C.sizeof(BatchDesc)
+        if _is_torch(logits):
+            import torch
+            assert logits.is_cuda and logits.dim() == 2 and logits.stride(1) == 1
+            rows = logits.shape[0]
+            d.vocab = logits.shape[1] if vocab is None else vocab
+            d.row_stride = logits.stride(0)
+            d.logits_dtype = PGS_BF16 if logits.dtype == torch.bfloat16 else PGS_F32
+            assert logits.dtype in (torch.float32, torch.bfloat16)
+            d.logits = logits.data_ptr()
+            d.logits_mem = MEM_DEVICE
+            keep.append(logits)
+        else:
+            logits = np.asarray(logits)
+            assert logits.ndim == 2 and logits.dtype in (np.float32, np.uint16)
+            if not logits.flags.c_contiguous and row_stride is None:
+                logits = np.ascontiguousarray(logits)
+            rows = logits.shape[0]
+            d.vocab = logits.shape[1] if vocab is None else vocab
+            d.row_stride = logits.shape[1] if row_stride is None else row_stride
+            d.logits_dtype = PGS_F32 if logits.dtype == np.float32 else PGS_BF16
+            d.logits = logits.ctypes.data
+            d.logits_mem = MEM_HOST
+            keep.append(logits)
+        d.rows = rows
+        d.aux_mem = MEM_HOST
+        d.eos_token_id = eos_token_id
+
+        def arr(x, dt, n=rows):
+            if x is None:
+                return None
+            a = np.ascontiguousarray(np.broadcast_to(np.asarray(x, dtype=dt), (n,)) if np.ndim(x) == 0 else x,
+                                     dtype=dt)
+            assert a.size == n, (a.size, n)
+            keep.append(a)
+            return a.ctypes.data
+
+        d.temperature = arr(temperature, np.float32)
+        d.top_k = arr(top_k, np.uint32)
+        d.top_p = arr(top_p, np.float32)
+        d.frequency_penalty = arr(frequency_penalty, np.float32)
+        d.presence_penalty = arr(presence_penalty, np.float32)
+        d.repetition_penalty = arr(repetition_penalty, np.float32)
+        if hist_offsets is not None:
+            ho = np.ascontiguousarray(hist_offsets, dtype=np.uint32)
+            hi = np.ascontiguousarray(hist_ids if hist_ids is not None else [], dtype=np.uint32)
+            assert ho.size == rows + 1
+            keep += [ho, hi]
+            d.hist_offsets, d.hist_ids = ho.ctypes.data, hi.ctypes.data
+        d.mask_table = arr(mask_table, np.int32)
+        d.mask_state = arr(mask_state, np.int32)
+        d.uniform = arr(uniform, np.float32)
+        res = BatchResult(np.zeros(rows, np.uint32), np.full(rows, -1, np.int32), np.zeros(rows, np.uint8))
+        d.token, d.status, d.drew = res.token.ctypes.data, res.status.ctypes.data, res.drew.ctypes.data
+        if diagnostics or dump_cap:
+            res.argmax = np.zeros(rows, np.uint32)
+            res.row_max = np.zeros(rows, np.float32)
+            res.sumexp = np.zeros(rows, np.float32)
+            res.total = np.zeros(rows, np.float32)
+            res.n_kept = np.zeros(rows, np.uint32)
+            d.argmax, d.row_max, d.sumexp = res.argmax.ctypes.data, res.row_max.ctypes.data, res.sumexp.ctypes.data
+            d.total, d.n_kept = res.total.ctypes.data, res.n_kept.ctypes.data
+        if dump_cap:
+            res.dump_ids = np.zeros((rows, dump_cap), np.uint32)
+            res.dump_probs = np.zeros((rows, dump_cap), np.float32)
+            d.dump_cap = dump_cap
+            d.dump_ids, d.dump_probs = res.dump_ids.ctypes.data, res.dump_probs.ctypes.data
+        self._check(self._lib.pgs_sample_batch(self._h, C.byref(d)))
+        return res
+
+    # ---------------------------------------------------------------- device-resident batch
+    def make_device_desc(self, logits, token, status, temperature=None, top_k=None, top_p=None,
+                         frequency_penalty=None, presence_penalty=None, repetition_penalty=None,
+                         hist_offsets=None, hist_ids=None, mask_table=None, mask_state=None, eos_token_id=-1,
+                         uniform=None, drew=None, argmax=None, row_max=None, sumexp=None, total=None,
+                         n_kept=None):
+        """Build a descriptor whose every array is a CUDA torch tensor (kept alive by the returned
+        object); launch it with `launch_device`."""
+        import torch
+        d = BatchDesc()
+        d.struct_size = C.sizeof(BatchDesc)
+        d.rows, d.vocab = logits.shape
+        d.row_stride = logits.stride(0)
+        d.logits_dtype = PGS_BF16 if logits.dtype == torch.bfloat16 else PGS_F32
+        d.logits, d.logits_mem, d.aux_mem = logits.data_ptr(), MEM_DEVICE, MEM_DEVICE
+        d.eos_token_id = eos_token_id
+        keep = [logits]
+
+        def p(t, dt):
+            if t is None:
+                return None
+            assert t.is_cuda and t.is_contiguous() and t.dtype == dt, (t.dtype, dt)
+            keep.append(t)
+            return t.data_ptr()
+
+        d.temperature, d.top_k, d.top_p = p(temperature, torch.float32), p(top_k, torch.int32), p(top_p, torch.float32)
+        d.frequency_penalty, d.presence_penalty = p(frequency_penalty, torch.float32), p(presence_penalty, torch.float32)
+        d.repetition_penalty = p(repetition_penalty, torch.float32)
+        d.hist_offsets, d.hist_ids = p(hist_offsets, torch.int32), p(hist_ids, torch.int32)
+        d.mask_table, d.mask_state = p(mask_table, torch.int32), p(mask_state, torch.int32)
+        d.uniform = p(uniform, torch.float32)
+        d.token, d.status, d.drew = p(token, torch.int32), p(status, torch.int32), p(drew, torch.uint8)
+        d.argmax, d.row_max, d.sumexp = p(argmax, torch.int32), p(row_max, torch.float32), p(sumexp, torch.float32)
+        d.total, d.n_kept = p(total, torch.float32), p(n_kept, torch.int32)
+        d._keep = keep
+        return d
+
+    def launch_device(self, desc, stream_ptr: Optional[int] = None):
+        """Enqueue one step without waiting (pgs_sample_batch_async)."""
+        self._check(self._lib.pgs_sample_batch_async(self._h, C.byref(desc), stream_ptr))

@@ -1,0 +1,415 @@
+// Host side of the C ABI declared in include/pagoda_sampler.h: handle lifecycle, grammar table
+// uploads, staging of host-resident batches and kernel launches.  No CPU fallback: every entry
+// point either runs the CUDA kernels or returns an error.
+#include "../../include/pagoda_sampler.h"
+
+#include <cuda_runtime.h>
+#include <stdarg.h>
+#include <stdio.h>
+#include <string.h>
+
+#include <new>
+#include <vector>
+
+#include "pgs_args.cuh"
+
+namespace pgs {
+cudaError_t configure_general();
+cudaError_t launch_general(const RowArgs& a, uint32_t grid, cudaStream_t stream);
+size_t general_smem_bytes();
+}  // namespace pgs
+
+static thread_local char g_create_error[256] = "";
+
+struct pgs_handle {
+    int device = 0;
+    int sm_count = 0;
+    cudaStream_t stream = nullptr;
+    uint32_t max_rows = 0, max_vocab = 0, max_history = 0;
+    uint32_t slots = 0, vocab_pad = 0, sort_pad = 0, hash_cap = 0;
+    // scratch slots
+    float* sx = nullptr;
+    uint32_t* sl_id = nullptr;
+    float* sl_p = nullptr;
+    unsigned long long* sl_key = nullptr;
+    uint32_t* sh_key = nullptr;
+    uint32_t* sh_cnt = nullptr;
+    // grammar tables
+    pgs::TableDir tables_host[pgs::MAX_TABLES];
+    pgs::TableDir* tables_dev = nullptr;
+    // staging for host-resident batches
+    void* logits_stage = nullptr;
+    size_t logits_stage_bytes = 0;
+    unsigned char* aux_host = nullptr;   // pinned
+    unsigned char* aux_dev = nullptr;
+    size_t aux_bytes = 0;
+    pgs_counters counters = {};
+    char err[256] = "";
+};
+
+static int fail(pgs_handle* h, int code, const char* fmt, ...) {
+    char* dst = h ? h->err : g_create_error;
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(dst, 256, fmt, ap);
+    va_end(ap);
+    return code;
+}
+
+#define PGS_CUDA(h, call)                                                                  \
+    do {                                                                                   \
+        cudaError_t e_ = (call);                                                           \
+        if (e_ != cudaSuccess)                                                             \
+            return fail(h, e_ == cudaErrorMemoryAllocation ? PGS_ERR_NOMEM : PGS_ERR_CUDA, \
+                        "%s: %s", #call, cudaGetErrorString(e_));                          \
+    } while (0)
+
+namespace {
+struct DeviceGuard {
+    int prev = -1;
+    explicit DeviceGuard(int dev) {
+        cudaGetDevice(&prev);
+        if (prev != dev) cudaSetDevice(dev);
+    }
+    ~DeviceGuard() {
+        int cur = -1;
+        cudaGetDevice(&cur);
+        if (prev >= 0 && prev != cur) cudaSetDevice(prev);
+    }
+};
+
+uint32_t pow2_at_least(uint32_t v, uint32_t lo) {
+    uint32_t p = lo;
+    while (p < v) p <<= 1;
+    return p;
+}
+}  // namespace
+
+extern "C" const char* pgs_last_error(const pgs_handle* h) { return h ? h->err : g_create_error; }
+
+static int destroy_impl(pgs_handle* h) {
+    DeviceGuard g(h->device);
+    if (h->stream) cudaStreamSynchronize(h->stream);
+    for (int t = 0; t < pgs::MAX_TABLES; t++) {
+        if (h->tables_host[t].live) {
+            cudaFree((void*)h->tables_host[t].words);
+            cudaFree((void*)h->tables_host[t].flags);
+        }
+    }
+    cudaFree(h->sx); cudaFree(h->sl_id); cudaFree(h->sl_p); cudaFree(h->sl_key);
+    cudaFree(h->sh_key); cudaFree(h->sh_cnt); cudaFree(h->tables_dev);
+    cudaFree(h->logits_stage); cudaFree(h->aux_dev);
+    if (h->aux_host) cudaFreeHost(h->aux_host);
+    if (h->stream) cudaStreamDestroy(h->stream);
+    delete h;
+    return PGS_OK;
+}
+
+extern "C" int pgs_create(int device, uint32_t max_rows, uint32_t max_vocab, uint32_t max_history,
+                          pgs_handle** out) {
+    if (!out) return fail(nullptr, PGS_ERR_INVALID, "pgs_create: out is NULL");
+    *out = nullptr;
+    if (max_rows == 0 || max_vocab == 0 || max_vocab > (1u << 24) || max_history > (1u << 22))
+        return fail(nullptr, PGS_ERR_INVALID,
+                    "pgs_create: need 1 <= max_rows, 1 <= max_vocab <= 2^24, max_history <= 2^22");
+    int n_dev = 0;
+    cudaError_t e = cudaGetDeviceCount(&n_dev);
+    if (e != cudaSuccess || n_dev == 0)
+        return fail(nullptr, PGS_ERR_CUDA, "pgs_create: no CUDA device (%s); this library has no CPU path",
+                    cudaGetErrorString(e));
+    if (device < 0 || device >= n_dev)
+        return fail(nullptr, PGS_ERR_INVALID, "pgs_create: device %d out of range (0..%d)", device, n_dev - 1);
+    pgs_handle* h = new (std::nothrow) pgs_handle();
+    if (!h) return fail(nullptr, PGS_ERR_NOMEM, "pgs_create: out of host memory");
+    h->device = device;
+    memset(h->tables_host, 0, sizeof h->tables_host);
+    DeviceGuard g(device);
+    int rc = [&]() -> int {
+        cudaDeviceProp prop;
+        PGS_CUDA(nullptr, cudaGetDeviceProperties(&prop, device));
+        if (prop.major < 10)
+            return fail(nullptr, PGS_ERR_CUDA, "pgs_create: device %d is sm_%d%d; this library is built for sm_100a",
+                        device, prop.major, prop.minor);
+        h->sm_count = prop.multiProcessorCount;
+        PGS_CUDA(nullptr, cudaStreamCreateWithFlags(&h->stream, cudaStreamNonBlocking));
+        PGS_CUDA(nullptr, pgs::configure_general());
+        h->max_rows = max_rows; h->max_vocab = max_vocab; h->max_history = max_history;
+        h->slots = max_rows < (uint32_t)h->sm_count ? max_rows : (uint32_t)h->sm_count;
+        h->vocab_pad = (max_vocab + 31u) & ~31u;
+        h->sort_pad = pow2_at_least(max_vocab, 2);
+        h->hash_cap = pow2_at_least(2 * (max_history ? max_history : 1), 64);
+        const size_t s = h->slots;
+        PGS_CUDA(nullptr, cudaMalloc(&h->sx, s * h->vocab_pad * sizeof(float)));
+        PGS_CUDA(nullptr, cudaMalloc(&h->sl_id, s * h->vocab_pad * sizeof(uint32_t)));
+        PGS_CUDA(nullptr, cudaMalloc(&h->sl_p, s * h->vocab_pad * sizeof(float)));
+        PGS_CUDA(nullptr, cudaMalloc(&h->sl_key, s * h->sort_pad * sizeof(unsigned long long)));
+        PGS_CUDA(nullptr, cudaMalloc(&h->sh_key, s * h->hash_cap * sizeof(uint32_t)));
+        PGS_CUDA(nullptr, cudaMalloc(&h->sh_cnt, s * h->hash_cap * sizeof(uint32_t)));
+        PGS_CUDA(nullptr, cudaMalloc(&h->tables_dev, sizeof h->tables_host));
+        PGS_CUDA(nullptr, cudaMemsetAsync(h->tables_dev, 0, sizeof h->tables_host, h->stream));
+        // aux staging: per-row parameter and output arrays of a host-resident batch
+        h->aux_bytes = (size_t)max_rows * 128 + (size_t)max_rows * max_history * 4 + 4096;
+        PGS_CUDA(nullptr, cudaMalloc(&h->aux_dev, h->aux_bytes));
+        PGS_CUDA(nullptr, cudaMallocHost(&h->aux_host, h->aux_bytes));
+        PGS_CUDA(nullptr, cudaStreamSynchronize(h->stream));
+        return PGS_OK;
+    }();
+    if (rc != PGS_OK) {
+        destroy_impl(h);
+        return rc;
+    }
+    *out = h;
+    return PGS_OK;
+}
+
+extern "C" int pgs_destroy(pgs_handle* h) {
+    if (!h) return PGS_OK;
+    return destroy_impl(h);
+}
+
+extern "C" void* pgs_stream(pgs_handle* h) { return h ? (void*)h->stream : nullptr; }
+
+extern "C" int pgs_get_counters(const pgs_handle* h, pgs_counters* out) {
+    if (!h || !out) return PGS_ERR_INVALID;
+    *out = h->counters;
+    return PGS_OK;
+}
+
+extern "C" int pgs_mask_table_upload(pgs_handle* h, uint32_t n_states, uint32_t words_per_state,
+                                     const uint32_t* host_words, const uint8_t* state_flags,
+                                     int32_t* table_id) {
+    if (!h) return PGS_ERR_INVALID;
+    if (!host_words || !table_id || n_states == 0 || words_per_state == 0)
+        return fail(h, PGS_ERR_INVALID, "pgs_mask_table_upload: empty table or NULL argument");
+    int t = -1;
+    for (int i = 0; i < pgs::MAX_TABLES; i++)
+        if (!h->tables_host[i].live) { t = i; break; }
+    if (t < 0) return fail(h, PGS_ERR_LIMIT, "pgs_mask_table_upload: all %d table slots in use", pgs::MAX_TABLES);
+    DeviceGuard g(h->device);
+    uint32_t* words = nullptr;
+    uint8_t* flags = nullptr;
+    const size_t wbytes = (size_t)n_states * words_per_state * sizeof(uint32_t);
+    PGS_CUDA(h, cudaMalloc(&words, wbytes));
+    cudaError_t e = cudaMalloc(&flags, n_states);
+    if (e != cudaSuccess) { cudaFree(words); return fail(h, PGS_ERR_NOMEM, "cudaMalloc(flags): %s", cudaGetErrorString(e)); }
+    std::vector<uint8_t> zero;
+    if (!state_flags) { zero.assign(n_states, 0); state_flags = zero.data(); }
+    pgs::TableDir d;
+    d.words = words; d.flags = flags; d.words_per_state = words_per_state; d.n_states = n_states;
+    d.live = 1; d.pad = 0;
+    e = cudaMemcpyAsync(words, host_words, wbytes, cudaMemcpyHostToDevice, h->stream);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(flags, state_flags, n_states, cudaMemcpyHostToDevice, h->stream);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(h->tables_dev + t, &d, sizeof d, cudaMemcpyHostToDevice, h->stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(h->stream);
+    if (e != cudaSuccess) {
+        cudaFree(words); cudaFree(flags);
+        return fail(h, PGS_ERR_CUDA, "pgs_mask_table_upload: %s", cudaGetErrorString(e));
+    }
+    h->tables_host[t] = d;
+    *table_id = t;
+    return PGS_OK;
+}
+
+extern "C" int pgs_mask_table_free(pgs_handle* h, int32_t table_id) {
+    if (!h) return PGS_ERR_INVALID;
+    if (table_id < 0 || table_id >= pgs::MAX_TABLES || !h->tables_host[table_id].live)
+        return fail(h, PGS_ERR_INVALID, "pgs_mask_table_free: table %d is not live", table_id);
+    DeviceGuard g(h->device);
+    pgs::TableDir d = h->tables_host[table_id];
+    pgs::TableDir dead;
+    memset(&dead, 0, sizeof dead);
+    PGS_CUDA(h, cudaMemcpyAsync(h->tables_dev + table_id, &dead, sizeof dead, cudaMemcpyHostToDevice, h->stream));
+    PGS_CUDA(h, cudaStreamSynchronize(h->stream));
+    cudaFree((void*)d.words);
+    cudaFree((void*)d.flags);
+    h->tables_host[table_id] = dead;
+    return PGS_OK;
+}
+
+// ------------------------------------------------------------------------------ batches
+
+namespace {
+
+struct AuxPlan {
+    pgs_handle* h;
+    size_t used = 0;
+    bool overflow = false;
+    // (host destination, offset, bytes) of every output to copy back
+    struct Out { void* dst; size_t off, bytes; };
+    std::vector<Out> outs;
+    size_t out_lo = 0, out_hi = 0;
+
+    size_t reserve(size_t bytes) {
+        size_t off = (used + 15) & ~size_t(15);
+        if (off + bytes > h->aux_bytes) { overflow = true; return 0; }
+        used = off + bytes;
+        return off;
+    }
+    template <class T> const T* in(const T* host, size_t n) {
+        if (!host) return nullptr;
+        size_t off = reserve(n * sizeof(T));
+        if (overflow) return nullptr;
+        memcpy(h->aux_host + off, host, n * sizeof(T));
+        return (const T*)(h->aux_dev + off);
+    }
+    template <class T> T* out(T* host, size_t n) {
+        if (!host) return nullptr;
+        size_t off = reserve(n * sizeof(T));
+        if (overflow) return nullptr;
+        outs.push_back({host, off, n * sizeof(T)});
+        return (T*)(h->aux_dev + off);
+    }
+};
+
+int validate(pgs_handle* h, const pgs_batch_desc* d) {
+    if (!d) return fail(h, PGS_ERR_INVALID, "desc is NULL");
+    if (d->struct_size != sizeof(pgs_batch_desc))
+        return fail(h, PGS_ERR_INVALID, "desc.struct_size %u != %zu (ABI mismatch)", d->struct_size,
+                    sizeof(pgs_batch_desc));
+    if (d->rows == 0) return PGS_OK;
+    if (d->rows > h->max_rows || d->vocab > h->max_vocab)
+        return fail(h, PGS_ERR_LIMIT, "batch %u x %u exceeds the handle's %u x %u", d->rows, d->vocab,
+                    h->max_rows, h->max_vocab);
+    if (d->vocab == 0 || !d->logits || !d->token || !d->status)
+        return fail(h, PGS_ERR_INVALID, "vocab, logits, token and status are required");
+    if (d->row_stride < d->vocab) return fail(h, PGS_ERR_INVALID, "row_stride < vocab");
+    if (d->logits_dtype > PGS_BF16 || d->logits_mem > PGS_MEM_HOST || d->aux_mem > PGS_MEM_HOST)
+        return fail(h, PGS_ERR_INVALID, "bad dtype / memory kind");
+    if ((d->hist_offsets == nullptr) != (d->hist_ids == nullptr) && d->hist_offsets == nullptr)
+        return fail(h, PGS_ERR_INVALID, "hist_ids given without hist_offsets");
+    if ((d->dump_ids || d->dump_probs) && d->dump_cap == 0)
+        return fail(h, PGS_ERR_INVALID, "dump arrays given with dump_cap == 0");
+    return PGS_OK;
+}
+
+int run_batch(pgs_handle* h, const pgs_batch_desc* d, cudaStream_t stream, bool wait) {
+    int rc = validate(h, d);
+    if (rc != PGS_OK) return rc;
+    if (d->rows == 0) return PGS_OK;
+    DeviceGuard g(h->device);
+    const uint32_t rows = d->rows;
+    const size_t esz = d->logits_dtype == PGS_F32 ? 4 : 2;
+    pgs::RowArgs a;
+    memset(&a, 0, sizeof a);
+    a.dtype = d->logits_dtype; a.rows = rows; a.vocab = d->vocab; a.eos = d->eos_token_id;
+    a.tables = h->tables_dev;
+    a.sx = h->sx; a.sl_id = h->sl_id; a.sl_p = h->sl_p; a.sl_key = h->sl_key;
+    a.sh_key = h->sh_key; a.sh_cnt = h->sh_cnt;
+    a.vocab_pad = h->vocab_pad; a.sort_pad = h->sort_pad; a.hash_cap = h->hash_cap;
+    a.max_history = h->max_history;
+    a.dump_cap = d->dump_cap;
+
+    // logits
+    if (d->logits_mem == PGS_MEM_HOST) {
+        const size_t need = (size_t)rows * d->vocab * esz;
+        if (need > h->logits_stage_bytes) {
+            if (h->logits_stage) { cudaStreamSynchronize(stream); cudaFree(h->logits_stage); h->logits_stage = nullptr; }
+            const size_t full = (size_t)h->max_rows * h->max_vocab * 4;
+            PGS_CUDA(h, cudaMalloc(&h->logits_stage, full));
+            h->logits_stage_bytes = full;
+        }
+        PGS_CUDA(h, cudaMemcpy2DAsync(h->logits_stage, (size_t)d->vocab * esz, d->logits,
+                                      (size_t)d->row_stride * esz, (size_t)d->vocab * esz, rows,
+                                      cudaMemcpyHostToDevice, stream));
+        a.logits = h->logits_stage;
+        a.row_stride = d->vocab;
+    } else {
+        a.logits = d->logits;
+        a.row_stride = d->row_stride;
+    }
+
+    AuxPlan plan{h};
+    uint64_t hist_total = 0, masked_rows = 0;
+    if (d->aux_mem == PGS_MEM_HOST) {
+        if (d->hist_offsets) {
+            hist_total = d->hist_offsets[rows];
+            for (uint32_t r = 0; r < rows; r++) {
+                if (d->hist_offsets[r + 1] < d->hist_offsets[r])
+                    return fail(h, PGS_ERR_INVALID, "hist_offsets must be non-decreasing");
+                if (d->hist_offsets[r + 1] - d->hist_offsets[r] > h->max_history)
+                    return fail(h, PGS_ERR_LIMIT, "row %u has %u history ids; the handle allows %u", r,
+                                d->hist_offsets[r + 1] - d->hist_offsets[r], h->max_history);
+            }
+        }
+        if (d->mask_table)
+            for (uint32_t r = 0; r < rows; r++) masked_rows += d->mask_table[r] >= 0;
+        a.temperature = plan.in(d->temperature, rows);
+        a.top_k = plan.in(d->top_k, rows);
+        a.top_p = plan.in(d->top_p, rows);
+        a.freq = plan.in(d->frequency_penalty, rows);
+        a.pres = plan.in(d->presence_penalty, rows);
+        a.rep = plan.in(d->repetition_penalty, rows);
+        a.hist_offsets = plan.in(d->hist_offsets, (size_t)rows + 1);
+        a.hist_ids = d->hist_offsets ? plan.in(d->hist_ids ? d->hist_ids : (const uint32_t*)"", hist_total) : nullptr;
+        a.mask_table = plan.in(d->mask_table, rows);
+        a.mask_state = plan.in(d->mask_state, rows);
+        a.uniform = plan.in(d->uniform, rows);
+        const size_t in_bytes = plan.used;
+        plan.out_lo = (plan.used + 15) & ~size_t(15);
+        a.token = plan.out(d->token, rows);
+        a.status = plan.out(d->status, rows);
+        a.drew = plan.out(d->drew, rows);
+        a.argmax = plan.out(d->argmax, rows);
+        a.row_max = plan.out(d->row_max, rows);
+        a.sumexp = plan.out(d->sumexp, rows);
+        a.total = plan.out(d->total, rows);
+        a.n_kept = plan.out(d->n_kept, rows);
+        plan.out_hi = plan.used;
+        if (plan.overflow)
+            return fail(h, PGS_ERR_LIMIT, "per-row arrays exceed the staging buffer sized at creation");
+        // the candidate dump can be large; it gets its own device buffer per call
+        uint32_t* dump_ids_dev = nullptr;
+        float* dump_probs_dev = nullptr;
+        const size_t dump_n = (size_t)rows * d->dump_cap;
+        if (d->dump_ids) PGS_CUDA(h, cudaMalloc(&dump_ids_dev, dump_n * 4));
+        if (d->dump_probs) PGS_CUDA(h, cudaMalloc(&dump_probs_dev, dump_n * 4));
+        a.dump_ids = dump_ids_dev; a.dump_probs = dump_probs_dev;
+        PGS_CUDA(h, cudaMemcpyAsync(h->aux_dev, h->aux_host, in_bytes, cudaMemcpyHostToDevice, stream));
+        const uint32_t grid = rows < h->slots ? rows : h->slots;
+        PGS_CUDA(h, pgs::launch_general(a, grid, stream));
+        h->counters.kernel_launches += 1;
+        PGS_CUDA(h, cudaMemcpyAsync(h->aux_host + plan.out_lo, h->aux_dev + plan.out_lo,
+                                    plan.out_hi - plan.out_lo, cudaMemcpyDeviceToHost, stream));
+        if (dump_ids_dev) PGS_CUDA(h, cudaMemcpyAsync(d->dump_ids, dump_ids_dev, dump_n * 4, cudaMemcpyDeviceToHost, stream));
+        if (dump_probs_dev) PGS_CUDA(h, cudaMemcpyAsync(d->dump_probs, dump_probs_dev, dump_n * 4, cudaMemcpyDeviceToHost, stream));
+        cudaError_t e = cudaStreamSynchronize(stream);
+        cudaFree(dump_ids_dev); cudaFree(dump_probs_dev);
+        if (e != cudaSuccess) return fail(h, PGS_ERR_CUDA, "kernel or copy failed: %s", cudaGetErrorString(e));
+        for (const auto& o : plan.outs) memcpy(o.dst, h->aux_host + o.off, o.bytes);
+    } else {
+        a.temperature = d->temperature; a.top_k = d->top_k; a.top_p = d->top_p;
+        a.freq = d->frequency_penalty; a.pres = d->presence_penalty; a.rep = d->repetition_penalty;
+        a.hist_offsets = d->hist_offsets; a.hist_ids = d->hist_ids;
+        a.mask_table = d->mask_table; a.mask_state = d->mask_state; a.uniform = d->uniform;
+        a.token = d->token; a.status = d->status; a.drew = d->drew; a.argmax = d->argmax;
+        a.row_max = d->row_max; a.sumexp = d->sumexp; a.total = d->total; a.n_kept = d->n_kept;
+        a.dump_ids = d->dump_ids; a.dump_probs = d->dump_probs;
+        const uint32_t grid = rows < h->slots ? rows : h->slots;
+        PGS_CUDA(h, pgs::launch_general(a, grid, stream));
+        h->counters.kernel_launches += 1;
+        if (wait) {
+            cudaError_t e = cudaStreamSynchronize(stream);
+            if (e != cudaSuccess) return fail(h, PGS_ERR_CUDA, "kernel failed: %s", cudaGetErrorString(e));
+        }
+    }
+    h->counters.calls += 1;
+    h->counters.rows += rows;
+    h->counters.bytes += (uint64_t)rows * (d->vocab * esz + 64) + hist_total * 4 + masked_rows * (d->vocab / 8);
+    if (d->aux_mem == PGS_MEM_HOST)
+        for (uint32_t r = 0; r < rows; r++) h->counters.rows_faulted += d->status[r] == PGS_ROW_NONFINITE;
+    return PGS_OK;
+}
+
+}  // namespace
+
+extern "C" int pgs_sample_batch(pgs_handle* h, const pgs_batch_desc* desc) {
+    if (!h) return PGS_ERR_INVALID;
+    return run_batch(h, desc, h->stream, true);
+}
+
+extern "C" int pgs_sample_batch_async(pgs_handle* h, const pgs_batch_desc* desc, void* cuda_stream) {
+    if (!h) return PGS_ERR_INVALID;
+    if (desc && (desc->logits_mem != PGS_MEM_DEVICE || desc->aux_mem != PGS_MEM_DEVICE))
+        return fail(h, PGS_ERR_INVALID, "pgs_sample_batch_async needs every array in device memory");
+    return run_batch(h, desc, cuda_stream ? (cudaStream_t)cuda_stream : h->stream, false);
+}

@@ -1,0 +1,299 @@
+// General row kernel: one 1024-thread CTA walks one batch row through the whole chain of
+// Engine::advance_with_logits (pagoda/src/engine.rs:1286-1314) with its working copy of the row
+// in a global-memory scratch slot.  It accepts every shape and parameter combination (any vocab
+// size or alignment, top-k off, top-p without top-k, thousands of tied candidates, long
+// histories) and is the path rows take when the fused cluster kernel cannot hold them.
+//
+// Order of operations per row, as the reference runs them:
+//   sanity (engine.rs:1278-1295) -> repetition* / frequency / presence penalties
+//   (engine.rs:1553-1573; * extension) -> grammar bitmask (grammar.rs:73-85) -> EOS fix
+//   (engine.rs:1307-1312) -> argmax (sampler.rs:59-70) or temperature softmax, top-k, top-p and
+//   the inverse-CDF walk (sampler.rs:28-55, 92-150).
+#include "pgs_args.cuh"
+#include "pgs_block.cuh"
+
+#include <cuda_bf16.h>
+
+namespace pgs {
+
+struct GeneralSmem {
+    ReduceSmem rs;
+    SeqSmem seq;
+    SelectSmem sel;
+    unsigned long long sort_tile[SORT_TILE];
+    unsigned long long exp_tab[32];
+};
+
+__device__ __forceinline__ float load_logit(const void* base, uint32_t dtype, size_t i) {
+    if (dtype == 0) return ((const float*)base)[i];
+    return __uint_as_float((uint32_t)((const unsigned short*)base)[i] << 16);
+}
+
+__device__ __forceinline__ void write_row(const RowArgs& a, uint32_t row, uint32_t token, int status,
+                                          int drew, uint32_t amax, float rmax, float sumexp,
+                                          float total, uint32_t n_kept) {
+    a.token[row] = token;
+    a.status[row] = status;
+    if (a.drew) a.drew[row] = (uint8_t)drew;
+    if (a.argmax) a.argmax[row] = amax;
+    if (a.row_max) a.row_max[row] = rmax;
+    if (a.sumexp) a.sumexp[row] = sumexp;
+    if (a.total) a.total[row] = total;
+    if (a.n_kept) a.n_kept[row] = n_kept;
+}
+
+__global__ void __launch_bounds__(NT, 1) general_row_kernel(const RowArgs a) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    GeneralSmem& sm = *reinterpret_cast<GeneralSmem*>(smem_raw);
+    const int tid = threadIdx.x;
+    const uint32_t V = a.vocab;
+    const uint32_t slot = blockIdx.x;
+    if (tid < 32) sm.exp_tab[tid] = kExp2TableDev[tid];
+    __syncthreads();
+    const unsigned long long* tab = sm.exp_tab;
+
+    const uint32_t n_work = a.work_rows ? *a.work_count : a.rows;
+    for (uint32_t w = blockIdx.x; w < n_work; w += gridDim.x) {
+        const uint32_t row = a.work_rows ? a.work_rows[w] : w;
+        __syncthreads();
+        // ---------------------------------------------------------------- parameters
+        const float temp = a.temperature ? a.temperature[row] : 0.0f;
+        const uint32_t top_k = a.top_k ? a.top_k[row] : 0u;
+        const float top_p = a.top_p ? a.top_p[row] : 1.0f;
+        const float freq = a.freq ? a.freq[row] : 0.0f;
+        const float pres = a.pres ? a.pres[row] : 0.0f;
+        const float rep = a.rep ? a.rep[row] : 1.0f;
+        const float u01 = a.uniform ? a.uniform[row] : 0.0f;
+        bool bad = !finite_f(temp) || !finite_f(top_p) || !finite_f(freq) || !finite_f(pres) ||
+                   !finite_f(rep) || !(rep > 0.0f) || !finite_f(u01);
+        const uint32_t* mw = nullptr;
+        uint32_t gflags = 0;
+        if (a.mask_table && a.mask_table[row] >= 0) {
+            const int32_t t = a.mask_table[row];
+            const int32_t st = a.mask_state ? a.mask_state[row] : 0;
+            if (t >= MAX_TABLES || !a.tables[t].live || st < 0 || (uint32_t)st >= a.tables[t].n_states ||
+                (unsigned long long)a.tables[t].words_per_state * 32ull < V) {
+                bad = true;
+            } else {
+                mw = a.tables[t].words + (size_t)st * a.tables[t].words_per_state;
+                gflags = a.tables[t].flags[st];
+            }
+        }
+        uint32_t h0 = 0, nh = 0;
+        if (a.hist_offsets) {
+            h0 = a.hist_offsets[row];
+            const uint32_t h1 = a.hist_offsets[row + 1];
+            if (h1 < h0 || h1 - h0 > a.max_history) bad = true; else nh = h1 - h0;
+        }
+        if (bad) {
+            if (tid == 0) write_row(a, row, 0u, ROW_BAD_PARAM, 0, 0u, -INFINITY, 0.0f, 0.0f, 0u);
+            continue;
+        }
+
+        // ------------------------------------------------ sanity + upcast + grammar bitmask
+        float* X = a.sx + (size_t)slot * a.vocab_pad;
+        const char* rowp = (const char*)a.logits + (size_t)row * a.row_stride * (a.dtype == 0 ? 4 : 2);
+        int nonfinite = 0;
+        if (a.dtype == 0 && (((uintptr_t)rowp & 15) == 0) && (V & 3) == 0) {
+            const float4* src = (const float4*)rowp;
+            for (uint32_t q = tid; q < V / 4; q += NT) {
+                float4 v = src[q];
+                nonfinite |= !finite_f(v.x) | !finite_f(v.y) | !finite_f(v.z) | !finite_f(v.w);
+                if (mw) {
+                    const uint32_t bits = mw[q >> 3] >> ((q & 7) * 4);
+                    if (!(bits & 1u)) v.x = -INFINITY;
+                    if (!(bits & 2u)) v.y = -INFINITY;
+                    if (!(bits & 4u)) v.z = -INFINITY;
+                    if (!(bits & 8u)) v.w = -INFINITY;
+                }
+                ((float4*)X)[q] = v;
+            }
+        } else {
+            for (uint32_t i = tid; i < V; i += NT) {
+                float x = load_logit(rowp, a.dtype, i);
+                nonfinite |= !finite_f(x);
+                if (mw && !((mw[i >> 5] >> (i & 31)) & 1u)) x = -INFINITY;
+                X[i] = x;
+            }
+        }
+        nonfinite = __syncthreads_or(nonfinite);
+        if (nonfinite) {
+            if (tid == 0) write_row(a, row, 0u, ROW_NONFINITE, 0, 0u, -INFINITY, 0.0f, 0.0f, 0u);
+            continue;
+        }
+        if (gflags & 2u) {
+            if (tid == 0) write_row(a, row, 0u, ROW_DEAD, 0, 0u, -INFINITY, 0.0f, 0.0f, 0u);
+            continue;
+        }
+
+        // ----------------------------------------------------------------- penalties
+        const bool do_fp = !(fabsf(freq) < 1e-6f && fabsf(pres) < 1e-6f);
+        const bool do_pres = fabsf(pres) > 1e-6f;
+        const bool do_rep = rep != 1.0f;
+        if (nh > 0 && (do_fp || do_rep)) {
+            uint32_t cap = 64;
+            while (cap < 2 * nh) cap <<= 1;   // <= hash_cap because nh <= max_history
+            uint32_t* hk = a.sh_key + (size_t)slot * a.hash_cap;
+            uint32_t* hc = a.sh_cnt + (size_t)slot * a.hash_cap;
+            for (uint32_t s = tid; s < cap; s += NT) { hk[s] = 0xffffffffu; hc[s] = 0u; }
+            __syncthreads();
+            for (uint32_t j = tid; j < nh; j += NT) {
+                const uint32_t id = a.hist_ids[h0 + j];
+                if (id >= V) continue;
+                uint32_t s = (id * 2654435761u) & (cap - 1);
+                for (uint32_t probe = 0; probe < cap; probe++) {
+                    const uint32_t prev = atomicCAS(&hk[s], 0xffffffffu, id);
+                    if (prev == 0xffffffffu || prev == id) { atomicAdd(&hc[s], 1u); break; }
+                    s = (s + 1) & (cap - 1);
+                }
+            }
+            __syncthreads();
+            for (uint32_t s = tid; s < cap; s += NT) {
+                const uint32_t id = hk[s];
+                if (id == 0xffffffffu) continue;
+                float x = X[id];
+                if (do_rep) x = x > 0.0f ? fdiv(x, rep) : fmul(x, rep);
+                if (do_fp) {
+                    x = fsub(x, fmul(freq, (float)hc[s]));
+                    if (do_pres) x = fsub(x, pres);
+                }
+                X[id] = x;
+            }
+            __syncthreads();
+        }
+        // ------------------------------------------------------------------- EOS fix
+        if (mw && (gflags & 1u) && a.eos >= 0 && (uint32_t)a.eos < V && tid == 0 &&
+            !finite_f(X[a.eos]))
+            X[a.eos] = 0.0f;
+        __syncthreads();
+
+        // --------------------------------------------------------- max / argmax (lowest id)
+        unsigned long long best = 0ull;
+        for (uint32_t i = tid; i < V; i += NT) {
+            const unsigned long long k = order_key(X[i]);
+            if (k) {
+                const unsigned long long cand = (k << 32) | (unsigned long long)(0xffffffffu - i);
+                best = cand > best ? cand : best;
+            }
+        }
+        best = block_max_u64(best, sm.rs);
+        const bool any = best != 0ull;
+        const float m = any ? key_to_float((uint32_t)(best >> 32)) : -INFINITY;
+        const uint32_t amax = any ? 0xffffffffu - (uint32_t)best : 0u;
+        const int status = any ? ROW_OK : ROW_EMPTY;
+        if (temp < 1e-5f) {
+            if (tid == 0) write_row(a, row, amax, status, 0, amax, m, 0.0f, 0.0f, 0u);
+            continue;
+        }
+
+        // ------------------------------- temperature softmax numerators and their f32 fold
+        const float t = fmaxf(temp, 1e-9f);
+        const float S = seq_scan(
+            [&](int i) { const float e = softmax_num(X[i], m, t, tab); X[i] = e; return e; },
+            (int)V, 0.0f, SEQ_SUM, 0.0f, nullptr, sm.seq, sm.rs);
+        const bool norm = S > 1e-9f;
+        auto prob = [&](int i) { const float e = X[i]; return norm ? fdiv(e, S) : e; };
+        const bool use_k = top_k != 0u && top_k < V;
+        const bool use_p = !(top_p >= 1.0f);
+        const bool want_list = use_k || use_p || a.n_kept || a.dump_ids || a.dump_probs;
+
+        uint32_t token = amax, n_kept = 0;
+        int drew = 0;
+        float total = 0.0f;
+        if (!want_list) {
+            // plain categorical over the whole vocabulary
+            total = seq_scan(prob, (int)V, 0.0f, SEQ_SUM, 0.0f, nullptr, sm.seq, sm.rs);
+            if (total > 1e-9f) {
+                int found;
+                seq_scan(prob, (int)V, 0.0f, SEQ_FIND_GT, fmul(u01, total), &found, sm.seq, sm.rs);
+                token = found >= 0 ? (uint32_t)found : V - 1;
+                drew = 1;
+            }
+        } else {
+            // top-k threshold on probabilities: ties at the threshold all survive (sampler.rs:124)
+            float thr = 0.0f;
+            if (use_k) {
+                const uint32_t kk = radix_select_kth([&](int i) { return f2u(X[i]); }, (int)V, top_k,
+                                                     sm.sel, sm.rs);
+                thr = norm ? fdiv(u2f(kk), S) : u2f(kk);
+            }
+            // ordered compaction of the survivors with non-zero probability
+            uint32_t* lid = a.sl_id + (size_t)slot * a.vocab_pad;
+            float* lp = a.sl_p + (size_t)slot * a.vocab_pad;
+            uint32_t n = 0;
+            for (uint32_t base = 0; base < V; base += NT * 4) {
+                const uint32_t i0 = base + tid * 4;
+                float p[4];
+                uint32_t cnt = 0;
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                    p[j] = (i0 + j < V) ? prob((int)(i0 + j)) : 0.0f;
+                    if (!(p[j] > 0.0f && p[j] >= thr)) p[j] = 0.0f;
+                    cnt += p[j] > 0.0f;
+                }
+                uint32_t tot;
+                uint32_t at = n + block_excl_scan_u32(cnt, &tot, sm.rs);
+#pragma unroll
+                for (int j = 0; j < 4; j++)
+                    if (p[j] > 0.0f) { lid[at] = i0 + j; lp[at] = p[j]; at++; }
+                n += tot;
+            }
+            __syncthreads();
+            // top-p: walk the candidates by probability descending, id ascending (sampler.rs:134-144)
+            if (use_p && n > 0) {
+                uint32_t npad = 2;
+                while (npad < n) npad <<= 1;
+                unsigned long long* keys =
+                    npad <= (uint32_t)SORT_TILE ? sm.sort_tile : a.sl_key + (size_t)slot * a.sort_pad;
+                for (uint32_t j = tid; j < npad; j += NT)
+                    keys[j] = j < n ? ((unsigned long long)(~f2u(lp[j])) << 32) | j : ~0ull;
+                bitonic_sort(keys, (int)npad, sm.sort_tile);
+                int found;
+                seq_scan([&](int j) { return u2f(~(uint32_t)(keys[j] >> 32)); }, (int)n, 0.0f,
+                         SEQ_FIND_GE, top_p, &found, sm.seq, sm.rs);
+                if (found >= 0)
+                    for (uint32_t j = (uint32_t)found + 1 + tid; j < n; j += NT)
+                        lp[(uint32_t)keys[j]] = 0.0f;
+                __syncthreads();
+            }
+            total = seq_scan([&](int j) { return lp[j]; }, (int)n, 0.0f, SEQ_SUM, 0.0f, nullptr, sm.seq,
+                             sm.rs);
+            if (total > 1e-9f) {
+                int found;
+                seq_scan([&](int j) { return lp[j]; }, (int)n, 0.0f, SEQ_FIND_GT, fmul(u01, total),
+                         &found, sm.seq, sm.rs);
+                token = found >= 0 ? lid[found] : V - 1;
+                drew = 1;
+            }
+            if (a.n_kept || a.dump_ids || a.dump_probs) {
+                for (uint32_t base = 0; base < n; base += NT) {
+                    const uint32_t j = base + tid;
+                    const uint32_t keep = (j < n && lp[j] > 0.0f) ? 1u : 0u;
+                    uint32_t tot;
+                    const uint32_t at = n_kept + block_excl_scan_u32(keep, &tot, sm.rs);
+                    if (keep && at < a.dump_cap) {
+                        if (a.dump_ids) a.dump_ids[(size_t)row * a.dump_cap + at] = lid[j];
+                        if (a.dump_probs) a.dump_probs[(size_t)row * a.dump_cap + at] = lp[j];
+                    }
+                    n_kept += tot;
+                }
+            }
+        }
+        if (tid == 0) write_row(a, row, token, status, drew, amax, m, S, total, n_kept);
+    }
+}
+
+size_t general_smem_bytes() { return sizeof(GeneralSmem); }
+
+// once per device, with that device current
+cudaError_t configure_general() {
+    return cudaFuncSetAttribute(general_row_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                (int)sizeof(GeneralSmem));
+}
+
+cudaError_t launch_general(const RowArgs& a, uint32_t grid, cudaStream_t stream) {
+    general_row_kernel<<<grid, NT, sizeof(GeneralSmem), stream>>>(a);
+    return cudaGetLastError();
+}
+
+}  // namespace pgs
