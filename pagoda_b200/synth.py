@@ -95,6 +95,19 @@ class Workload:
     def logits_f32(self) -> np.ndarray:
         return bf16_bits_to_f32(self.logits).reshape(self.logits.shape) if self.is_bf16 else self.logits
 
+    def head(self, n: int) -> "Workload":
+        """The first n rows as a workload of their own."""
+        import copy
+        w = copy.copy(self)
+        for k in ("logits", "temperature", "top_k", "top_p", "frequency_penalty", "presence_penalty",
+                  "repetition_penalty", "uniform"):
+            setattr(w, k, getattr(self, k)[:n])
+        if self.hist_offsets is not None:
+            w.hist_offsets = self.hist_offsets[:n + 1]
+        if self.mask_state is not None:
+            w.mask_state = self.mask_state[:n]
+        return w
+
     def algorithmic_bytes(self) -> int:
         """Bytes the chain has to touch: every logit once, the bitmask of masked rows, the history
         ids, and 64 B of per-row parameters and results."""
