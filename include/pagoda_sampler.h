@@ -128,6 +128,14 @@ PGS_API int pgs_sample_batch(pgs_handle *h, const pgs_batch_desc *desc);
  * without waiting.  Every array must be device memory. */
 PGS_API int pgs_sample_batch_async(pgs_handle *h, const pgs_batch_desc *desc, void *cuda_stream);
 
+/* Fidelity switch.  By default rows run in the fused kernel: every decision follows the
+ * reference, candidate probabilities use the exact expf, and the f32 left-fold sum of
+ * temperature_softmax (sampler.rs:99-113) agrees with the reference's to about 1e-6 relative,
+ * so a top-p or CDF decision can differ only when it sits that close to its boundary.  With
+ * `on` != 0 every row takes the general kernel, which reproduces that sum -- and therefore
+ * every token id -- bit for bit, at a fraction of the speed.  (Environment: PGS_EXACT=1.) */
+PGS_API int pgs_set_exact(pgs_handle *h, int on);
+
 /* Counters since creation (for the engine's /stats): rows sampled, rows faulted, algorithmic
  * bytes touched. */
 typedef struct pgs_counters {

@@ -19,7 +19,7 @@ MEM_DEVICE, MEM_HOST = 0, 1
 ROW_OK, ROW_NONFINITE, ROW_DEAD, ROW_EMPTY, ROW_BAD_PARAM = 0, 1, 2, 3, 4
 
 EXPORTS = ["pgs_create", "pgs_destroy", "pgs_last_error", "pgs_mask_table_upload", "pgs_mask_table_free",
-           "pgs_sample_batch", "pgs_sample_batch_async", "pgs_get_counters", "pgs_stream"]
+           "pgs_sample_batch", "pgs_sample_batch_async", "pgs_get_counters", "pgs_stream", "pgs_set_exact"]
 
 
 class SamplerError(RuntimeError):
@@ -76,6 +76,7 @@ def load_library():
     L.pgs_sample_batch.argtypes = [C.c_void_p, C.POINTER(BatchDesc)]
     L.pgs_sample_batch_async.argtypes = [C.c_void_p, C.POINTER(BatchDesc), C.c_void_p]
     L.pgs_get_counters.argtypes = [C.c_void_p, C.POINTER(Counters)]
+    L.pgs_set_exact.argtypes = [C.c_void_p, C.c_int]
     L.pgs_stream.restype = C.c_void_p
     L.pgs_stream.argtypes = [C.c_void_p]
     _lib = L
@@ -130,6 +131,10 @@ class Sampler:
     def _check(self, rc: int):
         if rc != 0:
             raise SamplerError(rc, self._lib.pgs_last_error(self._h).decode())
+
+    def set_exact(self, on: bool):
+        """Route every row through the bit-exact general kernel (see pgs_set_exact)."""
+        self._check(self._lib.pgs_set_exact(self._h, int(on)))
 
     @property
     def stream_ptr(self) -> int:

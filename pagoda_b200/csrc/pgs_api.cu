@@ -6,6 +6,7 @@
 #include <cuda_runtime.h>
 #include <stdarg.h>
 #include <stdio.h>
+#include <stdlib.h>
 #include <string.h>
 
 #include <new>
@@ -17,6 +18,17 @@ namespace pgs {
 cudaError_t configure_general();
 cudaError_t launch_general(const RowArgs& a, uint32_t grid, cudaStream_t stream);
 size_t general_smem_bytes();
+
+struct FusedLaunch {
+    uint32_t cluster, slice_len, chunk;
+    uint32_t* work_rows;
+    uint32_t* work_count;
+};
+size_t fused_smem_bytes(uint32_t slice_len);
+cudaError_t configure_fused(size_t max_smem);
+cudaError_t fused_max_clusters(uint32_t cluster, size_t smem, int* out);
+cudaError_t launch_fused(const RowArgs& a, const FusedLaunch& fl, uint32_t n_clusters, size_t smem,
+                         cudaStream_t stream);
 }  // namespace pgs
 
 static thread_local char g_create_error[256] = "";
@@ -43,6 +55,13 @@ struct pgs_handle {
     unsigned char* aux_host = nullptr;   // pinned
     unsigned char* aux_dev = nullptr;
     size_t aux_bytes = 0;
+    // fused cluster kernel: launch shape for the last vocabulary size seen, and its work list
+    size_t smem_optin = 0;
+    uint32_t fused_vocab = 0, fused_cluster = 0, fused_slice = 0, fused_chunk = 0, fused_clusters = 0;
+    size_t fused_smem = 0;
+    uint32_t* work_rows = nullptr;
+    uint32_t* work_count = nullptr;   // [2]
+    int exact = 0;
     pgs_counters counters = {};
     char err[256] = "";
 };
@@ -98,7 +117,7 @@ static int destroy_impl(pgs_handle* h) {
     }
     cudaFree(h->sx); cudaFree(h->sl_id); cudaFree(h->sl_p); cudaFree(h->sl_key);
     cudaFree(h->sh_key); cudaFree(h->sh_cnt); cudaFree(h->tables_dev);
-    cudaFree(h->logits_stage); cudaFree(h->aux_dev);
+    cudaFree(h->logits_stage); cudaFree(h->aux_dev); cudaFree(h->work_rows); cudaFree(h->work_count);
     if (h->aux_host) cudaFreeHost(h->aux_host);
     if (h->stream) cudaStreamDestroy(h->stream);
     delete h;
@@ -133,6 +152,12 @@ extern "C" int pgs_create(int device, uint32_t max_rows, uint32_t max_vocab, uin
         h->sm_count = prop.multiProcessorCount;
         PGS_CUDA(nullptr, cudaStreamCreateWithFlags(&h->stream, cudaStreamNonBlocking));
         PGS_CUDA(nullptr, pgs::configure_general());
+        h->smem_optin = prop.sharedMemPerBlockOptin;
+        PGS_CUDA(nullptr, pgs::configure_fused(h->smem_optin));
+        PGS_CUDA(nullptr, cudaMalloc(&h->work_rows, (size_t)max_rows * sizeof(uint32_t)));
+        PGS_CUDA(nullptr, cudaMalloc(&h->work_count, 2 * sizeof(uint32_t)));
+        PGS_CUDA(nullptr, cudaMemsetAsync(h->work_count, 0, 2 * sizeof(uint32_t), h->stream));
+        if (const char* ev = getenv("PGS_EXACT")) h->exact = atoi(ev);
         h->max_rows = max_rows; h->max_vocab = max_vocab; h->max_history = max_history;
         h->slots = max_rows < (uint32_t)h->sm_count ? max_rows : (uint32_t)h->sm_count;
         h->vocab_pad = (max_vocab + 31u) & ~31u;
@@ -229,6 +254,49 @@ extern "C" int pgs_mask_table_free(pgs_handle* h, int32_t table_id) {
 // ------------------------------------------------------------------------------ batches
 
 namespace {
+
+// Launch shape of the fused kernel for a vocabulary size: the smallest cluster whose slices fit
+// in shared memory.  Returns false when no cluster of up to 8 CTAs can hold the row.
+bool fused_shape(pgs_handle* h, uint32_t vocab) {
+    if (h->fused_vocab == vocab) return h->fused_clusters > 0;
+    h->fused_vocab = vocab;
+    h->fused_clusters = 0;
+    for (uint32_t c = 1; c <= 8; c *= 2) {
+        const uint32_t slice = (((vocab + c - 1) / c) + 31u) & ~31u;
+        const size_t smem = pgs::fused_smem_bytes(slice);
+        if (smem > h->smem_optin) continue;
+        int n = 0;
+        if (pgs::fused_max_clusters(c, smem, &n) != cudaSuccess || n <= 0) { cudaGetLastError(); continue; }
+        uint32_t chunk = (slice + 1023u) / 1024u;
+        if ((chunk & 1u) == 0) chunk += 1;   // odd stride: conflict-free shared-memory access
+        h->fused_cluster = c; h->fused_slice = slice; h->fused_chunk = chunk; h->fused_smem = smem;
+        h->fused_clusters = (uint32_t)n;
+        return true;
+    }
+    return false;
+}
+
+// One step: the fused cluster kernel serves every row it can hold and lists the others, which
+// the general kernel then processes.  In exact mode every row takes the general kernel.
+int launch_step(pgs_handle* h, pgs::RowArgs& a, cudaStream_t stream) {
+    const uint32_t rows = a.rows;
+    const uint32_t grid = rows < h->slots ? rows : h->slots;
+    if (h->exact || !fused_shape(h, a.vocab)) {
+        PGS_CUDA(h, pgs::launch_general(a, grid, stream));
+        h->counters.kernel_launches += 1;
+        return PGS_OK;
+    }
+    pgs::FusedLaunch fl;
+    fl.cluster = h->fused_cluster; fl.slice_len = h->fused_slice; fl.chunk = h->fused_chunk;
+    fl.work_rows = h->work_rows; fl.work_count = h->work_count;
+    const uint32_t nc = rows < h->fused_clusters ? rows : h->fused_clusters;
+    PGS_CUDA(h, pgs::launch_fused(a, fl, nc, h->fused_smem, stream));
+    a.work_rows = h->work_rows;
+    a.work_count = h->work_count;
+    PGS_CUDA(h, pgs::launch_general(a, grid, stream));
+    h->counters.kernel_launches += 2;
+    return PGS_OK;
+}
 
 struct AuxPlan {
     pgs_handle* h;
@@ -365,9 +433,8 @@ int run_batch(pgs_handle* h, const pgs_batch_desc* d, cudaStream_t stream, bool 
         if (d->dump_probs) PGS_CUDA(h, cudaMalloc(&dump_probs_dev, dump_n * 4));
         a.dump_ids = dump_ids_dev; a.dump_probs = dump_probs_dev;
         PGS_CUDA(h, cudaMemcpyAsync(h->aux_dev, h->aux_host, in_bytes, cudaMemcpyHostToDevice, stream));
-        const uint32_t grid = rows < h->slots ? rows : h->slots;
-        PGS_CUDA(h, pgs::launch_general(a, grid, stream));
-        h->counters.kernel_launches += 1;
+        rc = launch_step(h, a, stream);
+        if (rc != PGS_OK) { cudaFree(dump_ids_dev); cudaFree(dump_probs_dev); return rc; }
         PGS_CUDA(h, cudaMemcpyAsync(h->aux_host + plan.out_lo, h->aux_dev + plan.out_lo,
                                     plan.out_hi - plan.out_lo, cudaMemcpyDeviceToHost, stream));
         if (dump_ids_dev) PGS_CUDA(h, cudaMemcpyAsync(d->dump_ids, dump_ids_dev, dump_n * 4, cudaMemcpyDeviceToHost, stream));
@@ -384,9 +451,8 @@ int run_batch(pgs_handle* h, const pgs_batch_desc* d, cudaStream_t stream, bool 
         a.token = d->token; a.status = d->status; a.drew = d->drew; a.argmax = d->argmax;
         a.row_max = d->row_max; a.sumexp = d->sumexp; a.total = d->total; a.n_kept = d->n_kept;
         a.dump_ids = d->dump_ids; a.dump_probs = d->dump_probs;
-        const uint32_t grid = rows < h->slots ? rows : h->slots;
-        PGS_CUDA(h, pgs::launch_general(a, grid, stream));
-        h->counters.kernel_launches += 1;
+        rc = launch_step(h, a, stream);
+        if (rc != PGS_OK) return rc;
         if (wait) {
             cudaError_t e = cudaStreamSynchronize(stream);
             if (e != cudaSuccess) return fail(h, PGS_ERR_CUDA, "kernel failed: %s", cudaGetErrorString(e));
@@ -401,6 +467,12 @@ int run_batch(pgs_handle* h, const pgs_batch_desc* d, cudaStream_t stream, bool 
 }
 
 }  // namespace
+
+extern "C" int pgs_set_exact(pgs_handle* h, int on) {
+    if (!h) return PGS_ERR_INVALID;
+    h->exact = on ? 1 : 0;
+    return PGS_OK;
+}
 
 extern "C" int pgs_sample_batch(pgs_handle* h, const pgs_batch_desc* desc) {
     if (!h) return PGS_ERR_INVALID;

@@ -62,7 +62,7 @@ struct RowArgs {
     uint32_t vocab_pad, sort_pad, hash_cap, max_history;
     // optional work list: process rows work_rows[0 .. *work_count) instead of 0 .. rows
     const uint32_t* work_rows;
-    const uint32_t* work_count;
+    uint32_t* work_count;           // [0] = number of listed rows, [1] = CTAs that finished the list
 };
 
 }  // namespace pgs

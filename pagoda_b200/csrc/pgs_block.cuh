@@ -340,7 +340,7 @@ __device__ __forceinline__ void bitonic_step(unsigned long long* a, int i, int j
     }
 }
 
-__device__ void bitonic_sort(unsigned long long* keys, int n_pad, unsigned long long* tile /*SORT_TILE*/) {
+__device__ __forceinline__ void bitonic_sort(unsigned long long* keys, int n_pad, unsigned long long* tile /*SORT_TILE*/) {
     const int tid = threadIdx.x;
     __syncthreads();
     if (n_pad <= SORT_TILE) {

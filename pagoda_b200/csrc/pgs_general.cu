@@ -281,6 +281,14 @@ __global__ void __launch_bounds__(NT, 1) general_row_kernel(const RowArgs a) {
         }
         if (tid == 0) write_row(a, row, token, status, drew, amax, m, S, total, n_kept);
     }
+    // the last CTA to finish a work list empties it for the next step
+    if (a.work_rows && tid == 0) {
+        __threadfence();
+        if (atomicAdd(a.work_count + 1, 1u) == gridDim.x - 1) {
+            a.work_count[0] = 0u;
+            a.work_count[1] = 0u;
+        }
+    }
 }
 
 size_t general_smem_bytes() { return sizeof(GeneralSmem); }

@@ -129,6 +129,15 @@ PGS_HD float fdiv(float a, float b) {
 #endif
 }
 
+#if defined(__CUDACC__)
+// hardware 2^x (a few ulp); 2^-inf = +0
+__device__ __forceinline__ float ex2_approx(float x) {
+    float y;
+    asm("ex2.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+#endif
+
 // Monotone map float -> uint32 (larger float = larger key).  Non-finite values get key 0, below
 // every finite value: the chain treats them as masked (sampler.rs:64, :100-108).
 PGS_HD uint32_t order_key(float x) {

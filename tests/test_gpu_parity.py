@@ -14,10 +14,14 @@ pytestmark = pytest.mark.gpu
 NEG_INF = float("-inf")
 
 
-@pytest.fixture(scope="module")
-def sampler():
+@pytest.fixture(scope="module", params=["exact", "fused"])
+def sampler(request):
+    """Both kernels behind the same ABI: `exact` routes every row through the general kernel
+    (bit-exact token ids), `fused` is the default fast path with its stated tolerance."""
     import pagoda_b200
     s = pagoda_b200.Sampler(device=0, max_rows=256, max_vocab=262144, max_history=4096)
+    s.set_exact(request.param == "exact")
+    s.exact = request.param == "exact"
     yield s
     s.close()
 
@@ -172,21 +176,26 @@ def test_random_small_shapes(sampler, oracle, synth, vocab):
     for seed in (11, 12):
         w = _random_workload(synth, seed * 100 + vocab, rows=24, vocab=vocab)
         got, want = run_both(sampler, oracle, w, dump_cap=min(vocab, 512))
-        assert_same(got, want, w)
+        assert_same(got, want, w, exact=sampler.exact)
         for r in range(w.rows):
             if want["status"][r] != 0 or w.temperature[r] < 1e-5:
                 continue
             _, probs = oracle_probs(oracle, w, r)
             ids = np.flatnonzero(probs > 0)
             n = min(len(ids), 512)
+            if not sampler.exact and want["margin"][r] <= 1e-5:
+                continue
             np.testing.assert_array_equal(got.dump_ids[r, :n], ids[:n].astype(np.uint32))
-            np.testing.assert_array_equal(got.dump_probs[r, :n].view(np.uint32), probs[ids[:n]].view(np.uint32))
+            if sampler.exact:
+                np.testing.assert_array_equal(got.dump_probs[r, :n].view(np.uint32), probs[ids[:n]].view(np.uint32))
+            else:
+                np.testing.assert_allclose(got.dump_probs[r, :n], probs[ids[:n]], rtol=1e-5, atol=0)
 
 
 def test_random_bf16_rows(sampler, oracle, synth):
     w = _random_workload(synth, 77, rows=16, vocab=5000, bf16=True)
     got, want = run_both(sampler, oracle, w)
-    assert_same(got, want, w)
+    assert_same(got, want, w, exact=sampler.exact)
 
 
 def test_row_stride_and_unaligned_rows(sampler, oracle, synth):
@@ -195,7 +204,7 @@ def test_row_stride_and_unaligned_rows(sampler, oracle, synth):
     padded[:, :1001] = w.logits
     got = sampler.sample_batch(padded, vocab=1001, row_stride=1027, diagnostics=True, **w.sampler_kwargs())
     want = oracle.sample_batch(w.logits, **w.oracle_kwargs())
-    assert_same(got, want, w)
+    assert_same(got, want, w, exact=sampler.exact)
 
 
 def test_ties_everywhere(sampler, oracle, synth):
@@ -210,7 +219,7 @@ def test_ties_everywhere(sampler, oracle, synth):
                    np.zeros(rows, np.float32), np.zeros(rows, np.float32), np.ones(rows, np.float32), None, None,
                    S.uniform_f32(6, rows))
     got, want = run_both(sampler, oracle, w)
-    assert_same(got, want, w)
+    assert_same(got, want, w, exact=sampler.exact)
 
 
 def test_uniform_of_exactly_one_falls_through(sampler, oracle):  # rng.rs:28-30, sampler.rs:54
@@ -230,7 +239,9 @@ def test_peaked_and_flat_temperatures(sampler, oracle, synth):
                    np.zeros(rows, np.float32), np.zeros(rows, np.float32), np.ones(rows, np.float32), None, None,
                    S.uniform_f32(22, rows))
     got, want = run_both(sampler, oracle, w)
-    assert_same(got, want, w)
+    # at T >= 100 neighbouring probabilities differ by less than the tolerance, so several rows
+    # legitimately sit on a boundary
+    assert_same(got, want, w, exact=sampler.exact, min_clear=0.5)
 
 
 # ---- the benchmark configurations at sizes the oracle finishes in seconds -----------------------
@@ -238,30 +249,35 @@ def test_peaked_and_flat_temperatures(sampler, oracle, synth):
 def test_config1_greedy_repetition(sampler, oracle, synth):
     w = synth.config1(rows=4)
     got, want = run_both(sampler, oracle, w)
-    assert_same(got, want, w)
+    assert_same(got, want, w, exact=sampler.exact)
 
 
 def test_config2_topk_topp(sampler, oracle, synth):
     w = synth.config2(rows=16)
     got, want = run_both(sampler, oracle, w, dump_cap=64)
-    assert_same(got, want, w)
+    assert_same(got, want, w, exact=sampler.exact)
     for r in range(w.rows):
         _, probs = oracle_probs(oracle, w, r)
         ids = np.flatnonzero(probs > 0)
+        if not sampler.exact and want["margin"][r] <= 1e-5:
+            continue
         np.testing.assert_array_equal(got.dump_ids[r, :len(ids)], ids.astype(np.uint32))
-        np.testing.assert_array_equal(got.dump_probs[r, :len(ids)].view(np.uint32), probs[ids].view(np.uint32))
+        if sampler.exact:
+            np.testing.assert_array_equal(got.dump_probs[r, :len(ids)].view(np.uint32), probs[ids].view(np.uint32))
+        else:
+            np.testing.assert_allclose(got.dump_probs[r, :len(ids)], probs[ids], rtol=1e-5, atol=0)
 
 
 def test_config3_grammar(sampler, oracle, synth):
     w = synth.config3(rows=16)
     got, want = run_both(sampler, oracle, w)
-    assert_same(got, want, w)
+    assert_same(got, want, w, exact=sampler.exact)
 
 
 def test_config4_heterogeneous_bf16(sampler, oracle, synth):
     w = synth.config4(rows=12)
     got, want = run_both(sampler, oracle, w)
-    assert_same(got, want, w)
+    assert_same(got, want, w, exact=sampler.exact)
 
 
 def test_full_vocab_categorical_and_top_p_without_top_k(sampler, oracle, synth):
@@ -271,7 +287,7 @@ def test_full_vocab_categorical_and_top_p_without_top_k(sampler, oracle, synth):
     w.top_k[:] = 0
     w.top_p[:] = np.array([1.0, 1.0, 0.9, 0.5, 0.99, 0.2], np.float32)
     got, want = run_both(sampler, oracle, w)
-    assert_same(got, want, w)
+    assert_same(got, want, w, exact=sampler.exact)
     # tokens only, no diagnostics: takes the list-free path
     plain = sampler.sample_batch(w.logits, **w.sampler_kwargs())
     np.testing.assert_array_equal(plain.token, want["token"])
