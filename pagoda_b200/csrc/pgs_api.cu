@@ -23,6 +23,7 @@ struct FusedLaunch {
     uint32_t cluster, slice_len, chunk;
     uint32_t* work_rows;
     uint32_t* work_count;
+    long long* prof;
 };
 size_t fused_smem_bytes(uint32_t slice_len);
 cudaError_t configure_fused(size_t max_smem);
@@ -62,6 +63,7 @@ struct pgs_handle {
     uint32_t* work_rows = nullptr;
     uint32_t* work_count = nullptr;   // [2]
     int exact = 0;
+    long long* prof = nullptr;        // phase timers of the fused kernel (PGS_PROFILE=1)
     pgs_counters counters = {};
     char err[256] = "";
 };
@@ -117,7 +119,7 @@ static int destroy_impl(pgs_handle* h) {
     }
     cudaFree(h->sx); cudaFree(h->sl_id); cudaFree(h->sl_p); cudaFree(h->sl_key);
     cudaFree(h->sh_key); cudaFree(h->sh_cnt); cudaFree(h->tables_dev);
-    cudaFree(h->logits_stage); cudaFree(h->aux_dev); cudaFree(h->work_rows); cudaFree(h->work_count);
+    cudaFree(h->logits_stage); cudaFree(h->aux_dev); cudaFree(h->work_rows); cudaFree(h->work_count); cudaFree(h->prof);
     if (h->aux_host) cudaFreeHost(h->aux_host);
     if (h->stream) cudaStreamDestroy(h->stream);
     delete h;
@@ -158,6 +160,12 @@ extern "C" int pgs_create(int device, uint32_t max_rows, uint32_t max_vocab, uin
         PGS_CUDA(nullptr, cudaMalloc(&h->work_count, 2 * sizeof(uint32_t)));
         PGS_CUDA(nullptr, cudaMemsetAsync(h->work_count, 0, 2 * sizeof(uint32_t), h->stream));
         if (const char* ev = getenv("PGS_EXACT")) h->exact = atoi(ev);
+        if (const char* ev = getenv("PGS_PROFILE")) {
+            if (atoi(ev)) {
+                PGS_CUDA(nullptr, cudaMalloc(&h->prof, 1024 * 16 * sizeof(long long)));
+                PGS_CUDA(nullptr, cudaMemsetAsync(h->prof, 0, 1024 * 16 * sizeof(long long), h->stream));
+            }
+        }
         h->max_rows = max_rows; h->max_vocab = max_vocab; h->max_history = max_history;
         h->slots = max_rows < (uint32_t)h->sm_count ? max_rows : (uint32_t)h->sm_count;
         h->vocab_pad = (max_vocab + 31u) & ~31u;
@@ -289,6 +297,7 @@ int launch_step(pgs_handle* h, pgs::RowArgs& a, cudaStream_t stream) {
     pgs::FusedLaunch fl;
     fl.cluster = h->fused_cluster; fl.slice_len = h->fused_slice; fl.chunk = h->fused_chunk;
     fl.work_rows = h->work_rows; fl.work_count = h->work_count;
+    fl.prof = h->prof;
     const uint32_t nc = rows < h->fused_clusters ? rows : h->fused_clusters;
     PGS_CUDA(h, pgs::launch_fused(a, fl, nc, h->fused_smem, stream));
     a.work_rows = h->work_rows;
@@ -467,6 +476,16 @@ int run_batch(pgs_handle* h, const pgs_batch_desc* d, cudaStream_t stream, bool 
 }
 
 }  // namespace
+
+// Phase timers of the fused kernel (clock ticks, [ctas x 16]); only with PGS_PROFILE=1.
+extern "C" PGS_API int pgs_debug_read_profile(pgs_handle* h, long long* out, uint32_t n_ctas) {
+    if (!h || !h->prof || n_ctas > 1024) return PGS_ERR_INVALID;
+    DeviceGuard g(h->device);
+    PGS_CUDA(h, cudaStreamSynchronize(h->stream));
+    PGS_CUDA(h, cudaMemcpy(out, h->prof, (size_t)n_ctas * 16 * sizeof(long long), cudaMemcpyDeviceToHost));
+    PGS_CUDA(h, cudaMemset(h->prof, 0, 1024 * 16 * sizeof(long long)));
+    return PGS_OK;
+}
 
 extern "C" int pgs_set_exact(pgs_handle* h, int on) {
     if (!h) return PGS_ERR_INVALID;

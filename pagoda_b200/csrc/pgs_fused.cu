@@ -11,7 +11,10 @@
 //   top-k: the k-th largest per-thread maximum bounds the k-th largest logit from below, so
 //          "logit >= that bound" is a superset of the top-k set that is only slightly larger;
 //          those candidates are gathered and the reference's rule is applied to them exactly
-//   softmax numerators in place + emulation of the reference's sequential f32 sum
+//   softmax numerators in place, then the reference's sequential f32 sum is followed chunk by
+//          chunk: every thread folds its consecutive terms with real f32 additions starting
+//          from the running value the fold has reached there (estimated by a prefix scan and
+//          refined once), so small terms are absorbed exactly where the reference absorbs them
 //   candidates: exact probabilities, top-k threshold with ties, top-p walk, inverse-CDF pick
 //
 // Fidelity of this path: argmax, masks, penalties and candidate sets follow the reference bit
@@ -40,38 +43,59 @@ constexpr int F_KMAX = 1024;       // largest top-k served here
 struct FusedXchg {                  // peers write their slot through DSMEM
     unsigned long long best[F_MAXC];
     int nonfinite[F_MAXC];
-    uint32_t ncand[F_MAXC];
     int spill[F_MAXC];
-    float approx_total[F_MAXC];
-    float acc_in;                   // exact running sum handed over by the previous CTA
-    float sum_final;                // written into CTA 0 by the last CTA
+    uint32_t ncand[F_MAXC];
+    float true_total[F_MAXC];       // plain sum of the slice's numerators
+    double fold1[F_MAXC];           // slice increment of the fold, first estimate
+    double fold2[F_MAXC];           // refined
+};
+
+// Candidate workspace of CTA 0.  It lives in the slice buffer, which is dead once the sum is known.
+struct FusedCand {
+    float p[F_MCAP];                // probabilities, arrival order
+    uint32_t sid[F_MCAP];           // ids ascending
+    float sp[F_MCAP];               // probabilities in id order (zeroed when dropped)
+    float rp[F_MCAP];               // probabilities descending (ties: id ascending)
+    uint32_t rpos[F_MCAP];          // position in the id-ordered list of the entry at each rank
+    SeqSmem seq;
 };
 
 // Shared-memory workspace of one CTA (the vocabulary slice follows it).  Regions are reused as
 // the row moves through its phases:
-//   r_a : id->count table (penalties)            -> merged candidate ids / logits (CTA 0)
-//   r_b : every CTA's per-thread maxima (top-k)   -> per-thread summaries of the sum emulation
-//   the slice itself (softmax numerators)         -> candidate probabilities / sort keys (CTA 0)
+//   r_a : id->count table (penalties)             -> merged candidate ids / logits (CTA 0)
+//   the slice itself (logits, then numerators)     -> FusedCand (CTA 0)
 struct FusedSmem {
     ReduceSmem rs;
+    double dscan[NW + 1];
     FusedXchg xchg[2];              // alternates between consecutive rows
     unsigned long long exp_tab[32];
     union {
         struct { uint32_t hkey[F_HASH]; uint32_t hcnt[F_HASH]; } pen;
         struct { uint32_t m_id[F_MCAP]; float m_x[F_MCAP]; } mrg;
     } r_a;
-    union {
-        float tmax_all[F_MAXC * NT];
-        struct { int tk[NT]; uint32_t td[NT]; } seq;
-    } r_b;
+    float tmax_all[F_MAXC * NT];    // every CTA's per-thread maxima
     uint8_t redo_max[NT];
     SelectSmem sel;
     uint32_t cand_id[F_LCAP];
     float cand_x[F_LCAP];
     uint32_t cand_n;
     uint32_t m_n;
-    float acc;
+    uint32_t n_live, n_keep;
+    float bcast_f;
+    uint32_t bcast_u;
+    int bcast_i;
 };
+
+// Optional phase timers (clock64 deltas of thread 0, summed over the rows of each CTA), enabled
+// by pointing `prof` at [gridDim.x x 16] counters.
+#define PGS_TICK(slot)                                              \
+    do {                                                            \
+        if (fl.prof && tid == 0) {                                  \
+            const long long now_ = clock64();                       \
+            fl.prof[blockIdx.x * 16 + (slot)] += now_ - tick_;      \
+            tick_ = now_;                                           \
+        }                                                           \
+    } while (0)
 
 struct FusedLaunch {
     uint32_t cluster;       // CTAs per row
@@ -79,14 +103,61 @@ struct FusedLaunch {
     uint32_t chunk;         // consecutive floats per thread in the sum pass (odd)
     uint32_t* work_rows;    // rows handed to the general kernel
     uint32_t* work_count;
+    long long* prof;
 };
 
-__device__ __forceinline__ float ld_stream_f32(const float* p) { return __ldcs(p); }
+// exclusive scan of one double per thread; *total = block sum
+__device__ __forceinline__ double block_excl_scan_f64(double v, double* total, double* ws /*NW+1*/) {
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+    double inc = v;
+    for (int o = 1; o < 32; o <<= 1) {
+        double t = __shfl_up_sync(FULL, inc, o);
+        if (lane >= o) inc += t;
+    }
+    __syncthreads();
+    if (lane == 31) ws[w] = inc;
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        double x = ws[threadIdx.x], xi = x;
+        for (int o = 1; o < 32; o <<= 1) {
+            double t = __shfl_up_sync(FULL, xi, o);
+            if (lane >= o) xi += t;
+        }
+        ws[threadIdx.x] = xi - x;
+        if (threadIdx.x == 31) ws[NW] = xi;
+    }
+    __syncthreads();
+    *total = ws[NW];
+    return ws[w] + (inc - v);
+}
 
-// exact left fold of `n` shared-memory floats starting from `a`
-__device__ __forceinline__ float fold_serial(const float* v, int n, float a) {
-    for (int j = 0; j < n; j++) a = fadd(a, v[j]);
-    return a;
+// Exact left fold of n <= 128 shared-memory floats by one warp (values travel by shuffle, so the
+// dependent chain is add + shuffle instead of add + shared-memory load).  mode/target as in
+// seq_scan; returns the running value, *found = first index where the predicate holds or -1.
+__device__ __forceinline__ float warp_fold(const float* v, int n, int mode, float target, int* found) {
+    const int lane = threadIdx.x & 31;
+    float reg[4];
+#pragma unroll
+    for (int u = 0; u < 4; u++) reg[u] = (lane + 32 * u < n) ? v[lane + 32 * u] : 0.0f;
+    float acc = 0.0f;
+    int f = -1;
+#pragma unroll
+    for (int u = 0; u < 4; u++) {
+        for (int l = 0; l < 32; l++) {
+            const int j = u * 32 + l;
+            if (j >= n || f >= 0) break;
+            acc = fadd(acc, __shfl_sync(FULL, reg[u], l));
+            if (mode != SEQ_SUM && seq_pred(mode, acc, target)) f = j;
+        }
+    }
+    if (found) *found = f;
+    return acc;
+}
+
+__device__ __forceinline__ uint32_t load_owner(uint32_t i, uint32_t len) {
+    // thread that loaded slice element i: 128-bit groups are dealt round-robin, then the ragged tail
+    const uint32_t body = (len / 4) * 4;
+    return i < body ? ((i >> 2) & (NT - 1)) : ((i - body) & (NT - 1));
 }
 
 __global__ void __launch_bounds__(NT, 1) fused_row_kernel(const RowArgs a, const FusedLaunch fl) {
@@ -94,7 +165,7 @@ __global__ void __launch_bounds__(NT, 1) fused_row_kernel(const RowArgs a, const
     FusedSmem& sm = *reinterpret_cast<FusedSmem*>(smem_raw);
     float* X = reinterpret_cast<float*>(smem_raw + ((sizeof(FusedSmem) + 15) & ~size_t(15)));
     cg::cluster_group cluster = cg::this_cluster();
-    const int tid = threadIdx.x, lane = tid & 31;
+    const int tid = threadIdx.x;
     const uint32_t C = fl.cluster;
     const uint32_t rank = cluster.block_rank();
     const uint32_t n_clusters = gridDim.x / C, cluster_id = blockIdx.x / C;
@@ -106,6 +177,7 @@ __global__ void __launch_bounds__(NT, 1) fused_row_kernel(const RowArgs a, const
     __syncthreads();
     const unsigned long long* tab = sm.exp_tab;
     uint32_t parity = 0;
+    long long tick_ = clock64();
 
     for (uint32_t row = cluster_id; row < a.rows; row += n_clusters) {
         FusedXchg& xc = sm.xchg[parity];
@@ -139,11 +211,9 @@ __global__ void __launch_bounds__(NT, 1) fused_row_kernel(const RowArgs a, const
             const uint32_t h1 = a.hist_offsets[row + 1];
             if (h1 < h0 || h1 - h0 > a.max_history) bad = true; else nh = h1 - h0;
         }
+        const bool writer = rank == 0 && tid == 0;
         if (bad) {
-            if (rank == 0 && tid == 0) {
-                a.token[row] = 0; a.status[row] = ROW_BAD_PARAM;
-                if (a.drew) a.drew[row] = 0;
-            }
+            if (writer) { a.token[row] = 0; a.status[row] = ROW_BAD_PARAM; if (a.drew) a.drew[row] = 0; }
             continue;
         }
         const bool greedy = temp < 1e-5f;
@@ -154,7 +224,7 @@ __global__ void __launch_bounds__(NT, 1) fused_row_kernel(const RowArgs a, const
         const bool aligned = (((uintptr_t)rowp & 15) == 0);
         const bool defer = !aligned || (!greedy && (!use_k || top_k > (uint32_t)F_KMAX));
         if (defer) {
-            if (rank == 0 && tid == 0) fl.work_rows[atomicAdd(fl.work_count, 1u)] = row;
+            if (writer) fl.work_rows[atomicAdd(fl.work_count, 1u)] = row;
             continue;
         }
 
@@ -162,57 +232,59 @@ __global__ void __launch_bounds__(NT, 1) fused_row_kernel(const RowArgs a, const
         float tmax = -INFINITY;
         int nonfinite = 0;
         sm.redo_max[tid] = 0;
+        const uint32_t nq = len / 4;   // 128-bit groups; a ragged tail exists only in the last slice
+        auto take4 = [&](uint32_t q, float4 v) {
+            nonfinite |= !finite_f(v.x) | !finite_f(v.y) | !finite_f(v.z) | !finite_f(v.w);
+            if (mw) {
+                const uint32_t bits = __ldg(mw + ((lo >> 5) + (q >> 3))) >> ((q & 7) * 4);
+                if (!(bits & 1u)) v.x = -INFINITY;
+                if (!(bits & 2u)) v.y = -INFINITY;
+                if (!(bits & 4u)) v.z = -INFINITY;
+                if (!(bits & 8u)) v.w = -INFINITY;
+            }
+            tmax = fmaxf(tmax, fmaxf(fmaxf(v.x, v.y), fmaxf(v.z, v.w)));
+            ((float4*)X)[q] = v;
+        };
+        auto take1 = [&](uint32_t i, float x) {
+            nonfinite |= !finite_f(x);
+            if (mw && !((__ldg(mw + ((lo + i) >> 5)) >> ((lo + i) & 31)) & 1u)) x = -INFINITY;
+            tmax = fmaxf(tmax, x);
+            X[i] = x;
+        };
         if (a.dtype == 0) {
             const float4* src = (const float4*)(rowp) + lo / 4;
-            const uint32_t nq = len / 4;   // len is a multiple of 4 except possibly in the last slice
-            for (uint32_t q = tid; q < nq; q += NT) {
-                float4 v = __ldcs(src + q);
-                nonfinite |= !finite_f(v.x) | !finite_f(v.y) | !finite_f(v.z) | !finite_f(v.w);
-                if (mw) {
-                    const uint32_t bits = __ldg(mw + ((lo >> 5) + (q >> 3))) >> ((q & 7) * 4);
-                    if (!(bits & 1u)) v.x = -INFINITY;
-                    if (!(bits & 2u)) v.y = -INFINITY;
-                    if (!(bits & 4u)) v.z = -INFINITY;
-                    if (!(bits & 8u)) v.w = -INFINITY;
-                }
-                tmax = fmaxf(tmax, fmaxf(fmaxf(v.x, v.y), fmaxf(v.z, v.w)));
-                ((float4*)X)[q] = v;
+            // four independent 128-bit loads in flight per thread before any of them is consumed
+            for (uint32_t q0 = tid; q0 < nq; q0 += 4 * NT) {
+                float4 v[4];
+#pragma unroll
+                for (int u = 0; u < 4; u++)
+                    if (q0 + u * NT < nq) v[u] = __ldcs(src + q0 + u * NT);
+#pragma unroll
+                for (int u = 0; u < 4; u++)
+                    if (q0 + u * NT < nq) take4(q0 + u * NT, v[u]);
             }
-            for (uint32_t i = nq * 4 + tid; i < len; i += NT) {   // ragged tail of the last slice
-                float x = __ldcs((const float*)rowp + lo + i);
-                nonfinite |= !finite_f(x);
-                if (mw && !((__ldg(mw + ((lo + i) >> 5)) >> ((lo + i) & 31)) & 1u)) x = -INFINITY;
-                tmax = fmaxf(tmax, x);
-                X[i] = x;
-            }
+            for (uint32_t i = nq * 4 + tid; i < len; i += NT) take1(i, __ldcs((const float*)rowp + lo + i));
         } else {
             const uint2* src = (const uint2*)(rowp) + lo / 4;    // 4 bf16 per 8-byte load
-            const uint32_t nq = len / 4;
-            for (uint32_t q = tid; q < nq; q += NT) {
-                const uint2 r = __ldcs(src + q);
-                float4 v;
-                v.x = __uint_as_float(r.x << 16); v.y = __uint_as_float(r.x & 0xffff0000u);
-                v.z = __uint_as_float(r.y << 16); v.w = __uint_as_float(r.y & 0xffff0000u);
-                nonfinite |= !finite_f(v.x) | !finite_f(v.y) | !finite_f(v.z) | !finite_f(v.w);
-                if (mw) {
-                    const uint32_t bits = __ldg(mw + ((lo >> 5) + (q >> 3))) >> ((q & 7) * 4);
-                    if (!(bits & 1u)) v.x = -INFINITY;
-                    if (!(bits & 2u)) v.y = -INFINITY;
-                    if (!(bits & 4u)) v.z = -INFINITY;
-                    if (!(bits & 8u)) v.w = -INFINITY;
-                }
-                tmax = fmaxf(tmax, fmaxf(fmaxf(v.x, v.y), fmaxf(v.z, v.w)));
-                ((float4*)X)[q] = v;
+            for (uint32_t q0 = tid; q0 < nq; q0 += 4 * NT) {
+                uint2 r[4];
+#pragma unroll
+                for (int u = 0; u < 4; u++)
+                    if (q0 + u * NT < nq) r[u] = __ldcs(src + q0 + u * NT);
+#pragma unroll
+                for (int u = 0; u < 4; u++)
+                    if (q0 + u * NT < nq) {
+                        float4 v;   // bf16 -> f32 is a 16-bit shift: exact
+                        v.x = __uint_as_float(r[u].x << 16); v.y = __uint_as_float(r[u].x & 0xffff0000u);
+                        v.z = __uint_as_float(r[u].y << 16); v.w = __uint_as_float(r[u].y & 0xffff0000u);
+                        take4(q0 + u * NT, v);
+                    }
             }
-            for (uint32_t i = nq * 4 + tid; i < len; i += NT) {
-                float x = __uint_as_float((uint32_t)((const unsigned short*)rowp)[lo + i] << 16);
-                nonfinite |= !finite_f(x);
-                if (mw && !((__ldg(mw + ((lo + i) >> 5)) >> ((lo + i) & 31)) & 1u)) x = -INFINITY;
-                tmax = fmaxf(tmax, x);
-                X[i] = x;
-            }
+            for (uint32_t i = nq * 4 + tid; i < len; i += NT)
+                take1(i, __uint_as_float((uint32_t)__ldcs((const unsigned short*)rowp + lo + i) << 16));
         }
         nonfinite = __syncthreads_or(nonfinite);
+        PGS_TICK(0);   // load
 
         // --------------------------------------------------------------- penalties
         const bool do_fp = !(fabsf(freq) < 1e-6f && fabsf(pres) < 1e-6f);
@@ -248,9 +320,7 @@ __global__ void __launch_bounds__(NT, 1) fused_row_kernel(const RowArgs a, const
                     }
                     // an overflowed penalty is non-finite; the chain treats that like a masked entry
                     X[i] = finite_f(x) ? x : -INFINITY;
-                    // the thread that loaded element i must refresh its maximum
-                    const uint32_t owner = (i < (len / 4) * 4) ? ((i >> 2) & (NT - 1)) : ((i - (len / 4) * 4) & (NT - 1));
-                    sm.redo_max[owner] = 1;
+                    sm.redo_max[load_owner(i, len)] = 1;   // that thread's maximum is stale now
                 }
             }
             __syncthreads();
@@ -259,29 +329,27 @@ __global__ void __launch_bounds__(NT, 1) fused_row_kernel(const RowArgs a, const
         if (mw && (gflags & 1u) && a.eos >= 0 && (uint32_t)a.eos >= lo && (uint32_t)a.eos < hi && tid == 0 &&
             !finite_f(X[a.eos - lo])) {
             X[a.eos - lo] = 0.0f;
-            const uint32_t i = a.eos - lo;
-            sm.redo_max[(i < (len / 4) * 4) ? ((i >> 2) & (NT - 1)) : ((i - (len / 4) * 4) & (NT - 1))] = 1;
+            sm.redo_max[load_owner(a.eos - lo, len)] = 1;
         }
         __syncthreads();
         if (sm.redo_max[tid]) {
             tmax = -INFINITY;
-            const uint32_t nq = len / 4;
             for (uint32_t q = tid; q < nq; q += NT) {
                 const float4 v = ((const float4*)X)[q];
                 tmax = fmaxf(tmax, fmaxf(fmaxf(v.x, v.y), fmaxf(v.z, v.w)));
             }
             for (uint32_t i = nq * 4 + tid; i < len; i += NT) tmax = fmaxf(tmax, X[i]);
         }
+        PGS_TICK(1);   // penalties
 
         // ------------------------------------------------- slice max / argmax, lowest id
-        // block max of the keys, then the lowest index holding it
-        unsigned long long best = (unsigned long long)order_key(tmax) << 32;
-        best = block_max_u64(best, sm.rs);
+        // the winning thread(s) look up the lowest index holding the block maximum
+        unsigned long long best = block_max_u64((unsigned long long)order_key(tmax) << 32, sm.rs);
         const uint32_t bkey = (uint32_t)(best >> 32);
-        if (bkey) {
+        best = 0ull;
+        if (bkey && order_key(tmax) == bkey) {
             const float bval = key_to_float(bkey);
             uint32_t first = 0xffffffffu;
-            const uint32_t nq = len / 4;
             for (uint32_t q = tid; q < nq && first == 0xffffffffu; q += NT) {
                 const float4 v = ((const float4*)X)[q];
                 if (v.x == bval) first = q * 4;
@@ -291,13 +359,11 @@ __global__ void __launch_bounds__(NT, 1) fused_row_kernel(const RowArgs a, const
             }
             for (uint32_t i = nq * 4 + tid; i < len && first == 0xffffffffu; i += NT)
                 if (X[i] == bval) first = i;
-            unsigned long long cand = first == 0xffffffffu ? 0ull
-                                                           : ((unsigned long long)bkey << 32) |
-                                                                 (unsigned long long)(0xffffffffu - (lo + first));
-            best = block_max_u64(cand, sm.rs);
-        } else {
-            best = 0ull;
+            if (first != 0xffffffffu)
+                best = ((unsigned long long)bkey << 32) | (unsigned long long)(0xffffffffu - (lo + first));
         }
+        if (bkey) best = block_max_u64(best, sm.rs);
+        PGS_TICK(2);   // argmax
         // ------------------------------------------------ cluster exchange #1
         for (uint32_t r = tid; r < C; r += NT) {
             FusedSmem* peer = cluster.map_shared_rank(&sm, r);
@@ -306,14 +372,11 @@ __global__ void __launch_bounds__(NT, 1) fused_row_kernel(const RowArgs a, const
             peer->xchg[pbuf].spill[rank] = spill;
         }
         if (!greedy) {
-            const float tm = tmax;
-            for (uint32_t r = 0; r < C; r++) {
-                FusedSmem* peer = cluster.map_shared_rank(&sm, r);
-                peer->r_b.tmax_all[rank * NT + tid] = tm;
-            }
+            for (uint32_t r = 0; r < C; r++) cluster.map_shared_rank(&sm, r)->tmax_all[rank * NT + tid] = tmax;
         }
         cluster.sync();
         parity ^= 1u;
+        PGS_TICK(3);   // sync 1
         unsigned long long gbest = 0ull;
         int any_nonfinite = 0, any_spill = 0;
         for (uint32_t r = 0; r < C; r++) {
@@ -325,7 +388,6 @@ __global__ void __launch_bounds__(NT, 1) fused_row_kernel(const RowArgs a, const
         const float m = any ? key_to_float((uint32_t)(gbest >> 32)) : -INFINITY;
         const uint32_t amax = any ? 0xffffffffu - (uint32_t)gbest : 0u;
         const int status = any ? ROW_OK : ROW_EMPTY;
-        const bool writer = rank == 0 && tid == 0;
         if (any_nonfinite) {
             if (writer) { a.token[row] = 0; a.status[row] = ROW_NONFINITE; if (a.drew) a.drew[row] = 0; }
             continue;
@@ -353,7 +415,7 @@ __global__ void __launch_bounds__(NT, 1) fused_row_kernel(const RowArgs a, const
 
         // -------------------------------- top-k bound: k-th largest per-thread maximum
         const float t = fmaxf(temp, 1e-9f);
-        const uint32_t kk = radix_select_kth([&](int i) { return order_key(sm.r_b.tmax_all[i]); }, (int)(C * NT),
+        const uint32_t kk = radix_select_kth([&](int i) { return order_key(sm.tmax_all[i]); }, (int)(C * NT),
                                              top_k, sm.sel, sm.rs);
         float cut = -INFINITY;
         if (kk) {
@@ -362,10 +424,10 @@ __global__ void __launch_bounds__(NT, 1) fused_row_kernel(const RowArgs a, const
             const float delta = 4.8e-7f * (fabsf(m - bound) + 4.0f * t) + 4.8e-7f * (fabsf(bound) + fabsf(m));
             cut = bound - delta;
         }
+        PGS_TICK(4);   // select
         if (tid == 0) sm.cand_n = 0;
         __syncthreads();
         {
-            const uint32_t nq = len / 4;
             for (uint32_t q = tid; q < nq; q += NT) {
                 const float4 v = ((const float4*)X)[q];
                 const float vv[4] = {v.x, v.y, v.z, v.w};
@@ -387,36 +449,34 @@ __global__ void __launch_bounds__(NT, 1) fused_row_kernel(const RowArgs a, const
         }
         __syncthreads();
         const uint32_t my_n = sm.cand_n;
+        PGS_TICK(5);   // gather
 
         // --------------- softmax numerators in place (hardware exp2) + per-thread chunk sums
         const float scale = 1.4426950408889634f / t;
         const uint32_t L = fl.chunk;
-        const uint32_t c0 = tid * L, c1 = min(len, c0 + L);
+        const uint32_t c0 = min(len, tid * L), c1 = min(len, c0 + L);
         float csum = 0.0f;
         for (uint32_t i = c0; i < c1; i++) {
-            const float x = X[i];
-            // masked entries are -inf: exp2(-inf) = +0
-            const float e = ex2_approx((x - m) * scale);
+            const float e = ex2_approx((X[i] - m) * scale);   // masked entries are -inf: 2^-inf = +0
             X[i] = e;
             csum += e;
         }
-        const float pre = block_excl_scan_f32(csum, sm.rs);
-        __syncthreads();
-        if (tid == NT - 1) sm.acc = pre + csum;    // CTA total (estimate)
-        __syncthreads();
-        const float cta_total = sm.acc;
+        double dtot;
+        const double pre0 = block_excl_scan_f64((double)csum, &dtot, sm.dscan);
+        PGS_TICK(6);   // exp pass
         // ------------------------------------------------ cluster exchange #2
         for (uint32_t r = tid; r < C; r += NT) {
             FusedSmem* peer = cluster.map_shared_rank(&sm, r);
             peer->xchg[pbuf].ncand[rank] = my_n;
-            peer->xchg[pbuf].approx_total[rank] = cta_total;
+            peer->xchg[pbuf].true_total[rank] = (float)dtot;
         }
         cluster.sync();
+        PGS_TICK(7);   // sync 2
         uint32_t cand_off = 0, cand_total = 0;
-        float before = 0.0f;
+        double before0 = 0.0;
         bool overflow = false;
         for (uint32_t r = 0; r < C; r++) {
-            if (r < rank) { cand_off += xc.ncand[r]; before += xc.approx_total[r]; }
+            if (r < rank) { cand_off += xc.ncand[r]; before0 += (double)xc.true_total[r]; }
             cand_total += xc.ncand[r];
             overflow |= xc.ncand[r] > (uint32_t)F_LCAP;
         }
@@ -425,150 +485,122 @@ __global__ void __launch_bounds__(NT, 1) fused_row_kernel(const RowArgs a, const
             if (writer) fl.work_rows[atomicAdd(fl.work_count, 1u)] = row;
             continue;
         }
-        // candidates -> CTA 0
+        // candidates -> CTA 0 (lands before exchange #4)
         {
             FusedSmem* root = cluster.map_shared_rank(&sm, 0);
             for (uint32_t j = tid; j < my_n; j += NT) {
                 root->r_a.mrg.m_id[cand_off + j] = sm.cand_id[j];
                 root->r_a.mrg.m_x[cand_off + j] = sm.cand_x[j];
             }
-            if (rank == 0 && tid == 0) sm.m_n = cand_total;
+            if (writer) sm.m_n = cand_total;
         }
-        // ---------------- per-thread summaries of the sequential sum (see pgs_block.cuh)
-        {
-            const float t_guess = before + pre;
-            const uint32_t e = f2u(t_guess) & 0x7f800000u;
-            int k;
-            uint32_t d = 0;
-            if (csum == 0.0f) {
-                k = SEQ_K_IDENT;
-            } else if (e == 0u || e == 0x7f800000u) {
-                k = SEQ_K_NONE;
-            } else {
-                k = (int)e;
-                float acc = u2f(e);
-                for (uint32_t i = c0; i < c1; i++) acc = fadd(acc, X[i]);
-                d = ((f2u(acc) & 0x7f800000u) == e) ? f2u(acc) - e : SEQ_SAT;
-            }
-            sm.r_b.seq.tk[tid] = k;
-            sm.r_b.seq.td[tid] = d;
-        }
-        __syncthreads();
-        // ----------- resolve, CTA after CTA: exact prefix while summaries apply, else re-add
-        for (uint32_t turn = 0; turn < C; turn++) {
-            if (turn == rank) {
-                float acc = rank == 0 ? 0.0f : xc.acc_in;
-                uint32_t start = 0;
-                // warp 0 walks the 1024 thread summaries: 32 at a time, prefix by shuffles
-                if (tid < 32) {
-                    while (start < (uint32_t)NT) {
-                        const uint32_t tt = start + lane;
-                        const int k = tt < (uint32_t)NT ? sm.r_b.seq.tk[tt] : SEQ_K_IDENT;
-                        uint32_t d = (tt < (uint32_t)NT && k >= 0) ? sm.r_b.seq.td[tt] : 0u;
-                        // inclusive prefix of d with saturation
-                        uint32_t inc = d;
-                        for (int s = 1; s < 32; s <<= 1) {
-                            uint32_t up = __shfl_up_sync(FULL, inc, s);
-                            if (lane >= s) inc = min(inc + up, SEQ_SAT);
-                        }
-                        const uint32_t ab = f2u(acc);
-                        const uint32_t mant = (ab & 0x007fffffu) | 0x00800000u;
-                        const bool ok = k == SEQ_K_IDENT ||
-                                        (k >= 0 && (uint32_t)k == (ab & 0x7f800000u) && (ab & 0x7f800000u) != 0u &&
-                                         d < SEQ_SAT && inc < SEQ_SAT && mant + inc < 0x01000000u);
-                        const unsigned okmask = __ballot_sync(FULL, ok);
-                        const int nok = okmask == FULL ? 32 : __ffs(~okmask) - 1;   // leading run of valid lanes
-                        if (nok > 0) {
-                            const uint32_t adv = __shfl_sync(FULL, inc, nok - 1);
-                            acc = u2f(ab + adv);
-                        }
-                        start += nok;
-                        if (nok < 32 && start < (uint32_t)NT) {
-                            // chunk `start` does not apply: add its terms one by one
-                            const uint32_t b0 = start * L, b1 = min(len, b0 + L);
-                            if (b1 > b0) acc = fold_serial(X + b0, (int)(b1 - b0), acc);
-                            start += 1;
-                        }
-                    }
-                    if (lane == 0) {
-                        if (rank + 1 < C) cluster.map_shared_rank(&sm, rank + 1)->xchg[pbuf].acc_in = acc;
-                        else cluster.map_shared_rank(&sm, 0)->xchg[pbuf].sum_final = acc;
-                    }
-                }
-            }
-            cluster.sync();
-        }
+        // ---------- the sequential fold, chunk by chunk: first from the plain prefix sums ...
+        const float start0 = (float)(before0 + pre0);
+        float acc = start0;
+        for (uint32_t i = c0; i < c1; i++) acc = fadd(acc, X[i]);
+        double inc1 = (double)acc - (double)start0;
+        double tot1;
+        const double pre1 = block_excl_scan_f64(inc1, &tot1, sm.dscan);
+        PGS_TICK(8);   // fold 1
+        for (uint32_t r = tid; r < C; r += NT) cluster.map_shared_rank(&sm, r)->xchg[pbuf].fold1[rank] = tot1;
+        cluster.sync();   // exchange #3
+        double before1 = 0.0;
+        for (uint32_t r = 0; r < rank; r++) before1 += xc.fold1[r];
+        // ... then once more from the running values that first pass implies
+        const float start1 = (float)(before1 + pre1);
+        acc = start1;
+        for (uint32_t i = c0; i < c1; i++) acc = fadd(acc, X[i]);
+        double inc2 = (double)acc - (double)start1;
+        double tot2;
+        block_excl_scan_f64(inc2, &tot2, sm.dscan);
+        if (tid == 0) cluster.map_shared_rank(&sm, 0)->xchg[pbuf].fold2[rank] = tot2;
+        cluster.sync();   // exchange #4
+        PGS_TICK(9);   // fold 2
         if (rank != 0) continue;
 
         // ------------------------------------------ CTA 0: the reference's rule on the candidates
-        const float S = xc.sum_final;
+        double s2 = 0.0;
+        for (uint32_t r = 0; r < C; r++) s2 += xc.fold2[r];
+        const float S = (float)s2;
         const uint32_t n = sm.m_n;
-        unsigned long long* m_key = reinterpret_cast<unsigned long long*>(X);   // [F_MCAP], slice is dead now
-        float* m_p = X + 2 * F_MCAP;                                             // [F_MCAP]
         const bool norm = S > 1e-9f;
-        // sort by id (ascending) so that the CDF walk runs in id order
-        uint32_t npad = 2;
-        while (npad < n) npad <<= 1;
-        for (uint32_t j = tid; j < npad; j += NT)
-            m_key[j] = j < n ? ((unsigned long long)sm.r_a.mrg.m_id[j] << 32) | f2u(sm.r_a.mrg.m_x[j]) : ~0ull;
-        bitonic_sort(m_key, (int)npad, m_key);
+        FusedCand& cd = *reinterpret_cast<FusedCand*>(X);
+        const uint32_t* m_id = sm.r_a.mrg.m_id;
         for (uint32_t j = tid; j < n; j += NT) {
-            const uint32_t id = (uint32_t)(m_key[j] >> 32);
-            const float x = u2f((uint32_t)m_key[j]);
-            const float e = softmax_num(x, m, t, tab);
-            sm.r_a.mrg.m_id[j] = id;
-            m_p[j] = norm ? fdiv(e, S) : e;
+            const float e = softmax_num(sm.r_a.mrg.m_x[j], m, t, tab);   // exact expf for candidates
+            cd.p[j] = norm ? fdiv(e, S) : e;
         }
         __syncthreads();
-        // rank by probability descending, id ascending (position in the id-sorted list)
-        for (uint32_t j = tid; j < npad; j += NT)
-            m_key[j] = j < n ? ((unsigned long long)(~f2u(m_p[j])) << 32) | j : ~0ull;
-        bitonic_sort(m_key, (int)npad, m_key);
-        // top-k threshold: every tie at the k-th probability survives (sampler.rs:116-128)
-        uint32_t n_live = n;
-        if (top_k <= n) {
-            const float thr = u2f(~(uint32_t)(m_key[top_k - 1] >> 32));
-            uint32_t cnt = 0;
-            for (uint32_t j = tid; j < n; j += NT) cnt += u2f(~(uint32_t)(m_key[j] >> 32)) >= thr;
-            n_live = block_sum_u32(cnt, sm.rs);   // sorted descending: the survivors are a prefix
-        }
-        // entries with zero probability never matter
-        {
-            uint32_t cnt = 0;
-            for (uint32_t j = tid; j < n_live; j += NT) cnt += u2f(~(uint32_t)(m_key[j] >> 32)) > 0.0f;
-            n_live = block_sum_u32(cnt, sm.rs);
-        }
-        // top-p walk in ranked order, then total and CDF in id order (sampler.rs:130-150, 40-55)
-        if (tid == 0) {
-            uint32_t keep = n_live;
-            if (use_p) {
-                float cum = 0.0f;
-                for (uint32_t j = 0; j < n_live; j++) {
-                    cum = fadd(cum, u2f(~(uint32_t)(m_key[j] >> 32)));
-                    if (cum >= top_p) { keep = j + 1; break; }
-                }
+        // rank every candidate by id and by (probability descending, id ascending)
+        for (uint32_t j = tid; j < n; j += NT) {
+            const uint32_t idj = m_id[j];
+            const float pj = cd.p[j];
+            uint32_t r_id = 0, r_p = 0;
+            for (uint32_t o = 0; o < n; o++) {
+                const uint32_t ido = m_id[o];
+                const float po = cd.p[o];
+                r_id += ido < idj;
+                r_p += (po > pj) || (po == pj && ido < idj);
             }
-            sm.m_n = keep;
+            cd.sid[r_id] = idj;
+            cd.sp[r_id] = pj;
+            cd.rp[r_p] = pj;
+            cd.rpos[r_p] = r_id;
+        }
+        if (tid == 0) { sm.n_live = 0; }
+        __syncthreads();
+        // top-k: every tie at the k-th probability survives (sampler.rs:116-128); zeros never matter
+        {
+            const float thr = top_k <= n ? cd.rp[top_k - 1] : 0.0f;
+            for (uint32_t j = tid; j < n; j += NT) {
+                const bool live = cd.rp[j] >= thr && cd.rp[j] > 0.0f;
+                const bool next_live = j + 1 < n && cd.rp[j + 1] >= thr && cd.rp[j + 1] > 0.0f;
+                if (live && !next_live) sm.n_live = j + 1;
+            }
         }
         __syncthreads();
-        const uint32_t keep = sm.m_n;
-        for (uint32_t j = keep + tid; j < n; j += NT) m_p[(uint32_t)m_key[j]] = 0.0f;
+        const uint32_t n_live = sm.n_live;
+        // top-p walk in ranked order (sampler.rs:130-150)
+        uint32_t keep = n_live;
+        if (use_p && n_live > 0) {
+            int found = -1;
+            if (n_live <= 128) {
+                if (tid < 32) {
+                    warp_fold(cd.rp, (int)n_live, SEQ_FIND_GE, top_p, &found);
+                    if (tid == 0) sm.bcast_i = found;
+                }
+                __syncthreads();
+                found = sm.bcast_i;
+            } else {
+                seq_scan([&](int j) { return cd.rp[j]; }, (int)n_live, 0.0f, SEQ_FIND_GE, top_p, &found, cd.seq, sm.rs);
+            }
+            if (found >= 0) keep = (uint32_t)found + 1;
+        }
+        for (uint32_t j = keep + tid; j < n; j += NT) cd.sp[cd.rpos[j]] = 0.0f;
         __syncthreads();
+        // total and inverse-CDF pick in id order (sampler.rs:40-55)
+        float total;
+        int pick = -1;
+        if (n <= 128) {
+            if (tid < 32) {
+                const float tt = warp_fold(cd.sp, (int)n, SEQ_SUM, 0.0f, nullptr);
+                int f = -1;
+                if (tt > 1e-9f) warp_fold(cd.sp, (int)n, SEQ_FIND_GT, fmul(u01, tt), &f);
+                if (tid == 0) { sm.bcast_f = tt; sm.bcast_i = f; }
+            }
+            __syncthreads();
+            total = sm.bcast_f;
+            pick = sm.bcast_i;
+        } else {
+            total = seq_scan([&](int j) { return cd.sp[j]; }, (int)n, 0.0f, SEQ_SUM, 0.0f, nullptr, cd.seq, sm.rs);
+            if (total > 1e-9f)
+                seq_scan([&](int j) { return cd.sp[j]; }, (int)n, 0.0f, SEQ_FIND_GT, fmul(u01, total), &pick, cd.seq,
+                         sm.rs);
+        }
         if (tid == 0) {
-            float total = 0.0f;
-            for (uint32_t j = 0; j < n; j++) total = fadd(total, m_p[j]);
             uint32_t token = amax;
             int drew = 0;
-            if (total > 1e-9f) {
-                const float u = fmul(u01, total);
-                float acc = 0.0f;
-                token = V - 1;
-                for (uint32_t j = 0; j < n; j++) {
-                    acc = fadd(acc, m_p[j]);
-                    if (u < acc) { token = sm.r_a.mrg.m_id[j]; break; }
-                }
-                drew = 1;
-            }
+            if (total > 1e-9f) { token = pick >= 0 ? cd.sid[pick] : V - 1; drew = 1; }
             a.token[row] = token; a.status[row] = status;
             if (a.drew) a.drew[row] = (uint8_t)drew;
             if (a.argmax) a.argmax[row] = amax;
@@ -576,16 +608,17 @@ __global__ void __launch_bounds__(NT, 1) fused_row_kernel(const RowArgs a, const
             if (a.sumexp) a.sumexp[row] = S;
             if (a.total) a.total[row] = total;
         }
+        PGS_TICK(10);  // candidates
         if (a.n_kept || a.dump_ids || a.dump_probs) {   // diagnostics: the kept set in id order
             uint32_t done = 0;
             for (uint32_t base = 0; base < n; base += NT) {
                 const uint32_t j = base + tid;
-                const uint32_t kept = (j < n && m_p[j] > 0.0f) ? 1u : 0u;
+                const uint32_t kept = (j < n && cd.sp[j] > 0.0f) ? 1u : 0u;
                 uint32_t tot;
                 const uint32_t at = done + block_excl_scan_u32(kept, &tot, sm.rs);
                 if (kept && at < a.dump_cap) {
-                    if (a.dump_ids) a.dump_ids[(size_t)row * a.dump_cap + at] = sm.r_a.mrg.m_id[j];
-                    if (a.dump_probs) a.dump_probs[(size_t)row * a.dump_cap + at] = m_p[j];
+                    if (a.dump_ids) a.dump_ids[(size_t)row * a.dump_cap + at] = cd.sid[j];
+                    if (a.dump_probs) a.dump_probs[(size_t)row * a.dump_cap + at] = cd.sp[j];
                 }
                 done += tot;
             }
@@ -597,9 +630,10 @@ __global__ void __launch_bounds__(NT, 1) fused_row_kernel(const RowArgs a, const
     cluster.sync();
 }
 
-// the slice buffer doubles as CTA 0's candidate workspace (sort keys + probabilities)
+// the slice buffer doubles as CTA 0's candidate workspace
 size_t fused_smem_bytes(uint32_t slice_len) {
-    const size_t floats = slice_len > 3u * F_MCAP ? slice_len : 3u * F_MCAP;
+    const size_t need = (sizeof(FusedCand) + 3) / 4;
+    const size_t floats = slice_len > need ? slice_len : need;
     return ((sizeof(FusedSmem) + 15) & ~size_t(15)) + floats * sizeof(float);
 }
 
