@@ -51,7 +51,8 @@ enum pgs_row_status {
     PGS_ROW_NONFINITE = 1, /* logits_sane failed (engine.rs:1278-1295) -> FinishReason::Fault */
     PGS_ROW_DEAD = 2,      /* grammar state is a dead end (engine.rs:1299-1303) -> Stop, no token */
     PGS_ROW_EMPTY = 3,     /* nothing finite left after masking; token 0, as sampler.rs:59-70 returns */
-    PGS_ROW_BAD_PARAM = 4  /* non-finite parameter, bad mask table/state, history too long */
+    PGS_ROW_BAD_PARAM = 4, /* non-finite parameter, bad mask table/state, history too long */
+    PGS_ROW_LOAD_TIMEOUT = 5 /* a bounded wait for an asynchronous copy ran out; nothing sampled */
 };
 
 enum pgs_mem { PGS_MEM_DEVICE = 0, PGS_MEM_HOST = 1 };

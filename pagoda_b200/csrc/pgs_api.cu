@@ -13,23 +13,20 @@
 #include <vector>
 
 #include "pgs_args.cuh"
+#include "pgs_fused.cuh"
 
 namespace pgs {
 cudaError_t configure_general();
 cudaError_t launch_general(const RowArgs& a, uint32_t grid, cudaStream_t stream);
 size_t general_smem_bytes();
 
-struct FusedLaunch {
-    uint32_t cluster, slice_len, chunk;
-    uint32_t* work_rows;
-    uint32_t* work_count;
-    long long* prof;
-};
 size_t fused_smem_bytes(uint32_t slice_len);
 cudaError_t configure_fused(size_t max_smem);
 cudaError_t fused_max_clusters(uint32_t cluster, size_t smem, int* out);
 cudaError_t launch_fused(const RowArgs& a, const FusedLaunch& fl, uint32_t n_clusters, size_t smem,
                          cudaStream_t stream);
+cudaError_t configure_finish();
+cudaError_t launch_finish(const RowArgs& a, const FusedLaunch& fl, cudaStream_t stream);
 }  // namespace pgs
 
 static thread_local char g_create_error[256] = "";
@@ -62,6 +59,9 @@ struct pgs_handle {
     size_t fused_smem = 0;
     uint32_t* work_rows = nullptr;
     uint32_t* work_count = nullptr;   // [2]
+    pgs::RowRec* recs = nullptr;      // [max_rows]
+    uint32_t* cand_id = nullptr;      // [max_rows x F_MCAP]
+    float* cand_x = nullptr;
     int exact = 0;
     long long* prof = nullptr;        // phase timers of the fused kernel (PGS_PROFILE=1)
     pgs_counters counters = {};
@@ -120,6 +120,7 @@ static int destroy_impl(pgs_handle* h) {
     cudaFree(h->sx); cudaFree(h->sl_id); cudaFree(h->sl_p); cudaFree(h->sl_key);
     cudaFree(h->sh_key); cudaFree(h->sh_cnt); cudaFree(h->tables_dev);
     cudaFree(h->logits_stage); cudaFree(h->aux_dev); cudaFree(h->work_rows); cudaFree(h->work_count); cudaFree(h->prof);
+    cudaFree(h->recs); cudaFree(h->cand_id); cudaFree(h->cand_x);
     if (h->aux_host) cudaFreeHost(h->aux_host);
     if (h->stream) cudaStreamDestroy(h->stream);
     delete h;
@@ -156,6 +157,11 @@ extern "C" int pgs_create(int device, uint32_t max_rows, uint32_t max_vocab, uin
         PGS_CUDA(nullptr, pgs::configure_general());
         h->smem_optin = prop.sharedMemPerBlockOptin;
         PGS_CUDA(nullptr, pgs::configure_fused(h->smem_optin));
+        PGS_CUDA(nullptr, pgs::configure_finish());
+        PGS_CUDA(nullptr, cudaMalloc(&h->recs, (size_t)max_rows * sizeof(pgs::RowRec)));
+        PGS_CUDA(nullptr, cudaMemsetAsync(h->recs, 0, (size_t)max_rows * sizeof(pgs::RowRec), h->stream));
+        PGS_CUDA(nullptr, cudaMalloc(&h->cand_id, (size_t)max_rows * pgs::F_MCAP * sizeof(uint32_t)));
+        PGS_CUDA(nullptr, cudaMalloc(&h->cand_x, (size_t)max_rows * pgs::F_MCAP * sizeof(float)));
         PGS_CUDA(nullptr, cudaMalloc(&h->work_rows, (size_t)max_rows * sizeof(uint32_t)));
         PGS_CUDA(nullptr, cudaMalloc(&h->work_count, 2 * sizeof(uint32_t)));
         PGS_CUDA(nullptr, cudaMemsetAsync(h->work_count, 0, 2 * sizeof(uint32_t), h->stream));
@@ -298,12 +304,15 @@ int launch_step(pgs_handle* h, pgs::RowArgs& a, cudaStream_t stream) {
     fl.cluster = h->fused_cluster; fl.slice_len = h->fused_slice; fl.chunk = h->fused_chunk;
     fl.work_rows = h->work_rows; fl.work_count = h->work_count;
     fl.prof = h->prof;
+    fl.recs = h->recs; fl.cand_id = h->cand_id; fl.cand_x = h->cand_x;
     const uint32_t nc = rows < h->fused_clusters ? rows : h->fused_clusters;
     PGS_CUDA(h, pgs::launch_fused(a, fl, nc, h->fused_smem, stream));
+    PGS_CUDA(h, pgs::launch_finish(a, fl, stream));
     a.work_rows = h->work_rows;
     a.work_count = h->work_count;
-    PGS_CUDA(h, pgs::launch_general(a, grid, stream));
-    h->counters.kernel_launches += 2;
+    // the listed rows are few or none: a small grid keeps the empty pass short
+    PGS_CUDA(h, pgs::launch_general(a, grid < 32u ? grid : 32u, stream));
+    h->counters.kernel_launches += 3;
     return PGS_OK;
 }
 

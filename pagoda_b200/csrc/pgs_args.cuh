@@ -18,7 +18,7 @@ struct TableDir {
 constexpr int MAX_TABLES = 256;
 
 // Row status values mirror pgs_row_status of the C ABI.
-enum { ROW_OK = 0, ROW_NONFINITE = 1, ROW_DEAD = 2, ROW_EMPTY = 3, ROW_BAD_PARAM = 4 };
+enum { ROW_OK = 0, ROW_NONFINITE = 1, ROW_DEAD = 2, ROW_EMPTY = 3, ROW_BAD_PARAM = 4, ROW_LOAD_TIMEOUT = 5 };
 
 struct RowArgs {
     // inputs (device pointers)

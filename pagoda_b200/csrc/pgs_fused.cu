@@ -21,6 +21,8 @@
 // for bit; candidate numerators use the exact expf; the bulk numerators that only enter the
 // running sum use the hardware exp2 (a few ulp), so the sum agrees with the reference's to
 // about 1e-6 relative and a decision can differ only when it sits that close to its boundary.
+// A stochastic row leaves this kernel as a record (max, partial folds, candidate list); the
+// finish kernel (pgs_finish.cu) applies the reference's top-k / top-p / CDF rule to it.
 // Rows this kernel cannot hold (top-k off or > 1024, more candidates than its buffers, too many
 // distinct history ids in one slice, unaligned rows) are appended to a work list that the
 // general row kernel processes afterwards.
@@ -29,16 +31,11 @@
 
 #include "pgs_args.cuh"
 #include "pgs_block.cuh"
+#include "pgs_fused.cuh"
 
 namespace cg = cooperative_groups;
 
 namespace pgs {
-
-constexpr int F_MAXC = 8;          // largest cluster
-constexpr int F_LCAP = 1024;       // candidates per CTA
-constexpr int F_MCAP = 2048;       // candidates per row (merged in CTA 0)
-constexpr int F_HASH = 2048;       // id->count slots per CTA
-constexpr int F_KMAX = 1024;       // largest top-k served here
 
 struct FusedXchg {                  // peers write their slot through DSMEM
     unsigned long long best[F_MAXC];
@@ -47,43 +44,21 @@ struct FusedXchg {                  // peers write their slot through DSMEM
     uint32_t ncand[F_MAXC];
     float true_total[F_MAXC];       // plain sum of the slice's numerators
     double fold1[F_MAXC];           // slice increment of the fold, first estimate
-    double fold2[F_MAXC];           // refined
 };
 
-// Candidate workspace of CTA 0.  It lives in the slice buffer, which is dead once the sum is known.
-struct FusedCand {
-    float p[F_MCAP];                // probabilities, arrival order
-    uint32_t sid[F_MCAP];           // ids ascending
-    float sp[F_MCAP];               // probabilities in id order (zeroed when dropped)
-    float rp[F_MCAP];               // probabilities descending (ties: id ascending)
-    uint32_t rpos[F_MCAP];          // position in the id-ordered list of the entry at each rank
-    SeqSmem seq;
-};
-
-// Shared-memory workspace of one CTA (the vocabulary slice follows it).  Regions are reused as
-// the row moves through its phases:
-//   r_a : id->count table (penalties)             -> merged candidate ids / logits (CTA 0)
-//   the slice itself (logits, then numerators)     -> FusedCand (CTA 0)
+// Shared-memory workspace of one CTA (the vocabulary slice follows it).
 struct FusedSmem {
     ReduceSmem rs;
     double dscan[NW + 1];
     FusedXchg xchg[2];              // alternates between consecutive rows
-    unsigned long long exp_tab[32];
-    union {
-        struct { uint32_t hkey[F_HASH]; uint32_t hcnt[F_HASH]; } pen;
-        struct { uint32_t m_id[F_MCAP]; float m_x[F_MCAP]; } mrg;
-    } r_a;
+    struct { uint32_t hkey[F_HASH]; uint32_t hcnt[F_HASH]; } pen;
     float tmax_all[F_MAXC * NT];    // every CTA's per-thread maxima
     uint8_t redo_max[NT];
     SelectSmem sel;
     uint32_t cand_id[F_LCAP];
     float cand_x[F_LCAP];
     uint32_t cand_n;
-    uint32_t m_n;
-    uint32_t n_live, n_keep;
-    float bcast_f;
-    uint32_t bcast_u;
-    int bcast_i;
+    unsigned long long load_bar;    // mbarrier of the bulk copy that fills the slice
 };
 
 // Optional phase timers (clock64 deltas of thread 0, summed over the rows of each CTA), enabled
@@ -96,15 +71,6 @@ struct FusedSmem {
             tick_ = now_;                                           \
         }                                                           \
     } while (0)
-
-struct FusedLaunch {
-    uint32_t cluster;       // CTAs per row
-    uint32_t slice_len;     // floats per CTA (multiple of 32)
-    uint32_t chunk;         // consecutive floats per thread in the sum pass (odd)
-    uint32_t* work_rows;    // rows handed to the general kernel
-    uint32_t* work_count;
-    long long* prof;
-};
 
 // exclusive scan of one double per thread; *total = block sum
 __device__ __forceinline__ double block_excl_scan_f64(double v, double* total, double* ws /*NW+1*/) {
@@ -131,28 +97,39 @@ __device__ __forceinline__ double block_excl_scan_f64(double v, double* total, d
     return ws[w] + (inc - v);
 }
 
-// Exact left fold of n <= 128 shared-memory floats by one warp (values travel by shuffle, so the
-// dependent chain is add + shuffle instead of add + shared-memory load).  mode/target as in
-// seq_scan; returns the running value, *found = first index where the predicate holds or -1.
-__device__ __forceinline__ float warp_fold(const float* v, int n, int mode, float target, int* found) {
-    const int lane = threadIdx.x & 31;
-    float reg[4];
-#pragma unroll
-    for (int u = 0; u < 4; u++) reg[u] = (lane + 32 * u < n) ? v[lane + 32 * u] : 0.0f;
-    float acc = 0.0f;
-    int f = -1;
-#pragma unroll
-    for (int u = 0; u < 4; u++) {
-        for (int l = 0; l < 32; l++) {
-            const int j = u * 32 + l;
-            if (j >= n || f >= 0) break;
-            acc = fadd(acc, __shfl_sync(FULL, reg[u], l));
-            if (mode != SEQ_SUM && seq_pred(mode, acc, target)) f = j;
-        }
-    }
-    if (found) *found = f;
-    return acc;
+// ---- bulk asynchronous copy (TMA, no tensor map, no multicast) global -> this CTA's shared memory
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(unsigned long long* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
 }
+__device__ __forceinline__ void mbar_expect_tx(unsigned long long* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t bytes, unsigned long long* bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                     smem_u32(dst)),
+                 "l"(src), "r"(bytes), "r"(smem_u32(bar))
+                 : "memory");
+}
+__device__ __forceinline__ void bulk_prefetch_l2(const void* src, uint32_t bytes) {
+    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src), "r"(bytes) : "memory");
+}
+// Bounded wait for phase `parity` of the barrier: false when the copy has not landed after ~2^22 polls.
+__device__ __forceinline__ bool mbar_wait(unsigned long long* bar, uint32_t parity) {
+    for (uint32_t spin = 0; spin < (1u << 22); spin++) {
+        uint32_t ok;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(ok)
+            : "r"(smem_u32(bar)), "r"(parity)
+            : "memory");
+        if (ok) return true;
+    }
+    return false;
+}
+constexpr uint32_t TMA_PIECE = 32768;   // bytes per bulk copy
 
 __device__ __forceinline__ uint32_t load_owner(uint32_t i, uint32_t len) {
     // thread that loaded slice element i: 128-bit groups are dealt round-robin, then the ragged tail
@@ -173,10 +150,14 @@ __global__ void __launch_bounds__(NT, 1) fused_row_kernel(const RowArgs a, const
     const uint32_t lo = rank * fl.slice_len;
     const uint32_t hi = min(V, lo + fl.slice_len);
     const uint32_t len = hi > lo ? hi - lo : 0u;
-    if (tid < 32) sm.exp_tab[tid] = kExp2TableDev[tid];
-    __syncthreads();
-    const unsigned long long* tab = sm.exp_tab;
     uint32_t parity = 0;
+    uint32_t load_phase = 0;        // parity of the next completion of load_bar
+    bool poisoned = false;          // a bulk copy never landed: later rows of this CTA report that too
+    if (tid == 0) {
+        mbar_init(&sm.load_bar, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
     long long tick_ = clock64();
 
     for (uint32_t row = cluster_id; row < a.rows; row += n_clusters) {
@@ -213,18 +194,17 @@ __global__ void __launch_bounds__(NT, 1) fused_row_kernel(const RowArgs a, const
         }
         const bool writer = rank == 0 && tid == 0;
         if (bad) {
-            if (writer) { a.token[row] = 0; a.status[row] = ROW_BAD_PARAM; if (a.drew) a.drew[row] = 0; }
+            if (writer) { a.token[row] = 0; a.status[row] = ROW_BAD_PARAM; if (a.drew) a.drew[row] = 0; fl.recs[row].kind = 0; }
             continue;
         }
         const bool greedy = temp < 1e-5f;
         const bool use_k = top_k != 0u && top_k < V;
-        const bool use_p = !(top_p >= 1.0f);
         // rows this kernel does not serve go to the general kernel (decided identically by every CTA)
         const char* rowp = (const char*)a.logits + (size_t)row * a.row_stride * (a.dtype == 0 ? 4 : 2);
         const bool aligned = (((uintptr_t)rowp & 15) == 0);
         const bool defer = !aligned || (!greedy && (!use_k || top_k > (uint32_t)F_KMAX));
         if (defer) {
-            if (writer) fl.work_rows[atomicAdd(fl.work_count, 1u)] = row;
+            if (writer) { fl.work_rows[atomicAdd(fl.work_count, 1u)] = row; fl.recs[row].kind = 0; }
             continue;
         }
 
@@ -252,18 +232,49 @@ __global__ void __launch_bounds__(NT, 1) fused_row_kernel(const RowArgs a, const
             X[i] = x;
         };
         if (a.dtype == 0) {
-            const float4* src = (const float4*)(rowp) + lo / 4;
-            // four independent 128-bit loads in flight per thread before any of them is consumed
-            for (uint32_t q0 = tid; q0 < nq; q0 += 4 * NT) {
-                float4 v[4];
-#pragma unroll
-                for (int u = 0; u < 4; u++)
-                    if (q0 + u * NT < nq) v[u] = __ldcs(src + q0 + u * NT);
-#pragma unroll
-                for (int u = 0; u < 4; u++)
-                    if (q0 + u * NT < nq) take4(q0 + u * NT, v[u]);
+            // f32 rows: one thread streams the slice into shared memory with bulk asynchronous copies,
+            // everybody then checks / masks / maximises it from there.  The next row's slice is
+            // prefetched into L2 meanwhile, so HBM keeps streaming while this row is processed.
+            const char* gsrc = rowp + (size_t)lo * 4;
+            const uint32_t body = nq * 16;
+            if (tid == 0) {
+                if (row + n_clusters < a.rows && body) {
+                    const char* nxt = (const char*)a.logits + (size_t)(row + n_clusters) * a.row_stride * 4 + (size_t)lo * 4;
+                    if (((uintptr_t)nxt & 15) == 0)
+                        for (uint32_t off = 0; off < body; off += TMA_PIECE)
+                            bulk_prefetch_l2(nxt + off, min(TMA_PIECE, body - off));
+                }
+                if (body && !poisoned) {
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // earlier generic writes to X
+                    mbar_expect_tx(&sm.load_bar, body);
+                    for (uint32_t off = 0; off < body; off += TMA_PIECE)
+                        bulk_g2s((char*)X + off, gsrc + off, min(TMA_PIECE, body - off), &sm.load_bar);
+                }
             }
-            for (uint32_t i = nq * 4 + tid; i < len; i += NT) take1(i, __ldcs((const float*)rowp + lo + i));
+            if (body && !poisoned) {
+                if (!mbar_wait(&sm.load_bar, load_phase)) poisoned = true;
+                load_phase ^= 1u;
+            }
+            poisoned = __syncthreads_or(poisoned);
+            PGS_TICK(11);  // bulk copy landed
+            if (poisoned) {
+                nonfinite = 2;   // reported as a load timeout after the exchange
+            } else {
+                for (uint32_t q = tid; q < nq; q += NT) {
+                    float4 v = ((const float4*)X)[q];
+                    nonfinite |= !finite_f(v.x) | !finite_f(v.y) | !finite_f(v.z) | !finite_f(v.w);
+                    if (mw) {
+                        const uint32_t bits = __ldg(mw + ((lo >> 5) + (q >> 3))) >> ((q & 7) * 4);
+                        if (!(bits & 1u)) v.x = -INFINITY;
+                        if (!(bits & 2u)) v.y = -INFINITY;
+                        if (!(bits & 4u)) v.z = -INFINITY;
+                        if (!(bits & 8u)) v.w = -INFINITY;
+                        ((float4*)X)[q] = v;
+                    }
+                    tmax = fmaxf(tmax, fmaxf(fmaxf(v.x, v.y), fmaxf(v.z, v.w)));
+                }
+                for (uint32_t i = nq * 4 + tid; i < len; i += NT) take1(i, __ldcs((const float*)rowp + lo + i));
+            }
         } else {
             const uint2* src = (const uint2*)(rowp) + lo / 4;    // 4 bf16 per 8-byte load
             for (uint32_t q0 = tid; q0 < nq; q0 += 4 * NT) {
@@ -292,7 +303,7 @@ __global__ void __launch_bounds__(NT, 1) fused_row_kernel(const RowArgs a, const
         const bool do_rep = rep != 1.0f;
         int spill = 0;
         if (nh > 0 && (do_fp || do_rep) && !nonfinite) {
-            for (int s = tid; s < F_HASH; s += NT) { sm.r_a.pen.hkey[s] = 0xffffffffu; sm.r_a.pen.hcnt[s] = 0u; }
+            for (int s = tid; s < F_HASH; s += NT) { sm.pen.hkey[s] = 0xffffffffu; sm.pen.hcnt[s] = 0u; }
             __syncthreads();
             for (uint32_t j = tid; j < nh; j += NT) {
                 const uint32_t id = __ldg(a.hist_ids + h0 + j);
@@ -300,8 +311,8 @@ __global__ void __launch_bounds__(NT, 1) fused_row_kernel(const RowArgs a, const
                 uint32_t s = (id * 2654435761u) >> 21;   // 11 bits
                 bool placed = false;
                 for (int probe = 0; probe < 64; probe++) {
-                    const uint32_t prev = atomicCAS(&sm.r_a.pen.hkey[s], 0xffffffffu, id);
-                    if (prev == 0xffffffffu || prev == id) { atomicAdd(&sm.r_a.pen.hcnt[s], 1u); placed = true; break; }
+                    const uint32_t prev = atomicCAS(&sm.pen.hkey[s], 0xffffffffu, id);
+                    if (prev == 0xffffffffu || prev == id) { atomicAdd(&sm.pen.hcnt[s], 1u); placed = true; break; }
                     s = (s + 1) & (F_HASH - 1);
                 }
                 if (!placed) spill = 1;
@@ -309,13 +320,13 @@ __global__ void __launch_bounds__(NT, 1) fused_row_kernel(const RowArgs a, const
             spill = __syncthreads_or(spill);
             if (!spill) {
                 for (int s = tid; s < F_HASH; s += NT) {
-                    const uint32_t id = sm.r_a.pen.hkey[s];
+                    const uint32_t id = sm.pen.hkey[s];
                     if (id == 0xffffffffu) continue;
                     const uint32_t i = id - lo;
                     float x = X[i];
                     if (do_rep) x = x > 0.0f ? fdiv(x, rep) : fmul(x, rep);
                     if (do_fp) {
-                        x = fsub(x, fmul(freq, (float)sm.r_a.pen.hcnt[s]));
+                        x = fsub(x, fmul(freq, (float)sm.pen.hcnt[s]));
                         if (do_pres) x = fsub(x, pres);
                     }
                     // an overflowed penalty is non-finite; the chain treats that like a masked entry
@@ -389,15 +400,15 @@ __global__ void __launch_bounds__(NT, 1) fused_row_kernel(const RowArgs a, const
         const uint32_t amax = any ? 0xffffffffu - (uint32_t)gbest : 0u;
         const int status = any ? ROW_OK : ROW_EMPTY;
         if (any_nonfinite) {
-            if (writer) { a.token[row] = 0; a.status[row] = ROW_NONFINITE; if (a.drew) a.drew[row] = 0; }
+            if (writer) { a.token[row] = 0; a.status[row] = (any_nonfinite & 2) ? ROW_LOAD_TIMEOUT : ROW_NONFINITE; if (a.drew) a.drew[row] = 0; fl.recs[row].kind = 0; }
             continue;
         }
         if (gflags & 2u) {
-            if (writer) { a.token[row] = 0; a.status[row] = ROW_DEAD; if (a.drew) a.drew[row] = 0; }
+            if (writer) { a.token[row] = 0; a.status[row] = ROW_DEAD; if (a.drew) a.drew[row] = 0; fl.recs[row].kind = 0; }
             continue;
         }
         if (any_spill) {
-            if (writer) fl.work_rows[atomicAdd(fl.work_count, 1u)] = row;
+            if (writer) { fl.work_rows[atomicAdd(fl.work_count, 1u)] = row; fl.recs[row].kind = 0; }
             continue;
         }
         if (greedy || !any) {
@@ -409,61 +420,116 @@ __global__ void __launch_bounds__(NT, 1) fused_row_kernel(const RowArgs a, const
                 if (a.sumexp) a.sumexp[row] = 0.0f;
                 if (a.total) a.total[row] = 0.0f;
                 if (a.n_kept) a.n_kept[row] = 0u;
+                fl.recs[row].kind = 0;
             }
             continue;
         }
 
         // -------------------------------- top-k bound: k-th largest per-thread maximum
+        // The C*NT maxima are spread over 2048 equal-width buckets between their smallest finite
+        // value and the row maximum (a monotone map), the bucket holding the k-th largest is found
+        // from the histogram, and the exact value is picked among that bucket's few members.
         const float t = fmaxf(temp, 1e-9f);
-        const uint32_t kk = radix_select_kth([&](int i) { return order_key(sm.tmax_all[i]); }, (int)(C * NT),
-                                             top_k, sm.sel, sm.rs);
         float cut = -INFINITY;
-        if (kk) {
-            const float bound = key_to_float(kk);
-            // every logit whose probability could still tie with the k-th one stays above the cut
-            const float delta = 4.8e-7f * (fabsf(m - bound) + 4.0f * t) + 4.8e-7f * (fabsf(bound) + fabsf(m));
-            cut = bound - delta;
-        }
-        PGS_TICK(4);   // select
-        if (tid == 0) sm.cand_n = 0;
-        __syncthreads();
         {
-            for (uint32_t q = tid; q < nq; q += NT) {
-                const float4 v = ((const float4*)X)[q];
-                const float vv[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-                for (int j = 0; j < 4; j++) {
-                    if (vv[j] >= cut && finite_f(vv[j])) {
-                        const uint32_t at = atomicAdd(&sm.cand_n, 1u);
-                        if (at < (uint32_t)F_LCAP) { sm.cand_id[at] = lo + q * 4 + j; sm.cand_x[at] = vv[j]; }
+            const uint32_t nv = C * NT;
+            uint32_t fin = 0;
+            unsigned long long inv_min = 0ull;
+            for (uint32_t i = tid; i < nv; i += NT) {
+                const uint32_t key = order_key(sm.tmax_all[i]);
+                if (key) { fin++; const unsigned long long iv = 0xffffffffull - key; inv_min = iv > inv_min ? iv : inv_min; }
+            }
+            const uint32_t n_fin = block_sum_u32(fin, sm.rs);
+            inv_min = block_max_u64(inv_min, sm.rs);
+            if (n_fin >= top_k) {
+                const float lo_v = key_to_float((uint32_t)(0xffffffffull - inv_min));
+                const float sc = m > lo_v ? 2047.0f / (m - lo_v) : 0.0f;
+                for (int bkt = tid; bkt < 2048; bkt += NT) sm.sel.hist[bkt] = 0u;
+                if (tid == 0) { sm.sel.prefix = 0xffffffffu; sm.sel.k = 0u; sm.cand_n = 0u; }
+                __syncthreads();
+                for (uint32_t i = tid; i < nv; i += NT) {
+                    const float v = sm.tmax_all[i];
+                    if (finite_f(v)) atomicAdd(&sm.sel.hist[min(2047u, (uint32_t)((v - lo_v) * sc))], 1u);
+                }
+                __syncthreads();
+                if (tid < 32) {
+                    // lane l owns buckets 2047-64l .. 2047-64l-63, i.e. the walk goes from the top down
+                    uint32_t mine = 0;
+                    for (int j = 0; j < 64; j++) mine += sm.sel.hist[2047 - 64 * tid - j];
+                    uint32_t inc = mine;
+                    for (int o = 1; o < 32; o <<= 1) {
+                        const uint32_t up = __shfl_up_sync(FULL, inc, o);
+                        if (tid >= o) inc += up;
+                    }
+                    if (inc >= top_k && inc - mine < top_k) {
+                        uint32_t above = inc - mine;
+                        for (int j = 0; j < 64; j++) {
+                            const uint32_t c = sm.sel.hist[2047 - 64 * tid - j];
+                            if (above + c >= top_k) { sm.sel.prefix = 2047 - 64 * tid - j; sm.sel.k = top_k - above; break; }
+                            above += c;
+                        }
                     }
                 }
-            }
-            for (uint32_t i = nq * 4 + tid; i < len; i += NT) {
-                const float x = X[i];
-                if (x >= cut && finite_f(x)) {
-                    const uint32_t at = atomicAdd(&sm.cand_n, 1u);
-                    if (at < (uint32_t)F_LCAP) { sm.cand_id[at] = lo + i; sm.cand_x[at] = x; }
+                __syncthreads();
+                const uint32_t bsel = sm.sel.prefix, ksel = sm.sel.k;
+                // members of the selected bucket -> cand_x (reused as scratch, at most F_LCAP of them)
+                for (uint32_t i = tid; i < nv; i += NT) {
+                    const float v = sm.tmax_all[i];
+                    if (finite_f(v) && min(2047u, (uint32_t)((v - lo_v) * sc)) == bsel) {
+                        const uint32_t at = atomicAdd(&sm.cand_n, 1u);
+                        if (at < (uint32_t)F_LCAP) sm.cand_x[at] = v;
+                    }
+                }
+                if (tid == 0) sm.sel.hist[0] = 0u;   // reused: order key of the bound
+                __syncthreads();
+                const uint32_t nm = sm.cand_n;
+                if (nm <= (uint32_t)F_LCAP) {
+                    for (uint32_t j = tid; j < nm; j += NT) {
+                        const float v = sm.cand_x[j];
+                        uint32_t gt = 0, ge = 0;
+                        for (uint32_t o = 0; o < nm; o++) { gt += sm.cand_x[o] > v; ge += sm.cand_x[o] >= v; }
+                        if (gt < ksel && ksel <= ge) sm.sel.hist[0] = order_key(v);
+                    }
+                } else {
+                    // too many equal-bucket maxima: any member bounds the k-th largest from below
+                    if (tid == 0) sm.sel.hist[0] = order_key(lo_v);
+                }
+                __syncthreads();
+                const uint32_t kk = sm.sel.hist[0];
+                if (kk) {
+                    const float bound = key_to_float(kk);
+                    // every logit whose probability could still tie with the k-th one stays above the cut
+                    const float delta = 4.8e-7f * (fabsf(m - bound) + 4.0f * t) + 4.8e-7f * (fabsf(bound) + fabsf(m));
+                    cut = bound - delta;
                 }
             }
         }
+        PGS_TICK(4);   // select
         __syncthreads();
-        const uint32_t my_n = sm.cand_n;
-        PGS_TICK(5);   // gather
-
-        // --------------- softmax numerators in place (hardware exp2) + per-thread chunk sums
+        if (tid == 0) sm.cand_n = 0;
+        __syncthreads();
+        // ---- one pass in chunk order: collect the candidates, then overwrite each logit with its
+        //      softmax numerator (hardware exp2) and accumulate the plain chunk sum
         const float scale = 1.4426950408889634f / t;
         const uint32_t L = fl.chunk;
         const uint32_t c0 = min(len, tid * L), c1 = min(len, c0 + L);
         float csum = 0.0f;
         for (uint32_t i = c0; i < c1; i++) {
-            const float e = ex2_approx((X[i] - m) * scale);   // masked entries are -inf: 2^-inf = +0
+            const float x = X[i];
+            if (x >= cut && finite_f(x)) {
+                const uint32_t at = atomicAdd(&sm.cand_n, 1u);
+                if (at < (uint32_t)F_LCAP) { sm.cand_id[at] = lo + i; sm.cand_x[at] = x; }
+            }
+            const float e = ex2_approx((x - m) * scale);   // masked entries are -inf: 2^-inf = +0
             X[i] = e;
             csum += e;
         }
+        __syncthreads();
+        const uint32_t my_n = sm.cand_n;
+        PGS_TICK(5);   // gather + exp
         double dtot;
         const double pre0 = block_excl_scan_f64((double)csum, &dtot, sm.dscan);
-        PGS_TICK(6);   // exp pass
+        PGS_TICK(6);   // scan
         // ------------------------------------------------ cluster exchange #2
         for (uint32_t r = tid; r < C; r += NT) {
             FusedSmem* peer = cluster.map_shared_rank(&sm, r);
@@ -482,17 +548,13 @@ __global__ void __launch_bounds__(NT, 1) fused_row_kernel(const RowArgs a, const
         }
         overflow |= cand_total > (uint32_t)F_MCAP;
         if (overflow) {   // identical decision in every CTA
-            if (writer) fl.work_rows[atomicAdd(fl.work_count, 1u)] = row;
+            if (writer) { fl.work_rows[atomicAdd(fl.work_count, 1u)] = row; fl.recs[row].kind = 0; }
             continue;
         }
-        // candidates -> CTA 0 (lands before exchange #4)
-        {
-            FusedSmem* root = cluster.map_shared_rank(&sm, 0);
-            for (uint32_t j = tid; j < my_n; j += NT) {
-                root->r_a.mrg.m_id[cand_off + j] = sm.cand_id[j];
-                root->r_a.mrg.m_x[cand_off + j] = sm.cand_x[j];
-            }
-            if (writer) sm.m_n = cand_total;
+        // candidates -> global memory, in slice order, for the finish kernel
+        for (uint32_t j = tid; j < my_n; j += NT) {
+            fl.cand_id[(size_t)row * F_MCAP + cand_off + j] = sm.cand_id[j];
+            fl.cand_x[(size_t)row * F_MCAP + cand_off + j] = sm.cand_x[j];
         }
         // ---------- the sequential fold, chunk by chunk: first from the plain prefix sums ...
         const float start0 = (float)(before0 + pre0);
@@ -506,135 +568,33 @@ __global__ void __launch_bounds__(NT, 1) fused_row_kernel(const RowArgs a, const
         cluster.sync();   // exchange #3
         double before1 = 0.0;
         for (uint32_t r = 0; r < rank; r++) before1 += xc.fold1[r];
-        // ... then once more from the running values that first pass implies
+        // ... then once more, for the chunks whose binade that first pass got wrong or crossed
         const float start1 = (float)(before1 + pre1);
-        acc = start1;
-        for (uint32_t i = c0; i < c1; i++) acc = fadd(acc, X[i]);
-        double inc2 = (double)acc - (double)start1;
+        const uint32_t e0 = f2u(start0) & 0x7f800000u;
+        double inc2 = inc1;
+        if ((f2u(start1) & 0x7f800000u) != e0 || (f2u(acc) & 0x7f800000u) != e0) {
+            acc = start1;
+            for (uint32_t i = c0; i < c1; i++) acc = fadd(acc, X[i]);
+            inc2 = (double)acc - (double)start1;
+        }
         double tot2;
         block_excl_scan_f64(inc2, &tot2, sm.dscan);
-        if (tid == 0) cluster.map_shared_rank(&sm, 0)->xchg[pbuf].fold2[rank] = tot2;
-        cluster.sync();   // exchange #4
-        PGS_TICK(9);   // fold 2
-        if (rank != 0) continue;
-
-        // ------------------------------------------ CTA 0: the reference's rule on the candidates
-        double s2 = 0.0;
-        for (uint32_t r = 0; r < C; r++) s2 += xc.fold2[r];
-        const float S = (float)s2;
-        const uint32_t n = sm.m_n;
-        const bool norm = S > 1e-9f;
-        FusedCand& cd = *reinterpret_cast<FusedCand*>(X);
-        const uint32_t* m_id = sm.r_a.mrg.m_id;
-        for (uint32_t j = tid; j < n; j += NT) {
-            const float e = softmax_num(sm.r_a.mrg.m_x[j], m, t, tab);   // exact expf for candidates
-            cd.p[j] = norm ? fdiv(e, S) : e;
-        }
-        __syncthreads();
-        // rank every candidate by id and by (probability descending, id ascending)
-        for (uint32_t j = tid; j < n; j += NT) {
-            const uint32_t idj = m_id[j];
-            const float pj = cd.p[j];
-            uint32_t r_id = 0, r_p = 0;
-            for (uint32_t o = 0; o < n; o++) {
-                const uint32_t ido = m_id[o];
-                const float po = cd.p[o];
-                r_id += ido < idj;
-                r_p += (po > pj) || (po == pj && ido < idj);
-            }
-            cd.sid[r_id] = idj;
-            cd.sp[r_id] = pj;
-            cd.rp[r_p] = pj;
-            cd.rpos[r_p] = r_id;
-        }
-        if (tid == 0) { sm.n_live = 0; }
-        __syncthreads();
-        // top-k: every tie at the k-th probability survives (sampler.rs:116-128); zeros never matter
-        {
-            const float thr = top_k <= n ? cd.rp[top_k - 1] : 0.0f;
-            for (uint32_t j = tid; j < n; j += NT) {
-                const bool live = cd.rp[j] >= thr && cd.rp[j] > 0.0f;
-                const bool next_live = j + 1 < n && cd.rp[j + 1] >= thr && cd.rp[j + 1] > 0.0f;
-                if (live && !next_live) sm.n_live = j + 1;
-            }
-        }
-        __syncthreads();
-        const uint32_t n_live = sm.n_live;
-        // top-p walk in ranked order (sampler.rs:130-150)
-        uint32_t keep = n_live;
-        if (use_p && n_live > 0) {
-            int found = -1;
-            if (n_live <= 128) {
-                if (tid < 32) {
-                    warp_fold(cd.rp, (int)n_live, SEQ_FIND_GE, top_p, &found);
-                    if (tid == 0) sm.bcast_i = found;
-                }
-                __syncthreads();
-                found = sm.bcast_i;
-            } else {
-                seq_scan([&](int j) { return cd.rp[j]; }, (int)n_live, 0.0f, SEQ_FIND_GE, top_p, &found, cd.seq, sm.rs);
-            }
-            if (found >= 0) keep = (uint32_t)found + 1;
-        }
-        for (uint32_t j = keep + tid; j < n; j += NT) cd.sp[cd.rpos[j]] = 0.0f;
-        __syncthreads();
-        // total and inverse-CDF pick in id order (sampler.rs:40-55)
-        float total;
-        int pick = -1;
-        if (n <= 128) {
-            if (tid < 32) {
-                const float tt = warp_fold(cd.sp, (int)n, SEQ_SUM, 0.0f, nullptr);
-                int f = -1;
-                if (tt > 1e-9f) warp_fold(cd.sp, (int)n, SEQ_FIND_GT, fmul(u01, tt), &f);
-                if (tid == 0) { sm.bcast_f = tt; sm.bcast_i = f; }
-            }
-            __syncthreads();
-            total = sm.bcast_f;
-            pick = sm.bcast_i;
-        } else {
-            total = seq_scan([&](int j) { return cd.sp[j]; }, (int)n, 0.0f, SEQ_SUM, 0.0f, nullptr, cd.seq, sm.rs);
-            if (total > 1e-9f)
-                seq_scan([&](int j) { return cd.sp[j]; }, (int)n, 0.0f, SEQ_FIND_GT, fmul(u01, total), &pick, cd.seq,
-                         sm.rs);
-        }
         if (tid == 0) {
-            uint32_t token = amax;
-            int drew = 0;
-            if (total > 1e-9f) { token = pick >= 0 ? cd.sid[pick] : V - 1; drew = 1; }
-            a.token[row] = token; a.status[row] = status;
-            if (a.drew) a.drew[row] = (uint8_t)drew;
-            if (a.argmax) a.argmax[row] = amax;
-            if (a.row_max) a.row_max[row] = m;
-            if (a.sumexp) a.sumexp[row] = S;
-            if (a.total) a.total[row] = total;
-        }
-        PGS_TICK(10);  // candidates
-        if (a.n_kept || a.dump_ids || a.dump_probs) {   // diagnostics: the kept set in id order
-            uint32_t done = 0;
-            for (uint32_t base = 0; base < n; base += NT) {
-                const uint32_t j = base + tid;
-                const uint32_t kept = (j < n && cd.sp[j] > 0.0f) ? 1u : 0u;
-                uint32_t tot;
-                const uint32_t at = done + block_excl_scan_u32(kept, &tot, sm.rs);
-                if (kept && at < a.dump_cap) {
-                    if (a.dump_ids) a.dump_ids[(size_t)row * a.dump_cap + at] = cd.sid[j];
-                    if (a.dump_probs) a.dump_probs[(size_t)row * a.dump_cap + at] = cd.sp[j];
-                }
-                done += tot;
+            RowRec& rec = fl.recs[row];
+            rec.part[rank] = tot2;
+            if (rank == 0) {
+                rec.kind = 1; rec.n_cand = cand_total; rec.amax = amax; rec.status = status;
+                rec.m = m; rec.t = t; rec.n_parts = C;
             }
-            if (tid == 0 && a.n_kept) a.n_kept[row] = done;
         }
-        __syncthreads();
+        PGS_TICK(9);   // fold 2
     }
     // no CTA may exit while a peer can still write into its shared memory
     cluster.sync();
 }
 
-// the slice buffer doubles as CTA 0's candidate workspace
 size_t fused_smem_bytes(uint32_t slice_len) {
-    const size_t need = (sizeof(FusedCand) + 3) / 4;
-    const size_t floats = slice_len > need ? slice_len : need;
-    return ((sizeof(FusedSmem) + 15) & ~size_t(15)) + floats * sizeof(float);
+    return ((sizeof(FusedSmem) + 15) & ~size_t(15)) + (size_t)slice_len * sizeof(float);
 }
 
 cudaError_t configure_fused(size_t max_smem) {
