@@ -452,22 +452,25 @@ __global__ void __launch_bounds__(NT, 1) fused_row_kernel(const RowArgs a, const
                     if (finite_f(v)) atomicAdd(&sm.sel.hist[min(2047u, (uint32_t)((v - lo_v) * sc))], 1u);
                 }
                 __syncthreads();
-                if (tid < 32) {
-                    // lane l owns buckets 2047-64l .. 2047-64l-63, i.e. the walk goes from the top down
-                    uint32_t mine = 0;
-                    for (int j = 0; j < 64; j++) mine += sm.sel.hist[2047 - 64 * tid - j];
-                    uint32_t inc = mine;
+                {
+                    // walk from the top bucket down: warp w owns buckets 2047-64w .. 2047-64w-63 (two per lane)
+                    const int w = tid >> 5, lane = tid & 31;
+                    const uint32_t h0v = sm.sel.hist[2047 - 64 * w - 2 * lane];
+                    const uint32_t h1v = sm.sel.hist[2047 - 64 * w - 2 * lane - 1];
+                    uint32_t inc = h0v + h1v;
                     for (int o = 1; o < 32; o <<= 1) {
                         const uint32_t up = __shfl_up_sync(FULL, inc, o);
-                        if (tid >= o) inc += up;
+                        if (lane >= o) inc += up;
                     }
-                    if (inc >= top_k && inc - mine < top_k) {
-                        uint32_t above = inc - mine;
-                        for (int j = 0; j < 64; j++) {
-                            const uint32_t c = sm.sel.hist[2047 - 64 * tid - j];
-                            if (above + c >= top_k) { sm.sel.prefix = 2047 - 64 * tid - j; sm.sel.k = top_k - above; break; }
-                            above += c;
-                        }
+                    if (lane == 31) sm.rs.u[w] = inc;
+                    __syncthreads();
+                    uint32_t above = 0;
+                    for (int ww = 0; ww < w; ww++) above += sm.rs.u[ww];
+                    const uint32_t before_me = above + inc - h0v - h1v;   // maxima in higher buckets
+                    if (before_me < top_k && before_me + h0v >= top_k) {
+                        sm.sel.prefix = 2047 - 64 * w - 2 * lane; sm.sel.k = top_k - before_me;
+                    } else if (before_me + h0v < top_k && before_me + h0v + h1v >= top_k) {
+                        sm.sel.prefix = 2047 - 64 * w - 2 * lane - 1; sm.sel.k = top_k - before_me - h0v;
                     }
                 }
                 __syncthreads();
