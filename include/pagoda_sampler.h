@@ -137,6 +137,42 @@ PGS_API int pgs_sample_batch_async(pgs_handle *h, const pgs_batch_desc *desc, vo
  * every token id -- bit for bit, at a fraction of the speed.  (Environment: PGS_EXACT=1.) */
 PGS_API int pgs_set_exact(pgs_handle *h, int on);
 
+/* ---- vocabulary-sharded sampling (extension; the reference has no multi-GPU code) ----------
+ * Rank r of n holds columns [r * vocab/n, (r+1) * vocab/n) of every row.  pgs_tp_partial emits one
+ * record of pgs_tp_record_bytes(cand) bytes per row (shard max, shard sum, argmax, the `cand`
+ * largest logits with global ids); the caller all-gathers the records of all ranks into
+ * [n_shards][rows][record] (NCCL over NVLink) and pgs_tp_merge turns them into tokens with the
+ * same softmax / top-p / inverse-CDF rule as Sampler::sample (sampler.rs:28-55) restricted to
+ * the union of the candidates.  All pointers are device memory; both calls only enqueue work
+ * on `cuda_stream` (NULL = the handle's stream). */
+typedef struct pgs_tp_desc {
+    uint32_t struct_size;
+    uint32_t rows;
+    uint32_t vocab;               /* full vocabulary; must be a multiple of n_shards */
+    uint32_t n_shards, shard_rank;
+    uint32_t cand;                /* candidates per shard, 1..128 */
+    uint64_t row_stride;          /* elements between rows of the shard */
+    const float *logits;          /* [rows x row_stride] f32, this rank's columns */
+    const float *temperature;     /* per row; NULL = greedy */
+    const float *top_p;           /* per row; NULL = 1.0 */
+    const float *uniform;         /* per row */
+} pgs_tp_desc;
+PGS_API size_t pgs_tp_record_bytes(uint32_t cand);
+PGS_API int pgs_tp_partial(pgs_handle *h, const pgs_tp_desc *desc, void *records_out, void *cuda_stream);
+typedef struct pgs_tp_out {
+    uint32_t *token; int32_t *status; uint8_t *drew;   /* token and status required */
+    uint32_t *argmax; float *gmax; float *gsum; float *total; uint32_t *n_kept; /* optional */
+} pgs_tp_out;
+PGS_API int pgs_tp_merge(pgs_handle *h, const pgs_tp_desc *desc, const void *records_all,
+                         const pgs_tp_out *out, void *cuda_stream);
+/* Draft verification over per-position argmax ids (pagoda-hf/src/qwen3_5.rs:663-755 produces
+ * them; the reference leaves the accept rule open): accepted[s] = length of the longest prefix
+ * with row_argmax[s][j] == draft[s][j]; next[s] = the argmax at the first mismatch, or of the
+ * last position when everything is accepted.  Device pointers. */
+PGS_API int pgs_draft_accept(pgs_handle *h, const uint32_t *row_argmax, const uint32_t *draft,
+                             uint32_t sequences, uint32_t positions, uint32_t *accepted,
+                             uint32_t *next, void *cuda_stream);
+
 /* Counters since creation (for the engine's /stats): rows sampled, rows faulted, algorithmic
  * bytes touched. */
 typedef struct pgs_counters {

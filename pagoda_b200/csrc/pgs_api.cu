@@ -25,6 +25,25 @@ cudaError_t configure_fused(size_t max_smem);
 cudaError_t fused_max_clusters(uint32_t cluster, size_t smem, int* out);
 cudaError_t launch_fused(const RowArgs& a, const FusedLaunch& fl, uint32_t n_clusters, size_t smem,
                          cudaStream_t stream);
+struct TpArgs {
+    const float* logits;
+    unsigned long long row_stride;
+    uint32_t rows, vocab, shard_vocab, shard_lo, n_shards, cand;
+    const float* temperature;
+    const float* top_p;
+    const float* uniform;
+    unsigned char* records;
+    uint32_t rec_bytes;
+};
+struct TpOut {
+    uint32_t* token; int32_t* status; uint8_t* drew; uint32_t* argmax;
+    float* gmax; float* gsum; float* total; uint32_t* n_kept;
+};
+cudaError_t configure_tp();
+cudaError_t launch_tp_partial(const TpArgs& a, uint32_t grid, cudaStream_t stream);
+cudaError_t launch_tp_merge(const TpArgs& a, const TpOut& o, cudaStream_t stream);
+cudaError_t launch_draft_accept(const uint32_t* row_argmax, const uint32_t* draft, uint32_t sequences,
+                                uint32_t positions, uint32_t* accepted, uint32_t* next, cudaStream_t stream);
 cudaError_t configure_finish();
 cudaError_t launch_finish(const RowArgs& a, const FusedLaunch& fl, cudaStream_t stream);
 }  // namespace pgs
@@ -158,6 +177,7 @@ extern "C" int pgs_create(int device, uint32_t max_rows, uint32_t max_vocab, uin
         h->smem_optin = prop.sharedMemPerBlockOptin;
         PGS_CUDA(nullptr, pgs::configure_fused(h->smem_optin));
         PGS_CUDA(nullptr, pgs::configure_finish());
+        PGS_CUDA(nullptr, pgs::configure_tp());
         PGS_CUDA(nullptr, cudaMalloc(&h->recs, (size_t)max_rows * sizeof(pgs::RowRec)));
         PGS_CUDA(nullptr, cudaMemsetAsync(h->recs, 0, (size_t)max_rows * sizeof(pgs::RowRec), h->stream));
         PGS_CUDA(nullptr, cudaMalloc(&h->cand_id, (size_t)max_rows * pgs::F_MCAP * sizeof(uint32_t)));
@@ -512,4 +532,67 @@ extern "C" int pgs_sample_batch_async(pgs_handle* h, const pgs_batch_desc* desc,
     if (desc && (desc->logits_mem != PGS_MEM_DEVICE || desc->aux_mem != PGS_MEM_DEVICE))
         return fail(h, PGS_ERR_INVALID, "pgs_sample_batch_async needs every array in device memory");
     return run_batch(h, desc, cuda_stream ? (cudaStream_t)cuda_stream : h->stream, false);
+}
+
+// ------------------------------------------------------------------- vocabulary-sharded mode
+
+extern "C" size_t pgs_tp_record_bytes(uint32_t cand) { return 16 + (size_t)cand * 8; }
+
+static int tp_args(pgs_handle* h, const pgs_tp_desc* d, pgs::TpArgs* a) {
+    if (!d || d->struct_size != sizeof(pgs_tp_desc)) return fail(h, PGS_ERR_INVALID, "bad pgs_tp_desc");
+    if (d->n_shards == 0 || d->n_shards > 8 || d->shard_rank >= d->n_shards || d->vocab % d->n_shards)
+        return fail(h, PGS_ERR_INVALID, "need 1 <= n_shards <= 8, rank < n_shards, vocab divisible by n_shards");
+    if (d->cand == 0 || d->cand > 128) return fail(h, PGS_ERR_INVALID, "cand must be in 1..128");
+    if (d->rows == 0 || d->rows > h->max_rows * 16u) return fail(h, PGS_ERR_LIMIT, "too many rows");
+    a->shard_vocab = d->vocab / d->n_shards;
+    if (d->row_stride < a->shard_vocab) return fail(h, PGS_ERR_INVALID, "row_stride < shard width");
+    a->logits = d->logits; a->row_stride = d->row_stride; a->rows = d->rows; a->vocab = d->vocab;
+    a->shard_lo = d->shard_rank * a->shard_vocab; a->n_shards = d->n_shards; a->cand = d->cand;
+    a->temperature = d->temperature; a->top_p = d->top_p; a->uniform = d->uniform;
+    a->rec_bytes = (uint32_t)pgs_tp_record_bytes(d->cand);
+    return PGS_OK;
+}
+
+extern "C" int pgs_tp_partial(pgs_handle* h, const pgs_tp_desc* d, void* records_out, void* cuda_stream) {
+    if (!h) return PGS_ERR_INVALID;
+    pgs::TpArgs a;
+    int rc = tp_args(h, d, &a);
+    if (rc != PGS_OK) return rc;
+    if (!d->logits || !records_out) return fail(h, PGS_ERR_INVALID, "logits and records_out are required");
+    DeviceGuard g(h->device);
+    a.records = (unsigned char*)records_out;
+    const uint32_t grid = a.rows < (uint32_t)h->sm_count ? a.rows : (uint32_t)h->sm_count;
+    PGS_CUDA(h, pgs::launch_tp_partial(a, grid, cuda_stream ? (cudaStream_t)cuda_stream : h->stream));
+    h->counters.kernel_launches += 1;
+    return PGS_OK;
+}
+
+extern "C" int pgs_tp_merge(pgs_handle* h, const pgs_tp_desc* d, const void* records_all, const pgs_tp_out* out,
+                            void* cuda_stream) {
+    if (!h) return PGS_ERR_INVALID;
+    pgs::TpArgs a;
+    int rc = tp_args(h, d, &a);
+    if (rc != PGS_OK) return rc;
+    if (!records_all || !out || !out->token || !out->status)
+        return fail(h, PGS_ERR_INVALID, "records_all, out->token and out->status are required");
+    DeviceGuard g(h->device);
+    a.records = (unsigned char*)records_all;
+    pgs::TpOut o{out->token, out->status, out->drew, out->argmax, out->gmax, out->gsum, out->total, out->n_kept};
+    PGS_CUDA(h, pgs::launch_tp_merge(a, o, cuda_stream ? (cudaStream_t)cuda_stream : h->stream));
+    h->counters.kernel_launches += 1;
+    h->counters.rows += a.rows;
+    return PGS_OK;
+}
+
+extern "C" int pgs_draft_accept(pgs_handle* h, const uint32_t* row_argmax, const uint32_t* draft, uint32_t sequences,
+                                uint32_t positions, uint32_t* accepted, uint32_t* next, void* cuda_stream) {
+    if (!h) return PGS_ERR_INVALID;
+    if (!row_argmax || !draft || !accepted || !next || positions == 0)
+        return fail(h, PGS_ERR_INVALID, "pgs_draft_accept: NULL argument or zero positions");
+    if (sequences == 0) return PGS_OK;
+    DeviceGuard g(h->device);
+    PGS_CUDA(h, pgs::launch_draft_accept(row_argmax, draft, sequences, positions, accepted, next,
+                                         cuda_stream ? (cudaStream_t)cuda_stream : h->stream));
+    h->counters.kernel_launches += 1;
+    return PGS_OK;
 }

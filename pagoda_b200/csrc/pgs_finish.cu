@@ -1,175 +1,21 @@
 // Finish kernel: one CTA per batch row turns the record the fused kernel left behind (row max,
-// the f32 sum, a short candidate list that contains the whole top-k set) into a token by applying
-// the reference's rule exactly: probabilities exp((x - max) / t) / sum (sampler.rs:92-114), top-k
-// threshold with every tie kept (sampler.rs:116-128), top-p walk by probability descending / id
-// ascending (sampler.rs:130-150), then the total and the inverse-CDF walk in id order
-// (sampler.rs:40-55).  All rows run side by side, so the short serial folds of one row overlap
-// with those of every other row.
-#include <cuda_runtime.h>
-
-#include "pgs_args.cuh"
-#include "pgs_block.cuh"
-#include "pgs_fused.cuh"
+// the f32 sum, a short candidate list that contains the whole top-k set) into a token.  All rows
+// run side by side, so the short serial folds of one row overlap with those of every other row.
+#include "pgs_finish.cuh"
 
 namespace pgs {
-
-struct FinishSmem {
-    ReduceSmem rs;
-    unsigned long long exp_tab[32];
-    uint32_t m_id[F_MCAP];          // candidate ids, arrival order
-    float p[F_MCAP];                // probabilities, arrival order
-    uint32_t sid[F_MCAP];           // ids ascending
-    float sp[F_MCAP];               // probabilities in id order (zeroed when dropped)
-    float rp[F_MCAP];               // probabilities descending (ties: id ascending)
-    uint32_t rpos[F_MCAP];          // position in the id-ordered list of the entry at each rank
-    SeqSmem seq;
-    uint32_t n_live;
-    float bcast_f;
-    int bcast_i;
-};
-
-// Exact left fold of n <= 128 shared-memory floats by one warp (values travel by shuffle, so the
-// dependent chain is add + shuffle instead of add + shared-memory load).  mode/target as in
-// seq_scan; returns the running value, *found = first index where the predicate holds or -1.
-__device__ __forceinline__ float warp_fold(const float* v, int n, int mode, float target, int* found) {
-    const int lane = threadIdx.x & 31;
-    float reg[4];
-#pragma unroll
-    for (int u = 0; u < 4; u++) reg[u] = (lane + 32 * u < n) ? v[lane + 32 * u] : 0.0f;
-    float acc = 0.0f;
-    int f = -1;
-#pragma unroll
-    for (int u = 0; u < 4; u++) {
-        for (int l = 0; l < 32; l++) {
-            const int j = u * 32 + l;
-            if (j >= n || f >= 0) break;
-            acc = fadd(acc, __shfl_sync(FULL, reg[u], l));
-            if (mode != SEQ_SUM && seq_pred(mode, acc, target)) f = j;
-        }
-    }
-    if (found) *found = f;
-    return acc;
-}
-
 
 __global__ void __launch_bounds__(NT, 1) finish_kernel(const RowArgs a, const FusedLaunch fl) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     FinishSmem& sm = *reinterpret_cast<FinishSmem*>(smem_raw);
-    const int tid = threadIdx.x;
     const uint32_t row = blockIdx.x;
-    const RowRec rec = fl.recs[row];
-    if (rec.kind != 1u) return;
-    const uint32_t V = a.vocab;
-    if (tid < 32) sm.exp_tab[tid] = kExp2TableDev[tid];
-    const uint32_t top_k = a.top_k ? a.top_k[row] : 0u;
-    const float top_p = a.top_p ? a.top_p[row] : 1.0f;
-    const float u01 = a.uniform ? a.uniform[row] : 0.0f;
-    const bool use_p = !(top_p >= 1.0f);
+    if (fl.recs[row].kind != 1u) return;
+    const RowRec& rec = fl.recs[row];
     double s2 = 0.0;
     for (uint32_t r = 0; r < rec.n_parts; r++) s2 += rec.part[r];
-    const float S = (float)s2;
-    const uint32_t n = rec.n_cand;
-    const bool norm = S > 1e-9f;
-    const float m = rec.m, t = rec.t;
-    __syncthreads();
-    for (uint32_t j = tid; j < n; j += NT) {
-        sm.m_id[j] = fl.cand_id[(size_t)row * F_MCAP + j];
-        const float e = softmax_num(fl.cand_x[(size_t)row * F_MCAP + j], m, t, sm.exp_tab);   // exact expf
-        sm.p[j] = norm ? fdiv(e, S) : e;
-    }
-    __syncthreads();
-    // rank every candidate by id and by (probability descending, id ascending)
-    for (uint32_t j = tid; j < n; j += NT) {
-        const uint32_t idj = sm.m_id[j];
-        const float pj = sm.p[j];
-        uint32_t r_id = 0, r_p = 0;
-        for (uint32_t o = 0; o < n; o++) {
-            const uint32_t ido = sm.m_id[o];
-            const float po = sm.p[o];
-            r_id += ido < idj;
-            r_p += (po > pj) || (po == pj && ido < idj);
-        }
-        sm.sid[r_id] = idj;
-        sm.sp[r_id] = pj;
-        sm.rp[r_p] = pj;
-        sm.rpos[r_p] = r_id;
-    }
-    if (tid == 0) sm.n_live = 0;
-    __syncthreads();
-    // top-k: every tie at the k-th probability survives; entries with zero probability never matter
-    {
-        const float thr = (top_k != 0u && top_k <= n) ? sm.rp[top_k - 1] : 0.0f;
-        for (uint32_t j = tid; j < n; j += NT) {
-            const bool live = sm.rp[j] >= thr && sm.rp[j] > 0.0f;
-            const bool next_live = j + 1 < n && sm.rp[j + 1] >= thr && sm.rp[j + 1] > 0.0f;
-            if (live && !next_live) sm.n_live = j + 1;
-        }
-    }
-    __syncthreads();
-    const uint32_t n_live = sm.n_live;
-    // top-p walk in ranked order
-    uint32_t keep = n_live;
-    if (use_p && n_live > 0) {
-        int found = -1;
-        if (n_live <= 128) {
-            if (tid < 32) {
-                warp_fold(sm.rp, (int)n_live, SEQ_FIND_GE, top_p, &found);
-                if (tid == 0) sm.bcast_i = found;
-            }
-            __syncthreads();
-            found = sm.bcast_i;
-        } else {
-            seq_scan([&](int j) { return sm.rp[j]; }, (int)n_live, 0.0f, SEQ_FIND_GE, top_p, &found, sm.seq, sm.rs);
-        }
-        if (found >= 0) keep = (uint32_t)found + 1;
-    }
-    __syncthreads();
-    for (uint32_t j = keep + tid; j < n; j += NT) sm.sp[sm.rpos[j]] = 0.0f;
-    __syncthreads();
-    // total and inverse-CDF pick in id order
-    float total;
-    int pick = -1;
-    if (n <= 128) {
-        if (tid < 32) {
-            const float tt = warp_fold(sm.sp, (int)n, SEQ_SUM, 0.0f, nullptr);
-            int f = -1;
-            if (tt > 1e-9f) warp_fold(sm.sp, (int)n, SEQ_FIND_GT, fmul(u01, tt), &f);
-            if (tid == 0) { sm.bcast_f = tt; sm.bcast_i = f; }
-        }
-        __syncthreads();
-        total = sm.bcast_f;
-        pick = sm.bcast_i;
-    } else {
-        total = seq_scan([&](int j) { return sm.sp[j]; }, (int)n, 0.0f, SEQ_SUM, 0.0f, nullptr, sm.seq, sm.rs);
-        if (total > 1e-9f)
-            seq_scan([&](int j) { return sm.sp[j]; }, (int)n, 0.0f, SEQ_FIND_GT, fmul(u01, total), &pick, sm.seq, sm.rs);
-    }
-    if (tid == 0) {
-        uint32_t token = rec.amax;
-        int drew = 0;
-        if (total > 1e-9f) { token = pick >= 0 ? sm.sid[pick] : V - 1; drew = 1; }
-        a.token[row] = token; a.status[row] = rec.status;
-        if (a.drew) a.drew[row] = (uint8_t)drew;
-        if (a.argmax) a.argmax[row] = rec.amax;
-        if (a.row_max) a.row_max[row] = m;
-        if (a.sumexp) a.sumexp[row] = S;
-        if (a.total) a.total[row] = total;
-    }
-    if (a.n_kept || a.dump_ids || a.dump_probs) {   // diagnostics: the kept set in id order
-        uint32_t done = 0;
-        for (uint32_t base = 0; base < n; base += NT) {
-            const uint32_t j = base + tid;
-            const uint32_t kept = (j < n && sm.sp[j] > 0.0f) ? 1u : 0u;
-            uint32_t tot;
-            const uint32_t at = done + block_excl_scan_u32(kept, &tot, sm.rs);
-            if (kept && at < a.dump_cap) {
-                if (a.dump_ids) a.dump_ids[(size_t)row * a.dump_cap + at] = sm.sid[j];
-                if (a.dump_probs) a.dump_probs[(size_t)row * a.dump_cap + at] = sm.sp[j];
-            }
-            done += tot;
-        }
-        if (tid == 0 && a.n_kept) a.n_kept[row] = done;
-    }
+    finish_row(sm, a, row, a.vocab, fl.cand_id + (size_t)row * F_MCAP, fl.cand_x + (size_t)row * F_MCAP, rec.n_cand,
+               rec.m, rec.t, (float)s2, a.top_k ? a.top_k[row] : 0u, a.top_p ? a.top_p[row] : 1.0f,
+               a.uniform ? a.uniform[row] : 0.0f, rec.amax, rec.status);
 }
 
 cudaError_t configure_finish() {
