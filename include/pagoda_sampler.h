@@ -79,6 +79,33 @@ PGS_API int pgs_mask_table_upload(pgs_handle *h, uint32_t n_states, uint32_t wor
                           int32_t *table_id);
 PGS_API int pgs_mask_table_free(pgs_handle *h, int32_t table_id);
 
+/* ---- host-side grammar state machines (no CUDA involved) ------------------------------------
+ * Replace Grammar::regex / Grammar::json / allowed_bytes / is_complete (grammar.rs:32-66,
+ * :458-575, :613-733).  A grammar is tabulated once into mask states (state 0 = dead end); the
+ * table goes to the device through pgs_mask_table_upload and each sequence keeps a small host
+ * state that is advanced by the bytes it emits, instead of re-running the grammar over the whole
+ * output at every step (engine.rs:1297-1313).  Byte-level tokenizers only, as the reference
+ * requires (engine.rs:986-987): token id = first_byte_id + byte. */
+typedef struct pgs_grammar pgs_grammar;
+typedef struct pgs_gstate pgs_gstate;
+PGS_API int pgs_grammar_regex(const char *pattern, pgs_grammar **out, char *err, size_t err_len);
+PGS_API int pgs_grammar_json(pgs_grammar **out);
+PGS_API void pgs_grammar_free(pgs_grammar *g);
+PGS_API uint32_t pgs_grammar_n_states(const pgs_grammar *g);
+/* words_out: [n_states x ceil(vocab/32)], flags_out: [n_states] -- the arguments of pgs_mask_table_upload */
+PGS_API int pgs_grammar_build_table(const pgs_grammar *g, uint32_t vocab, uint32_t first_byte_id,
+                                    uint32_t *words_out, uint8_t *flags_out);
+PGS_API int pgs_grammar_state_new(const pgs_grammar *g, pgs_gstate **out);
+PGS_API int pgs_grammar_state_reset(const pgs_grammar *g, pgs_gstate *s);
+PGS_API void pgs_grammar_state_free(pgs_gstate *s);
+/* feed the bytes of the newly generated token(s) */
+PGS_API int pgs_grammar_advance(const pgs_grammar *g, pgs_gstate *s, const uint8_t *bytes, size_t n);
+/* the row's mask_state for the next step */
+PGS_API uint32_t pgs_grammar_mask_state(const pgs_grammar *g, const pgs_gstate *s);
+/* allowed bytes (256 flags), completeness and deadness of a table state */
+PGS_API int pgs_grammar_state_info(const pgs_grammar *g, uint32_t state, uint8_t *allowed256, int *complete,
+                                   int *dead);
+
 /* One decode step for a batch of rows.  Per-row arrays may be NULL (defaults in
  * brackets, the reference's SamplingParams::default(), spec.rs:90-105). */
 typedef struct pgs_batch_desc {

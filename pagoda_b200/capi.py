@@ -19,7 +19,11 @@ MEM_DEVICE, MEM_HOST = 0, 1
 ROW_OK, ROW_NONFINITE, ROW_DEAD, ROW_EMPTY, ROW_BAD_PARAM = 0, 1, 2, 3, 4
 
 EXPORTS = ["pgs_create", "pgs_destroy", "pgs_last_error", "pgs_mask_table_upload", "pgs_mask_table_free",
-           "pgs_sample_batch", "pgs_sample_batch_async", "pgs_get_counters", "pgs_stream", "pgs_set_exact"]
+           "pgs_sample_batch", "pgs_sample_batch_async", "pgs_get_counters", "pgs_stream", "pgs_set_exact",
+           "pgs_grammar_regex", "pgs_grammar_json", "pgs_grammar_free", "pgs_grammar_n_states",
+           "pgs_grammar_build_table", "pgs_grammar_state_new", "pgs_grammar_state_reset", "pgs_grammar_state_free",
+           "pgs_grammar_advance", "pgs_grammar_mask_state", "pgs_grammar_state_info",
+           "pgs_tp_record_bytes", "pgs_tp_partial", "pgs_tp_merge", "pgs_draft_accept"]
 
 
 class SamplerError(RuntimeError):
@@ -42,6 +46,17 @@ class BatchDesc(C.Structure):
         ("n_kept", C.c_void_p), ("dump_cap", C.c_uint32), ("reserved1", C.c_uint32),
         ("dump_ids", C.c_void_p), ("dump_probs", C.c_void_p),
     ]
+
+
+class TpDesc(C.Structure):
+    _fields_ = [("struct_size", C.c_uint32), ("rows", C.c_uint32), ("vocab", C.c_uint32), ("n_shards", C.c_uint32),
+                ("shard_rank", C.c_uint32), ("cand", C.c_uint32), ("row_stride", C.c_uint64),
+                ("logits", C.c_void_p), ("temperature", C.c_void_p), ("top_p", C.c_void_p), ("uniform", C.c_void_p)]
+
+
+class TpOut(C.Structure):
+    _fields_ = [("token", C.c_void_p), ("status", C.c_void_p), ("drew", C.c_void_p), ("argmax", C.c_void_p),
+                ("gmax", C.c_void_p), ("gsum", C.c_void_p), ("total", C.c_void_p), ("n_kept", C.c_void_p)]
 
 
 class Counters(C.Structure):
@@ -77,6 +92,27 @@ def load_library():
     L.pgs_sample_batch_async.argtypes = [C.c_void_p, C.POINTER(BatchDesc), C.c_void_p]
     L.pgs_get_counters.argtypes = [C.c_void_p, C.POINTER(Counters)]
     L.pgs_set_exact.argtypes = [C.c_void_p, C.c_int]
+    L.pgs_grammar_regex.argtypes = [C.c_char_p, C.POINTER(C.c_void_p), C.c_char_p, C.c_size_t]
+    L.pgs_grammar_json.argtypes = [C.POINTER(C.c_void_p)]
+    L.pgs_grammar_free.argtypes = [C.c_void_p]
+    L.pgs_grammar_free.restype = None
+    L.pgs_grammar_n_states.argtypes = [C.c_void_p]
+    L.pgs_grammar_n_states.restype = C.c_uint32
+    L.pgs_grammar_build_table.argtypes = [C.c_void_p, C.c_uint32, C.c_uint32, C.c_void_p, C.c_void_p]
+    L.pgs_grammar_state_new.argtypes = [C.c_void_p, C.POINTER(C.c_void_p)]
+    L.pgs_grammar_state_reset.argtypes = [C.c_void_p, C.c_void_p]
+    L.pgs_grammar_state_free.argtypes = [C.c_void_p]
+    L.pgs_grammar_state_free.restype = None
+    L.pgs_grammar_advance.argtypes = [C.c_void_p, C.c_void_p, C.c_char_p, C.c_size_t]
+    L.pgs_grammar_mask_state.argtypes = [C.c_void_p, C.c_void_p]
+    L.pgs_grammar_mask_state.restype = C.c_uint32
+    L.pgs_grammar_state_info.argtypes = [C.c_void_p, C.c_uint32, C.c_void_p, C.POINTER(C.c_int), C.POINTER(C.c_int)]
+    L.pgs_tp_record_bytes.restype = C.c_size_t
+    L.pgs_tp_record_bytes.argtypes = [C.c_uint32]
+    L.pgs_tp_partial.argtypes = [C.c_void_p, C.POINTER(TpDesc), C.c_void_p, C.c_void_p]
+    L.pgs_tp_merge.argtypes = [C.c_void_p, C.POINTER(TpDesc), C.c_void_p, C.POINTER(TpOut), C.c_void_p]
+    L.pgs_draft_accept.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_uint32, C.c_uint32, C.c_void_p,
+                                   C.c_void_p, C.c_void_p]
     L.pgs_stream.restype = C.c_void_p
     L.pgs_stream.argtypes = [C.c_void_p]
     _lib = L
@@ -103,6 +139,92 @@ class BatchResult:
     def kept(self, row: int):
         n = min(int(self.n_kept[row]), self.dump_ids.shape[1])
         return self.dump_ids[row, :n], self.dump_probs[row, :n]
+
+
+class GrammarState:
+    """Per-sequence host state of a grammar: advanced by the emitted bytes, read as a table state."""
+
+    def __init__(self, grammar: "Grammar"):
+        self.g = grammar
+        self._s = C.c_void_p()
+        rc = load_library().pgs_grammar_state_new(grammar._g, C.byref(self._s))
+        if rc != 0:
+            raise SamplerError(rc, "pgs_grammar_state_new failed")
+
+    def __del__(self):
+        if getattr(self, "_s", None):
+            load_library().pgs_grammar_state_free(self._s)
+            self._s = None
+
+    def reset(self):
+        load_library().pgs_grammar_state_reset(self.g._g, self._s)
+
+    def advance(self, data: bytes):
+        load_library().pgs_grammar_advance(self.g._g, self._s, data, len(data))
+
+    @property
+    def mask_state(self) -> int:
+        return load_library().pgs_grammar_mask_state(self.g._g, self._s)
+
+    def allowed_bytes(self):
+        """`Grammar::allowed_bytes` of the reference for the bytes fed so far: None when dead."""
+        allowed, complete, dead = self.g.state_info(self.mask_state)
+        return None if dead else allowed
+
+    def is_complete(self) -> bool:
+        return self.g.state_info(self.mask_state)[1]
+
+
+class Grammar:
+    """A tabulated grammar (mirror of `pagoda::Grammar`: `Grammar.regex(pattern)`, `Grammar.json()`)."""
+
+    def __init__(self, handle, name):
+        self._g, self.name = handle, name
+
+    @classmethod
+    def regex(cls, pattern: str) -> "Grammar":
+        g = C.c_void_p()
+        err = C.create_string_buffer(256)
+        rc = load_library().pgs_grammar_regex(pattern.encode("latin-1"), C.byref(g), err, 256)
+        if rc != 0:
+            raise ValueError(err.value.decode())
+        return cls(g, "regex")
+
+    @classmethod
+    def json(cls) -> "Grammar":
+        g = C.c_void_p()
+        load_library().pgs_grammar_json(C.byref(g))
+        return cls(g, "json")
+
+    def __del__(self):
+        if getattr(self, "_g", None):
+            load_library().pgs_grammar_free(self._g)
+            self._g = None
+
+    @property
+    def n_states(self) -> int:
+        return load_library().pgs_grammar_n_states(self._g)
+
+    def state_info(self, state: int):
+        a = (C.c_uint8 * 256)()
+        c, d = C.c_int(0), C.c_int(0)
+        rc = load_library().pgs_grammar_state_info(self._g, state, a, C.byref(c), C.byref(d))
+        if rc != 0:
+            raise SamplerError(rc, "bad grammar state")
+        return bytes(b for b in range(256) if a[b]), bool(c.value), bool(d.value)
+
+    def build_table(self, vocab: int, first_byte_id: int = 3):
+        """(words [n_states, ceil(vocab/32)] uint32, flags [n_states] uint8) for upload_mask_table."""
+        n = self.n_states
+        words = np.zeros((n, (vocab + 31) // 32), dtype=np.uint32)
+        flags = np.zeros(n, dtype=np.uint8)
+        rc = load_library().pgs_grammar_build_table(self._g, vocab, first_byte_id, words.ctypes.data, flags.ctypes.data)
+        if rc != 0:
+            raise SamplerError(rc, "pgs_grammar_build_table failed")
+        return words, flags
+
+    def new_state(self) -> GrammarState:
+        return GrammarState(self)
 
 
 class Sampler:
@@ -274,6 +396,75 @@ class Sampler:
         d._keep = keep
         return d
 
+    @staticmethod
+    def _stream(stream_ptr):
+        """None = the handle's own stream.  torch reports its default stream as 0, which the C ABI
+        reads as "the handle's stream", so 0 is translated to CUDA's legacy-default-stream handle."""
+        if stream_ptr is None:
+            return None
+        return stream_ptr if stream_ptr else 1   # cudaStreamLegacy
+
     def launch_device(self, desc, stream_ptr: Optional[int] = None):
         """Enqueue one step without waiting (pgs_sample_batch_async)."""
-        self._check(self._lib.pgs_sample_batch_async(self._h, C.byref(desc), stream_ptr))
+        self._check(self._lib.pgs_sample_batch_async(self._h, C.byref(desc), self._stream(stream_ptr)))
+
+    # ------------------------------------------------------------ vocabulary-sharded sampling
+    def tp_record_bytes(self, cand: int) -> int:
+        return self._lib.pgs_tp_record_bytes(cand)
+
+    def _tp_desc(self, rows, vocab, n_shards, rank, cand, logits=None, temperature=None, top_p=None, uniform=None):
+        d = TpDesc()
+        d.struct_size = C.sizeof(TpDesc)
+        d.rows, d.vocab, d.n_shards, d.shard_rank, d.cand = rows, vocab, n_shards, rank, cand
+        if logits is not None:
+            assert logits.is_cuda and logits.stride(1) == 1
+            d.row_stride, d.logits = logits.stride(0), logits.data_ptr()
+        else:
+            d.row_stride = vocab // n_shards
+        d.temperature = None if temperature is None else temperature.data_ptr()
+        d.top_p = None if top_p is None else top_p.data_ptr()
+        d.uniform = None if uniform is None else uniform.data_ptr()
+        return d
+
+    def tp_partial(self, shard_logits, vocab, n_shards, rank, cand, temperature=None, records=None, stream_ptr=None):
+        """Emit this rank's per-row records (uint8 CUDA tensor [rows, record_bytes]) for its column
+        shard `shard_logits` [rows, vocab // n_shards] (float32, CUDA)."""
+        import torch
+        rows = shard_logits.shape[0]
+        if records is None:
+            records = torch.empty((rows, self.tp_record_bytes(cand)), dtype=torch.uint8, device=shard_logits.device)
+        d = self._tp_desc(rows, vocab, n_shards, rank, cand, shard_logits, temperature)
+        self._check(self._lib.pgs_tp_partial(self._h, C.byref(d), records.data_ptr(), self._stream(stream_ptr)))
+        return records
+
+    def tp_merge(self, records_all, vocab, n_shards, rank, cand, temperature=None, top_p=None, uniform=None,
+                 stream_ptr=None):
+        """Merge the all-gathered records [n_shards, rows, record_bytes] into tokens; returns a dict of
+        CUDA tensors (token, status, drew, argmax, gmax, gsum, total, n_kept)."""
+        import torch
+        rows = records_all.shape[1]
+        dev = records_all.device
+        out = dict(token=torch.zeros(rows, dtype=torch.int32, device=dev),
+                   status=torch.full((rows,), -1, dtype=torch.int32, device=dev),
+                   drew=torch.zeros(rows, dtype=torch.uint8, device=dev),
+                   argmax=torch.zeros(rows, dtype=torch.int32, device=dev),
+                   gmax=torch.zeros(rows, dtype=torch.float32, device=dev),
+                   gsum=torch.zeros(rows, dtype=torch.float32, device=dev),
+                   total=torch.zeros(rows, dtype=torch.float32, device=dev),
+                   n_kept=torch.zeros(rows, dtype=torch.int32, device=dev))
+        o = TpOut(**{k: v.data_ptr() for k, v in out.items()})
+        d = self._tp_desc(rows, vocab, n_shards, rank, cand, None, temperature, top_p, uniform)
+        self._check(self._lib.pgs_tp_merge(self._h, C.byref(d), records_all.data_ptr(), C.byref(o),
+                                           self._stream(stream_ptr)))
+        return out
+
+    def draft_accept(self, row_argmax, draft, stream_ptr=None):
+        """row_argmax, draft: int32 CUDA tensors [sequences, positions] -> (accepted, next)."""
+        import torch
+        seqs, pos = row_argmax.shape
+        acc = torch.zeros(seqs, dtype=torch.int32, device=row_argmax.device)
+        nxt = torch.zeros(seqs, dtype=torch.int32, device=row_argmax.device)
+        self._check(self._lib.pgs_draft_accept(self._h, row_argmax.contiguous().data_ptr(),
+                                               draft.contiguous().data_ptr(), seqs, pos, acc.data_ptr(),
+                                               nxt.data_ptr(), self._stream(stream_ptr)))
+        return acc, nxt

@@ -161,7 +161,7 @@ __global__ void __launch_bounds__(NT, 1) tp_merge_kernel(const TpArgs a, const T
                 if (!have || h->m > best) { best = h->m; amax = h->argmax; have = true; }
                 S = fadd(S, fmul(h->s, pgs_expf_tab(fdiv(fsub(h->m, M), t), sm.fin.exp_tab)));
             }
-            n += h->n;
+            n += min(h->n, a.cand);   // a record can never hold more than `cand` entries
         }
         sm.M = M; sm.S = S; sm.amax = amax; sm.n = n; sm.fault = fault;
     }
@@ -176,8 +176,9 @@ __global__ void __launch_bounds__(NT, 1) tp_merge_kernel(const TpArgs a, const T
         const TpRecHead* h = rec(r);
         const float* rx = reinterpret_cast<const float*>(h + 1);
         const uint32_t* rid = reinterpret_cast<const uint32_t*>(rx + a.cand);
-        for (uint32_t j = tid; j < h->n; j += NT) { sm.cx[off + j] = rx[j]; sm.cid[off + j] = rid[j]; }
-        off += h->n;
+        const uint32_t hn = min(h->n, a.cand);
+        for (uint32_t j = tid; j < hn; j += NT) { sm.cx[off + j] = rx[j]; sm.cid[off + j] = rid[j]; }
+        off += hn;
     }
     __syncthreads();
     const bool any = finite_f(sm.M);
