@@ -24,9 +24,10 @@ def all_gather_records(local: torch.Tensor, group=None) -> torch.Tensor:
     """[rows, record_bytes] uint8 per rank -> [world, rows, record_bytes] on every rank (NCCL
     all-gather over NVLink on GPUs).  The merge kernel reads shard r at index r."""
     world = dist.get_world_size(group)
-    out = torch.empty((world,) + tuple(local.shape), dtype=local.dtype, device=local.device)
-    dist.all_gather_into_tensor(out, local.contiguous(), group=group)
-    return out
+    local = local.contiguous()
+    out = torch.empty((world * local.shape[0],) + tuple(local.shape[1:]), dtype=local.dtype, device=local.device)
+    dist.all_gather_into_tensor(out, local, group=group)
+    return out.view((world,) + tuple(local.shape))
 
 
 def max_over_ranks(value: float, device, group=None) -> float:
