@@ -156,6 +156,22 @@ PGS_API int pgs_sample_batch(pgs_handle *h, const pgs_batch_desc *desc);
  * without waiting.  Every array must be device memory. */
 PGS_API int pgs_sample_batch_async(pgs_handle *h, const pgs_batch_desc *desc, void *cuda_stream);
 
+/* Allocation-free variant of pgs_sample_batch_async.  It has no counterpart in the reference
+ * (whose sampler works on host vectors and never touches device memory); it exists for callers
+ * that may not allocate device memory once they are running -- a server whose memory pool owns
+ * the whole GPU, a plugin inside a runtime that forbids allocation after start-up.  It needs no
+ * handle and calls no allocator: the rows' working storage is a fixed array inside the library
+ * (about 10.6 MB on every GPU that loads it).  Limits: vocab <= 65536, at most 1024 history ids
+ * per row (longer rows report PGS_ROW_BAD_PARAM), no grammar tables, every array of the
+ * descriptor in device memory; beyond them the call fails with PGS_ERR_LIMIT / PGS_ERR_INVALID
+ * and a message in pgs_static_last_error().  Results are those of the general (bit-exact)
+ * kernel.  All calls on one device share the array: calls whose kernels may overlap on the GPU
+ * (different streams or host threads) race and must be serialised by the caller.  The first
+ * call on each device does a one-time set-up and should be made outside any stream capture.
+ * Only enqueues work on `cuda_stream` (a cudaStream_t; NULL = the default stream). */
+PGS_API int pgs_sample_batch_static(int device_ordinal, const pgs_batch_desc *desc, void *cuda_stream);
+PGS_API const char *pgs_static_last_error(void);
+
 /* Fidelity switch.  By default rows run in the fused kernel: every decision follows the
  * reference, candidate probabilities use the exact expf, and the f32 left-fold sum of
  * temperature_softmax (sampler.rs:99-113) agrees with the reference's to about 1e-6 relative,

@@ -20,6 +20,7 @@ ROW_OK, ROW_NONFINITE, ROW_DEAD, ROW_EMPTY, ROW_BAD_PARAM = 0, 1, 2, 3, 4
 
 EXPORTS = ["pgs_create", "pgs_destroy", "pgs_last_error", "pgs_mask_table_upload", "pgs_mask_table_free",
            "pgs_sample_batch", "pgs_sample_batch_async", "pgs_get_counters", "pgs_stream", "pgs_set_exact",
+           "pgs_sample_batch_static", "pgs_static_last_error",
            "pgs_grammar_regex", "pgs_grammar_json", "pgs_grammar_free", "pgs_grammar_n_states",
            "pgs_grammar_build_table", "pgs_grammar_state_new", "pgs_grammar_state_reset", "pgs_grammar_state_free",
            "pgs_grammar_advance", "pgs_grammar_mask_state", "pgs_grammar_state_info",
@@ -92,6 +93,8 @@ def load_library():
     L.pgs_sample_batch_async.argtypes = [C.c_void_p, C.POINTER(BatchDesc), C.c_void_p]
     L.pgs_get_counters.argtypes = [C.c_void_p, C.POINTER(Counters)]
     L.pgs_set_exact.argtypes = [C.c_void_p, C.c_int]
+    L.pgs_sample_batch_static.argtypes = [C.c_int, C.POINTER(BatchDesc), C.c_void_p]
+    L.pgs_static_last_error.restype = C.c_char_p
     L.pgs_grammar_regex.argtypes = [C.c_char_p, C.POINTER(C.c_void_p), C.c_char_p, C.c_size_t]
     L.pgs_grammar_json.argtypes = [C.POINTER(C.c_void_p)]
     L.pgs_grammar_free.argtypes = [C.c_void_p]
@@ -139,6 +142,15 @@ class BatchResult:
     def kept(self, row: int):
         n = min(int(self.n_kept[row]), self.dump_ids.shape[1])
         return self.dump_ids[row, :n], self.dump_probs[row, :n]
+
+
+def sample_batch_static(device: int, desc: "BatchDesc", stream_ptr: Optional[int] = None):
+    """pgs_sample_batch_static: the allocation-free entry point (fixed in-library working storage,
+    no handle).  `desc` is a device-resident descriptor as built by Sampler.make_device_desc."""
+    L = load_library()
+    rc = L.pgs_sample_batch_static(device, C.byref(desc), Sampler._stream(stream_ptr))
+    if rc != 0:
+        raise SamplerError(rc, L.pgs_static_last_error().decode())
 
 
 class GrammarState:

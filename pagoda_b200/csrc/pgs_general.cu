@@ -305,3 +305,114 @@ cudaError_t launch_general(const RowArgs& a, uint32_t grid, cudaStream_t stream)
 }
 
 }  // namespace pgs
+
+// ------------------------------------------------------------------------------------------
+// Entry point for callers that cannot allocate device memory.
+//
+// Some hosts of this library may not call cudaMalloc at all: a serving process whose memory
+// pool already owns the whole device, a plugin loaded into a runtime that forbids allocation
+// after start-up, or code that runs where an allocation would synchronise the device at the
+// wrong moment.  pgs_sample_batch_static runs the general row kernel above with its per-row
+// working storage placed in the fixed array below instead of in buffers owned by a handle, so
+// it needs no handle and performs no allocation of any kind (no cudaMalloc / cudaFree, no
+// library call that allocates).  The price is a fixed capacity and shared storage:
+//   - vocab <= PGS_STATIC_MAX_VOCAB, at most PGS_STATIC_MAX_HISTORY history ids per row (longer
+//     rows get PGS_ROW_BAD_PARAM), no grammar tables, every array in device memory;
+//   - the array belongs to the device, not to the call: every call on that device uses the same
+//     storage and leaves its last rows' working data behind.  Nothing in it has to start at zero
+//     (each row rewrites every part of its slot before reading it), but two calls whose kernels
+//     overlap on the GPU -- different streams, or different host threads -- race on it;
+//   - every GPU that loads the library holds the array (about 10.6 MB) until the process exits.
+// The first call on a device looks up the array's device address and raises the kernel's
+// shared-memory limit; make that first call outside of any stream capture.
+#include <stdio.h>
+#include <string.h>
+
+#include "../../include/pagoda_sampler.h"
+
+namespace pgs {
+
+constexpr uint32_t STATIC_SLOTS = 8;            // rows in flight
+constexpr uint32_t STATIC_MAX_VOCAB = 65536;
+constexpr uint32_t STATIC_MAX_HISTORY = 1024;
+constexpr uint32_t STATIC_HASH_CAP = 2048;      // >= 2 * STATIC_MAX_HISTORY, power of two
+constexpr size_t STATIC_BYTES = (size_t)STATIC_SLOTS * STATIC_MAX_VOCAB * (4 + 4 + 4 + 8) +
+                                (size_t)STATIC_SLOTS * STATIC_HASH_CAP * 8;
+
+// In host code this name is only a handle for cudaGetSymbolAddress, never a device pointer.
+static __device__ __align__(256) unsigned char g_static_scratch[STATIC_BYTES];
+
+static void* g_static_addr[64];                 // device address of the array, per device ordinal
+static thread_local char g_static_error[256] = "";
+
+static int static_fail(int code, const char* what, cudaError_t e) {
+    snprintf(g_static_error, sizeof g_static_error, "%s%s%s", what, e == cudaSuccess ? "" : ": ",
+             e == cudaSuccess ? "" : cudaGetErrorString(e));
+    return code;
+}
+
+}  // namespace pgs
+
+extern "C" const char* pgs_static_last_error(void) {
+    return pgs::g_static_error;
+}
+
+extern "C" int pgs_sample_batch_static(int device, const pgs_batch_desc* desc_ptr, void* cuda_stream) {
+    using namespace pgs;
+    const pgs_batch_desc* d = desc_ptr;
+    if (!d || d->struct_size != sizeof(pgs_batch_desc)) return static_fail(-1, "pgs_sample_batch_static: bad descriptor size", cudaSuccess);
+    if (device < 0 || device >= 64) return static_fail(-1, "pgs_sample_batch_static: device ordinal out of range", cudaSuccess);
+    if (d->rows == 0) return 0;
+    if (d->vocab == 0 || d->vocab > STATIC_MAX_VOCAB)
+        return static_fail(-4, "pgs_sample_batch_static: vocab exceeds the static capacity of 65536", cudaSuccess);
+    if (!d->logits || !d->token || !d->status || d->row_stride < d->vocab || d->logits_dtype > 1)
+        return static_fail(-1, "pgs_sample_batch_static: logits, token, status required; row_stride >= vocab", cudaSuccess);
+    if (d->logits_mem != 0 || d->aux_mem != 0)
+        return static_fail(-1, "pgs_sample_batch_static: every array must be device memory (staging would allocate)",
+                           cudaSuccess);
+    if (d->mask_table || d->mask_state)
+        return static_fail(-1, "pgs_sample_batch_static: grammar tables belong to a handle and are not supported here",
+                           cudaSuccess);
+    if ((d->dump_ids || d->dump_probs) && d->dump_cap == 0)
+        return static_fail(-1, "pgs_sample_batch_static: dump arrays given with dump_cap == 0", cudaSuccess);
+    int prev = -1;
+    cudaError_t e = cudaGetDevice(&prev);
+    if (e != cudaSuccess) return static_fail(-2, "cudaGetDevice", e);
+    if (prev != device && (e = cudaSetDevice(device)) != cudaSuccess) return static_fail(-2, "cudaSetDevice", e);
+    int rc = 0;
+    if (!g_static_addr[device]) {   // set-up, once per device, with that device current
+        void* p = nullptr;
+        e = cudaGetSymbolAddress(&p, g_static_scratch);
+        if (e == cudaSuccess) e = configure_general();
+        if (e != cudaSuccess) rc = static_fail(-2, "pgs_sample_batch_static set-up", e);
+        else g_static_addr[device] = p;
+    }
+    if (rc == 0) {
+        unsigned char* base = static_cast<unsigned char*>(g_static_addr[device]);
+        const size_t per = (size_t)STATIC_SLOTS * STATIC_MAX_VOCAB;
+        RowArgs a;
+        memset(&a, 0, sizeof a);
+        a.logits = d->logits; a.dtype = d->logits_dtype; a.rows = d->rows; a.vocab = d->vocab;
+        a.row_stride = d->row_stride;
+        a.temperature = d->temperature; a.top_k = d->top_k; a.top_p = d->top_p;
+        a.freq = d->frequency_penalty; a.pres = d->presence_penalty; a.rep = d->repetition_penalty;
+        a.hist_offsets = d->hist_offsets; a.hist_ids = d->hist_ids;
+        a.eos = d->eos_token_id; a.uniform = d->uniform;
+        a.token = d->token; a.status = d->status; a.drew = d->drew; a.argmax = d->argmax; a.row_max = d->row_max;
+        a.sumexp = d->sumexp; a.total = d->total; a.n_kept = d->n_kept;
+        a.dump_cap = d->dump_cap; a.dump_ids = d->dump_ids; a.dump_probs = d->dump_probs;
+        a.sx = reinterpret_cast<float*>(base);
+        a.sl_id = reinterpret_cast<uint32_t*>(base + per * 4);
+        a.sl_p = reinterpret_cast<float*>(base + per * 8);
+        a.sl_key = reinterpret_cast<unsigned long long*>(base + per * 12);
+        a.sh_key = reinterpret_cast<uint32_t*>(base + per * 20);
+        a.sh_cnt = reinterpret_cast<uint32_t*>(base + per * 20 + (size_t)STATIC_SLOTS * STATIC_HASH_CAP * 4);
+        a.vocab_pad = STATIC_MAX_VOCAB; a.sort_pad = STATIC_MAX_VOCAB; a.hash_cap = STATIC_HASH_CAP;
+        a.max_history = STATIC_MAX_HISTORY;
+        const uint32_t grid = d->rows < STATIC_SLOTS ? d->rows : STATIC_SLOTS;
+        e = launch_general(a, grid, static_cast<cudaStream_t>(cuda_stream));
+        if (e != cudaSuccess) rc = static_fail(-2, "pgs_sample_batch_static launch", e);
+    }
+    if (prev != device && prev >= 0) cudaSetDevice(prev);
+    return rc;
+}
