@@ -513,7 +513,9 @@ __global__ void __launch_bounds__(NT, 1) fused_row_kernel(const RowArgs a, const
         __syncthreads();
         // ---- one pass in chunk order: collect the candidates, then overwrite each logit with its
         //      softmax numerator (hardware exp2) and accumulate the plain chunk sum
-        const float scale = 1.4426950408889634f / t;
+        // log2(e) / t as a two-float sum, so that the exponent's argument carries no systematic error
+        const double scale_d = 1.4426950408889634 / (double)t;
+        const float s_hi = (float)scale_d, s_lo = (float)(scale_d - (double)s_hi);
         const uint32_t L = fl.chunk;
         const uint32_t c0 = min(len, tid * L), c1 = min(len, c0 + L);
         float csum = 0.0f;
@@ -523,7 +525,13 @@ __global__ void __launch_bounds__(NT, 1) fused_row_kernel(const RowArgs a, const
                 const uint32_t at = atomicAdd(&sm.cand_n, 1u);
                 if (at < (uint32_t)F_LCAP) { sm.cand_id[at] = lo + i; sm.cand_x[at] = x; }
             }
-            const float e = ex2_approx((x - m) * scale);   // masked entries are -inf: 2^-inf = +0
+            // 2^(p + r) with p + r = (x - m) * log2(e) / t: hardware exp2 of p, first-order term for r;
+            // below 2^-160 (and for masked entries, which are -inf) the numerator is +0
+            const float a_ = fsub(x, m);
+            const float p_ = fmul(a_, s_hi);
+            const float r_ = __fmaf_rn(a_, s_lo, __fmaf_rn(a_, s_hi, -p_));
+            float e = ex2_approx(p_);
+            e = p_ < -160.0f ? 0.0f : __fmaf_rn(e, r_ * 0.69314718f, e);
             X[i] = e;
             csum += e;
         }

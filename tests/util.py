@@ -66,6 +66,9 @@ def assert_close(got, want, name="", min_clear=0.9):
     np.testing.assert_array_equal(got.argmax[live], want["argmax"][live], err_msg=f"{name}: argmax")
     np.testing.assert_array_equal(got.row_max[live].view(np.uint32), want["row_max"][live].view(np.uint32),
                                   err_msg=f"{name}: row_max")
+    with np.errstate(divide="ignore", invalid="ignore"):
+        rel = np.abs(got.sumexp[live] - want["sumexp"][live]) / np.abs(want["sumexp"][live])
+    print(f"[{name}] fused sumexp max relative error {np.nanmax(rel) if rel.size else 0:.3g}")
     np.testing.assert_allclose(got.sumexp[live], want["sumexp"][live], rtol=TOL, atol=0, err_msg=f"{name}: sumexp")
     np.testing.assert_allclose(got.total[live], want["total"][live], rtol=TOL, atol=0, err_msg=f"{name}: total")
     np.testing.assert_array_equal(got.drew.astype(np.int32), want["drew"], err_msg=f"{name}: drew")
