@@ -216,6 +216,16 @@ PGS_API int pgs_draft_accept(pgs_handle *h, const uint32_t *row_argmax, const ui
                              uint32_t sequences, uint32_t positions, uint32_t *accepted,
                              uint32_t *next, void *cuda_stream);
 
+/* Replaces sampler::log_softmax + the gather of Engine::score (sampler.rs:73-87,
+ * engine.rs:1066-1090): per row out = ln(exp(x - max)) - max(ln(sum), f32::MIN_POSITIVE) with the
+ * reference's f32 left-fold sum.  `ids` (one token id per row) selects what out_gather[row]
+ * receives; out_full ([rows x vocab], may be NULL) receives the whole vector.  Device pointers;
+ * only enqueues work on `cuda_stream` (NULL = the handle's stream).  Rows holding a non-finite
+ * logit get status PGS_ROW_NONFINITE and NaN. */
+PGS_API int pgs_log_softmax(pgs_handle *h, const float *logits, uint32_t rows, uint32_t vocab,
+                            uint64_t row_stride, const uint32_t *ids, float *out_gather, float *out_full,
+                            int32_t *status, void *cuda_stream);
+
 /* Counters since creation (for the engine's /stats): rows sampled, rows faulted, algorithmic
  * bytes touched. */
 typedef struct pgs_counters {

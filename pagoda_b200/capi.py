@@ -24,7 +24,7 @@ EXPORTS = ["pgs_create", "pgs_destroy", "pgs_last_error", "pgs_mask_table_upload
            "pgs_grammar_regex", "pgs_grammar_json", "pgs_grammar_free", "pgs_grammar_n_states",
            "pgs_grammar_build_table", "pgs_grammar_state_new", "pgs_grammar_state_reset", "pgs_grammar_state_free",
            "pgs_grammar_advance", "pgs_grammar_mask_state", "pgs_grammar_state_info",
-           "pgs_tp_record_bytes", "pgs_tp_partial", "pgs_tp_merge", "pgs_draft_accept"]
+           "pgs_log_softmax", "pgs_tp_record_bytes", "pgs_tp_partial", "pgs_tp_merge", "pgs_draft_accept"]
 
 
 class SamplerError(RuntimeError):
@@ -110,6 +110,8 @@ def load_library():
     L.pgs_grammar_mask_state.argtypes = [C.c_void_p, C.c_void_p]
     L.pgs_grammar_mask_state.restype = C.c_uint32
     L.pgs_grammar_state_info.argtypes = [C.c_void_p, C.c_uint32, C.c_void_p, C.POINTER(C.c_int), C.POINTER(C.c_int)]
+    L.pgs_log_softmax.argtypes = [C.c_void_p, C.c_void_p, C.c_uint32, C.c_uint32, C.c_uint64, C.c_void_p, C.c_void_p,
+                                  C.c_void_p, C.c_void_p, C.c_void_p]
     L.pgs_tp_record_bytes.restype = C.c_size_t
     L.pgs_tp_record_bytes.argtypes = [C.c_uint32]
     L.pgs_tp_partial.argtypes = [C.c_void_p, C.POINTER(TpDesc), C.c_void_p, C.c_void_p]
@@ -480,3 +482,19 @@ class Sampler:
                                                draft.contiguous().data_ptr(), seqs, pos, acc.data_ptr(),
                                                nxt.data_ptr(), self._stream(stream_ptr)))
         return acc, nxt
+
+    # ------------------------------------------------------------------------------ scoring
+    def log_softmax(self, logits, ids=None, full=False, stream_ptr=None):
+        """`sampler::log_softmax` on a CUDA float32 tensor [rows, vocab]; returns (gathered [rows] or
+        None, full [rows, vocab] or None, status [rows])."""
+        import torch
+        rows, vocab = logits.shape
+        dev = logits.device
+        gathered = torch.empty(rows, dtype=torch.float32, device=dev) if ids is not None else None
+        out_full = torch.empty((rows, vocab), dtype=torch.float32, device=dev) if full else None
+        status = torch.zeros(rows, dtype=torch.int32, device=dev)
+        self._check(self._lib.pgs_log_softmax(
+            self._h, logits.data_ptr(), rows, vocab, logits.stride(0), None if ids is None else ids.data_ptr(),
+            None if gathered is None else gathered.data_ptr(), None if out_full is None else out_full.data_ptr(),
+            status.data_ptr(), self._stream(stream_ptr)))
+        return gathered, out_full, status

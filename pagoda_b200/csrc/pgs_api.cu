@@ -39,6 +39,17 @@ struct TpOut {
     uint32_t* token; int32_t* status; uint8_t* drew; uint32_t* argmax;
     float* gmax; float* gsum; float* total; uint32_t* n_kept;
 };
+struct ScoreArgs {
+    const float* logits;
+    unsigned long long row_stride;
+    uint32_t rows, vocab;
+    const uint32_t* ids;
+    float* out_gather;
+    float* out_full;
+    int32_t* status;
+};
+cudaError_t configure_score();
+cudaError_t launch_log_softmax(const ScoreArgs& a, uint32_t grid, cudaStream_t stream);
 cudaError_t configure_tp();
 cudaError_t launch_tp_partial(const TpArgs& a, uint32_t grid, cudaStream_t stream);
 cudaError_t launch_tp_merge(const TpArgs& a, const TpOut& o, cudaStream_t stream);
@@ -178,6 +189,7 @@ extern "C" int pgs_create(int device, uint32_t max_rows, uint32_t max_vocab, uin
         PGS_CUDA(nullptr, pgs::configure_fused(h->smem_optin));
         PGS_CUDA(nullptr, pgs::configure_finish());
         PGS_CUDA(nullptr, pgs::configure_tp());
+        PGS_CUDA(nullptr, pgs::configure_score());
         PGS_CUDA(nullptr, cudaMalloc(&h->recs, (size_t)max_rows * sizeof(pgs::RowRec)));
         PGS_CUDA(nullptr, cudaMemsetAsync(h->recs, 0, (size_t)max_rows * sizeof(pgs::RowRec), h->stream));
         PGS_CUDA(nullptr, cudaMalloc(&h->cand_id, (size_t)max_rows * pgs::F_MCAP * sizeof(uint32_t)));
@@ -593,6 +605,23 @@ extern "C" int pgs_draft_accept(pgs_handle* h, const uint32_t* row_argmax, const
     DeviceGuard g(h->device);
     PGS_CUDA(h, pgs::launch_draft_accept(row_argmax, draft, sequences, positions, accepted, next,
                                          cuda_stream ? (cudaStream_t)cuda_stream : h->stream));
+    h->counters.kernel_launches += 1;
+    return PGS_OK;
+}
+
+// ------------------------------------------------------------------------------ scoring
+
+extern "C" int pgs_log_softmax(pgs_handle* h, const float* logits, uint32_t rows, uint32_t vocab, uint64_t row_stride,
+                               const uint32_t* ids, float* out_gather, float* out_full, int32_t* status,
+                               void* cuda_stream) {
+    if (!h) return PGS_ERR_INVALID;
+    if (!logits || vocab == 0 || row_stride < vocab || (!out_full && !(ids && out_gather)))
+        return fail(h, PGS_ERR_INVALID, "pgs_log_softmax: need logits, row_stride >= vocab and an output");
+    if (rows == 0) return PGS_OK;
+    DeviceGuard g(h->device);
+    pgs::ScoreArgs a{logits, row_stride, rows, vocab, ids, out_gather, out_full, status};
+    const uint32_t grid = rows < (uint32_t)h->sm_count ? rows : (uint32_t)h->sm_count;
+    PGS_CUDA(h, pgs::launch_log_softmax(a, grid, cuda_stream ? (cudaStream_t)cuda_stream : h->stream));
     h->counters.kernel_launches += 1;
     return PGS_OK;
 }
