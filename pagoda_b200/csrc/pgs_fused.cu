@@ -72,6 +72,21 @@ struct FusedSmem {
         }                                                           \
     } while (0)
 
+// block sum of one double per thread
+__device__ __forceinline__ double block_sum_f64(double v, double* ws /*NW+1*/) {
+    for (int o = 16; o; o >>= 1) v += __shfl_xor_sync(FULL, v, o);
+    __syncthreads();
+    if ((threadIdx.x & 31) == 0) ws[threadIdx.x >> 5] = v;
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        double w = ws[threadIdx.x];
+        for (int o = 16; o; o >>= 1) w += __shfl_xor_sync(FULL, w, o);
+        if (threadIdx.x == 0) ws[NW] = w;
+    }
+    __syncthreads();
+    return ws[NW];
+}
+
 // exclusive scan of one double per thread; *total = block sum
 __device__ __forceinline__ double block_excl_scan_f64(double v, double* total, double* ws /*NW+1*/) {
     const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
@@ -252,7 +267,8 @@ __global__ void __launch_bounds__(NT, 1) fused_row_kernel(const RowArgs a, const
                 }
             }
             if (body && !poisoned) {
-                if (!mbar_wait(&sm.load_bar, load_phase)) poisoned = true;
+                // one thread polls; the CTA barrier below publishes the landed data to everybody
+                if (tid == 0 && !mbar_wait(&sm.load_bar, load_phase)) poisoned = true;
                 load_phase ^= 1u;
             }
             poisoned = __syncthreads_or(poisoned);
@@ -260,9 +276,11 @@ __global__ void __launch_bounds__(NT, 1) fused_row_kernel(const RowArgs a, const
             if (poisoned) {
                 nonfinite = 2;   // reported as a load timeout after the exchange
             } else {
+                float poison = 0.0f;   // 0 * v is NaN exactly when v is infinite or NaN, and NaN sticks
                 for (uint32_t q = tid; q < nq; q += NT) {
                     float4 v = ((const float4*)X)[q];
-                    nonfinite |= !finite_f(v.x) | !finite_f(v.y) | !finite_f(v.z) | !finite_f(v.w);
+                    poison = __fmaf_rn(v.x, 0.0f, poison); poison = __fmaf_rn(v.y, 0.0f, poison);
+                    poison = __fmaf_rn(v.z, 0.0f, poison); poison = __fmaf_rn(v.w, 0.0f, poison);
                     if (mw) {
                         const uint32_t bits = __ldg(mw + ((lo >> 5) + (q >> 3))) >> ((q & 7) * 4);
                         if (!(bits & 1u)) v.x = -INFINITY;
@@ -273,6 +291,7 @@ __global__ void __launch_bounds__(NT, 1) fused_row_kernel(const RowArgs a, const
                     }
                     tmax = fmaxf(tmax, fmaxf(fmaxf(v.x, v.y), fmaxf(v.z, v.w)));
                 }
+                nonfinite |= poison != poison;
                 for (uint32_t i = nq * 4 + tid; i < len; i += NT) take1(i, __ldcs((const float*)rowp + lo + i));
             }
         } else {
@@ -515,31 +534,33 @@ __global__ void __launch_bounds__(NT, 1) fused_row_kernel(const RowArgs a, const
         //      softmax numerator (hardware exp2) and accumulate the plain chunk sum
         // log2(e) / t as a two-float sum, so that the exponent's argument carries no systematic error
         const double scale_d = 1.4426950408889634 / (double)t;
-        const float s_hi = (float)scale_d, s_lo = (float)(scale_d - (double)s_hi);
+        const float s_hi = (float)scale_d, s_lo2 = (float)((scale_d - (double)(float)scale_d) * 0.6931471805599453);
+        const float cut_f = fmaxf(cut, -3.4e38f);   // masked entries (-inf) are never candidates
         const uint32_t L = fl.chunk;
         const uint32_t c0 = min(len, tid * L), c1 = min(len, c0 + L);
         float csum = 0.0f;
         for (uint32_t i = c0; i < c1; i++) {
             const float x = X[i];
-            if (x >= cut && finite_f(x)) {
+            if (x >= cut_f) {
                 const uint32_t at = atomicAdd(&sm.cand_n, 1u);
                 if (at < (uint32_t)F_LCAP) { sm.cand_id[at] = lo + i; sm.cand_x[at] = x; }
             }
-            // 2^(p + r) with p + r = (x - m) * log2(e) / t: hardware exp2 of p, first-order term for r;
-            // below 2^-160 (and for masked entries, which are -inf) the numerator is +0
-            const float a_ = fsub(x, m);
-            const float p_ = fmul(a_, s_hi);
-            const float r_ = __fmaf_rn(a_, s_lo, __fmaf_rn(a_, s_hi, -p_));
-            float e = ex2_approx(p_);
-            e = p_ < -160.0f ? 0.0f : __fmaf_rn(e, r_ * 0.69314718f, e);
+            // 2^((x - m) * log2(e) / t): hardware exp2 of the product with the rounded scale, times
+            // (1 + ln2 * the part of the scale that rounding dropped), which removes the systematic
+            // error; the clamp keeps masked entries (-inf) finite so that they come out as +0
+            const float a_ = fmaxf(fsub(x, m), -1e30f);
+            const float e2 = ex2_approx(fmul(a_, s_hi));
+            const float e = __fmaf_rn(e2, fmul(a_, s_lo2), e2);
             X[i] = e;
             csum += e;
         }
         __syncthreads();
         const uint32_t my_n = sm.cand_n;
         PGS_TICK(5);   // gather + exp
-        double dtot;
-        const double pre0 = block_excl_scan_f64((double)csum, &dtot, sm.dscan);
+        const float pre0 = block_excl_scan_f32(csum, sm.rs);
+        if (tid == NT - 1) sm.dscan[0] = (double)pre0 + (double)csum;
+        __syncthreads();
+        const double dtot = sm.dscan[0];
         PGS_TICK(6);   // scan
         // ------------------------------------------------ cluster exchange #2
         for (uint32_t r = tid; r < C; r += NT) {
@@ -568,28 +589,30 @@ __global__ void __launch_bounds__(NT, 1) fused_row_kernel(const RowArgs a, const
             fl.cand_x[(size_t)row * F_MCAP + cand_off + j] = sm.cand_x[j];
         }
         // ---------- the sequential fold, chunk by chunk: first from the plain prefix sums ...
-        const float start0 = (float)(before0 + pre0);
+        const float start0 = (float)before0 + pre0;
         float acc = start0;
         for (uint32_t i = c0; i < c1; i++) acc = fadd(acc, X[i]);
-        double inc1 = (double)acc - (double)start0;
-        double tot1;
-        const double pre1 = block_excl_scan_f64(inc1, &tot1, sm.dscan);
+        const float inc1 = fsub(acc, start0);   // exact: both ends lie within a factor two or the chunk is re-folded
+        const float pre1 = block_excl_scan_f32(inc1, sm.rs);
+        __syncthreads();
+        if (tid == NT - 1) sm.dscan[0] = (double)pre1 + (double)inc1;
+        __syncthreads();
+        const double tot1 = sm.dscan[0];
         PGS_TICK(8);   // fold 1
         for (uint32_t r = tid; r < C; r += NT) cluster.map_shared_rank(&sm, r)->xchg[pbuf].fold1[rank] = tot1;
         cluster.sync();   // exchange #3
         double before1 = 0.0;
         for (uint32_t r = 0; r < rank; r++) before1 += xc.fold1[r];
         // ... then once more, for the chunks whose binade that first pass got wrong or crossed
-        const float start1 = (float)(before1 + pre1);
+        const float start1 = (float)before1 + pre1;
         const uint32_t e0 = f2u(start0) & 0x7f800000u;
-        double inc2 = inc1;
+        double inc2 = (double)inc1;
         if ((f2u(start1) & 0x7f800000u) != e0 || (f2u(acc) & 0x7f800000u) != e0) {
             acc = start1;
             for (uint32_t i = c0; i < c1; i++) acc = fadd(acc, X[i]);
             inc2 = (double)acc - (double)start1;
         }
-        double tot2;
-        block_excl_scan_f64(inc2, &tot2, sm.dscan);
+        const double tot2 = block_sum_f64(inc2, sm.dscan);
         if (tid == 0) {
             RowRec& rec = fl.recs[row];
             rec.part[rank] = tot2;
