@@ -401,8 +401,18 @@ __global__ void __launch_bounds__(NT, 1) fused_row_kernel(const RowArgs a, const
             peer->xchg[pbuf].nonfinite[rank] = nonfinite;
             peer->xchg[pbuf].spill[rank] = spill;
         }
+        // material for the top-k bound: the 32*C warp maxima when there are comfortably more warps than
+        // top_k, else all NT*C thread maxima
+        const bool warp_bound = !greedy && 2u * top_k <= C * NW;
         if (!greedy) {
-            for (uint32_t r = 0; r < C; r++) cluster.map_shared_rank(&sm, r)->tmax_all[rank * NT + tid] = tmax;
+            if (warp_bound) {
+                float wmax = tmax;
+                for (int o = 16; o; o >>= 1) wmax = fmaxf(wmax, __shfl_xor_sync(FULL, wmax, o));
+                if ((tid & 31) < (int)C)
+                    cluster.map_shared_rank(&sm, tid & 31)->tmax_all[rank * NW + (tid >> 5)] = wmax;
+            } else {
+                for (uint32_t r = 0; r < C; r++) cluster.map_shared_rank(&sm, r)->tmax_all[rank * NT + tid] = tmax;
+            }
         }
         cluster.sync();
         parity ^= 1u;
@@ -450,7 +460,25 @@ __global__ void __launch_bounds__(NT, 1) fused_row_kernel(const RowArgs a, const
         // from the histogram, and the exact value is picked among that bucket's few members.
         const float t = fmaxf(temp, 1e-9f);
         float cut = -INFINITY;
-        {
+        if (warp_bound) {
+            // k-th largest of the 32*C warp maxima: thread j ranks maximum j against all others
+            const uint32_t nvw = C * NW;
+            if (tid == 0) sm.sel.hist[0] = 0u;
+            __syncthreads();
+            if ((uint32_t)tid < nvw) {
+                const float v = sm.tmax_all[tid];
+                uint32_t gt = 0, ge = 0;
+                for (uint32_t o = 0; o < nvw; o++) { const float u = sm.tmax_all[o]; gt += u > v; ge += u >= v; }
+                if (finite_f(v) && gt < top_k && top_k <= ge) sm.sel.hist[0] = order_key(v);
+            }
+            __syncthreads();
+            const uint32_t kk = sm.sel.hist[0];
+            if (kk) {
+                const float bound = key_to_float(kk);
+                const float delta = 4.8e-7f * (fabsf(m - bound) + 4.0f * t) + 4.8e-7f * (fabsf(bound) + fabsf(m));
+                cut = bound - delta;
+            }
+        } else {
             const uint32_t nv = C * NT;
             uint32_t fin = 0;
             unsigned long long inv_min = 0ull;

@@ -19,9 +19,9 @@ struct RowRec {
     int32_t status;
     float m;              // max over finite processed logits
     float t;              // max(temperature, 1e-9)
-    uint32_t n_parts;     // CTAs that contributed a partial fold
+    uint32_t n_parts;     // warps that contributed a partial fold
     uint32_t pad;
-    double part[F_MAXC];  // per-slice increments of the sequential f32 sum, in slice order
+    double part[F_MAXC * 32];  // per-warp increments of the sequential f32 sum
 };
 
 struct FusedLaunch {
