@@ -57,6 +57,7 @@ cudaError_t launch_draft_accept(const uint32_t* row_argmax, const uint32_t* draf
                                 uint32_t positions, uint32_t* accepted, uint32_t* next, cudaStream_t stream);
 cudaError_t configure_finish();
 cudaError_t launch_finish(const RowArgs& a, const FusedLaunch& fl, cudaStream_t stream);
+cudaError_t launch_finish_small(const RowArgs& a, const FusedLaunch& fl, cudaStream_t stream);
 }  // namespace pgs
 
 static thread_local char g_create_error[256] = "";
@@ -65,6 +66,8 @@ struct pgs_handle {
     int device = 0;
     int sm_count = 0;
     cudaStream_t stream = nullptr;
+    cudaStream_t side = nullptr;      // runs the rarely needed passes beside the main one
+    cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
     uint32_t max_rows = 0, max_vocab = 0, max_history = 0;
     uint32_t slots = 0, vocab_pad = 0, sort_pad = 0, hash_cap = 0;
     // scratch slots
@@ -152,6 +155,9 @@ static int destroy_impl(pgs_handle* h) {
     cudaFree(h->logits_stage); cudaFree(h->aux_dev); cudaFree(h->work_rows); cudaFree(h->work_count); cudaFree(h->prof);
     cudaFree(h->recs); cudaFree(h->cand_id); cudaFree(h->cand_x);
     if (h->aux_host) cudaFreeHost(h->aux_host);
+    if (h->side) { cudaStreamSynchronize(h->side); cudaStreamDestroy(h->side); }
+    if (h->ev_fork) cudaEventDestroy(h->ev_fork);
+    if (h->ev_join) cudaEventDestroy(h->ev_join);
     if (h->stream) cudaStreamDestroy(h->stream);
     delete h;
     return PGS_OK;
@@ -184,6 +190,9 @@ extern "C" int pgs_create(int device, uint32_t max_rows, uint32_t max_vocab, uin
                         device, prop.major, prop.minor);
         h->sm_count = prop.multiProcessorCount;
         PGS_CUDA(nullptr, cudaStreamCreateWithFlags(&h->stream, cudaStreamNonBlocking));
+        PGS_CUDA(nullptr, cudaStreamCreateWithFlags(&h->side, cudaStreamNonBlocking));
+        PGS_CUDA(nullptr, cudaEventCreateWithFlags(&h->ev_fork, cudaEventDisableTiming));
+        PGS_CUDA(nullptr, cudaEventCreateWithFlags(&h->ev_join, cudaEventDisableTiming));
         PGS_CUDA(nullptr, pgs::configure_general());
         h->smem_optin = prop.sharedMemPerBlockOptin;
         PGS_CUDA(nullptr, pgs::configure_fused(h->smem_optin));
@@ -339,12 +348,21 @@ int launch_step(pgs_handle* h, pgs::RowArgs& a, cudaStream_t stream) {
     fl.recs = h->recs; fl.cand_id = h->cand_id; fl.cand_x = h->cand_x;
     const uint32_t nc = rows < h->fused_clusters ? rows : h->fused_clusters;
     PGS_CUDA(h, pgs::launch_fused(a, fl, nc, h->fused_smem, stream));
-    PGS_CUDA(h, pgs::launch_finish(a, fl, stream));
-    a.work_rows = h->work_rows;
-    a.work_count = h->work_count;
+    // Three independent consumers of the fused kernel's output: rows with a short candidate list
+    // (the common case) finish on the caller's stream; rows with a long list and the rows on the
+    // work list are usually none, so those two passes run beside it on a side stream.
+    PGS_CUDA(h, cudaEventRecord(h->ev_fork, stream));
+    PGS_CUDA(h, cudaStreamWaitEvent(h->side, h->ev_fork, 0));
+    PGS_CUDA(h, pgs::launch_finish_small(a, fl, stream));
+    PGS_CUDA(h, pgs::launch_finish(a, fl, h->side));
+    pgs::RowArgs wl = a;
+    wl.work_rows = h->work_rows;
+    wl.work_count = h->work_count;
     // the listed rows are few or none: a small grid keeps the empty pass short
-    PGS_CUDA(h, pgs::launch_general(a, grid < 32u ? grid : 32u, stream));
-    h->counters.kernel_launches += 3;
+    PGS_CUDA(h, pgs::launch_general(wl, grid < 32u ? grid : 32u, h->side));
+    PGS_CUDA(h, cudaEventRecord(h->ev_join, h->side));
+    PGS_CUDA(h, cudaStreamWaitEvent(stream, h->ev_join, 0));
+    h->counters.kernel_launches += 4;
     return PGS_OK;
 }
 

@@ -5,17 +5,128 @@
 
 namespace pgs {
 
+constexpr int FS_NT = 128;   // rows with at most this many candidates take finish_small_kernel
+
 __global__ void __launch_bounds__(NT, 1) finish_kernel(const RowArgs a, const FusedLaunch fl) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     FinishSmem& sm = *reinterpret_cast<FinishSmem*>(smem_raw);
     const uint32_t row = blockIdx.x;
-    if (fl.recs[row].kind != 1u) return;
+    if (fl.recs[row].kind != 1u || fl.recs[row].n_cand <= (uint32_t)FS_NT) return;   // small rows: finish_small_kernel
     const RowRec& rec = fl.recs[row];
     double s2 = 0.0;
     for (uint32_t r = 0; r < rec.n_parts; r++) s2 += rec.part[r];
     finish_row(sm, a, row, a.vocab, fl.cand_id + (size_t)row * F_MCAP, fl.cand_x + (size_t)row * F_MCAP, rec.n_cand,
                rec.m, rec.t, (float)s2, a.top_k ? a.top_k[row] : 0u, a.top_p ? a.top_p[row] : 1.0f,
                a.uniform ? a.uniform[row] : 0.0f, rec.amax, rec.status);
+}
+
+// ---- small rows: at most 128 candidates (top-k 50 leaves about 60).  Four warps per row are enough,
+// every row of the batch is resident at once, and the three exact folds run in one warp by shuffles.
+
+struct FinishSmallSmem {
+    unsigned long long exp_tab[32];
+    uint32_t m_id[FS_NT];
+    float p[FS_NT];
+    uint32_t sid[FS_NT];
+    float sp[FS_NT];
+    float rp[FS_NT];
+    uint32_t rpos[FS_NT];
+    uint32_t n_live;
+    float S;
+};
+
+__global__ void __launch_bounds__(FS_NT) finish_small_kernel(const RowArgs a, const FusedLaunch fl) {
+    __shared__ FinishSmallSmem sm;
+    const int tid = threadIdx.x, lane = tid & 31;
+    const uint32_t row = blockIdx.x;
+    if (fl.recs[row].kind != 1u || fl.recs[row].n_cand > (uint32_t)FS_NT) return;
+    const RowRec& rec = fl.recs[row];
+    const uint32_t n = rec.n_cand, V = a.vocab;
+    const float m = rec.m, t = rec.t;
+    const uint32_t top_k = a.top_k ? a.top_k[row] : 0u;
+    const float top_p = a.top_p ? a.top_p[row] : 1.0f;
+    const float u01 = a.uniform ? a.uniform[row] : 0.0f;
+    if (tid < 32) {
+        sm.exp_tab[tid] = kExp2TableDev[tid];
+        double s2 = 0.0;
+        for (uint32_t r = lane; r < rec.n_parts; r += 32) s2 += rec.part[r];
+        for (int o = 16; o; o >>= 1) s2 += __shfl_xor_sync(FULL, s2, o);
+        if (tid == 0) { sm.S = (float)s2; sm.n_live = 0; }
+    }
+    __syncthreads();
+    const float S = sm.S;
+    const bool norm = S > 1e-9f;
+    if ((uint32_t)tid < n) {
+        sm.m_id[tid] = fl.cand_id[(size_t)row * F_MCAP + tid];
+        const float e = softmax_num(fl.cand_x[(size_t)row * F_MCAP + tid], m, t, sm.exp_tab);   // exact expf
+        sm.p[tid] = norm ? fdiv(e, S) : e;
+    }
+    __syncthreads();
+    if ((uint32_t)tid < n) {   // rank by id and by (probability descending, id ascending)
+        const uint32_t idj = sm.m_id[tid];
+        const float pj = sm.p[tid];
+        uint32_t r_id = 0, r_p = 0;
+        for (uint32_t o = 0; o < n; o++) {
+            const uint32_t ido = sm.m_id[o];
+            const float po = sm.p[o];
+            r_id += ido < idj;
+            r_p += (po > pj) || (po == pj && ido < idj);
+        }
+        sm.sid[r_id] = idj; sm.sp[r_id] = pj; sm.rp[r_p] = pj; sm.rpos[r_p] = r_id;
+    }
+    __syncthreads();
+    if ((uint32_t)tid < n) {   // top-k: every tie at the k-th probability survives; zeros never matter
+        const float thr = (top_k != 0u && top_k <= n) ? sm.rp[top_k - 1] : 0.0f;
+        const bool live = sm.rp[tid] >= thr && sm.rp[tid] > 0.0f;
+        const bool next_live = (uint32_t)tid + 1 < n && sm.rp[tid + 1] >= thr && sm.rp[tid + 1] > 0.0f;
+        if (live && !next_live) sm.n_live = tid + 1;
+    }
+    __syncthreads();
+    if (tid >= 32) return;
+    // one warp: top-p walk in ranked order, then total and inverse-CDF pick in id order
+    const uint32_t n_live = sm.n_live;
+    uint32_t keep = n_live;
+    if (!(top_p >= 1.0f) && n_live > 0) {
+        int found = -1;
+        warp_fold(sm.rp, (int)n_live, SEQ_FIND_GE, top_p, &found);
+        if (found >= 0) keep = (uint32_t)found + 1;
+    }
+    for (uint32_t j = keep + lane; j < n; j += 32) sm.sp[sm.rpos[j]] = 0.0f;
+    __syncwarp();
+    const float total = warp_fold(sm.sp, (int)n, SEQ_SUM, 0.0f, nullptr);
+    int pick = -1;
+    if (total > 1e-9f) warp_fold(sm.sp, (int)n, SEQ_FIND_GT, fmul(u01, total), &pick);
+    if (lane == 0) {
+        uint32_t token = rec.amax;
+        int drew = 0;
+        if (total > 1e-9f) { token = pick >= 0 ? sm.sid[pick] : V - 1; drew = 1; }
+        a.token[row] = token; a.status[row] = rec.status;
+        if (a.drew) a.drew[row] = (uint8_t)drew;
+        if (a.argmax) a.argmax[row] = rec.amax;
+        if (a.row_max) a.row_max[row] = m;
+        if (a.sumexp) a.sumexp[row] = S;
+        if (a.total) a.total[row] = total;
+    }
+    if (a.n_kept || a.dump_ids || a.dump_probs) {   // diagnostics: the kept set in id order
+        uint32_t done = 0;
+        for (uint32_t base = 0; base < n; base += 32) {
+            const uint32_t j = base + lane;
+            const bool kept = j < n && sm.sp[j] > 0.0f;
+            const unsigned mask = __ballot_sync(FULL, kept);
+            const uint32_t at = done + __popc(mask & ((1u << lane) - 1u));
+            if (kept && at < a.dump_cap) {
+                if (a.dump_ids) a.dump_ids[(size_t)row * a.dump_cap + at] = sm.sid[j];
+                if (a.dump_probs) a.dump_probs[(size_t)row * a.dump_cap + at] = sm.sp[j];
+            }
+            done += __popc(mask);
+        }
+        if (lane == 0 && a.n_kept) a.n_kept[row] = done;
+    }
+}
+
+cudaError_t launch_finish_small(const RowArgs& a, const FusedLaunch& fl, cudaStream_t stream) {
+    finish_small_kernel<<<a.rows, FS_NT, 0, stream>>>(a, fl);
+    return cudaGetLastError();
 }
 
 cudaError_t configure_finish() {
