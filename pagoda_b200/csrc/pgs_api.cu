@@ -322,8 +322,11 @@ bool fused_shape(pgs_handle* h, uint32_t vocab) {
         if (smem > h->smem_optin) continue;
         int n = 0;
         if (pgs::fused_max_clusters(c, smem, &n) != cudaSuccess || n <= 0) { cudaGetLastError(); continue; }
-        uint32_t chunk = (slice + 1023u) / 1024u;
-        if ((chunk & 1u) == 0) chunk += 1;   // odd stride: conflict-free shared-memory access
+        // consecutive logits per thread in the sum passes: 4 * odd, so that the 128-bit shared-memory
+        // accesses of a warp (stride = chunk words) fall into distinct bank groups
+        uint32_t groups = ((slice + 1023u) / 1024u + 3u) / 4u;
+        if ((groups & 1u) == 0) groups += 1;
+        const uint32_t chunk = groups * 4u;
         h->fused_cluster = c; h->fused_slice = slice; h->fused_chunk = chunk; h->fused_smem = smem;
         h->fused_clusters = (uint32_t)n;
         return true;

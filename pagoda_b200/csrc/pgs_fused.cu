@@ -564,24 +564,29 @@ __global__ void __launch_bounds__(NT, 1) fused_row_kernel(const RowArgs a, const
         const double scale_d = 1.4426950408889634 / (double)t;
         const float s_hi = (float)scale_d, s_lo2 = (float)((scale_d - (double)(float)scale_d) * 0.6931471805599453);
         const float cut_f = fmaxf(cut, -3.4e38f);   // masked entries (-inf) are never candidates
-        const uint32_t L = fl.chunk;
+        const uint32_t L = fl.chunk;   // 4 * odd: 128-bit shared-memory accesses of a warp do not collide
         const uint32_t c0 = min(len, tid * L), c1 = min(len, c0 + L);
+        const uint32_t c1b = c0 + ((c1 - c0) & ~3u);   // whole 128-bit groups; a remainder only at the ragged end
         float csum = 0.0f;
-        for (uint32_t i = c0; i < c1; i++) {
-            const float x = X[i];
+        // candidate test, then 2^((x - m) * log2(e) / t): hardware exp2 of the product with the rounded
+        // scale, times (1 + ln2 * the part of the scale that rounding dropped), which removes the
+        // systematic error; the clamp keeps masked entries (-inf) finite so that they come out as +0
+        auto numerator = [&](float x, uint32_t i) -> float {
             if (x >= cut_f) {
                 const uint32_t at = atomicAdd(&sm.cand_n, 1u);
                 if (at < (uint32_t)F_LCAP) { sm.cand_id[at] = lo + i; sm.cand_x[at] = x; }
             }
-            // 2^((x - m) * log2(e) / t): hardware exp2 of the product with the rounded scale, times
-            // (1 + ln2 * the part of the scale that rounding dropped), which removes the systematic
-            // error; the clamp keeps masked entries (-inf) finite so that they come out as +0
             const float a_ = fmaxf(fsub(x, m), -1e30f);
             const float e2 = ex2_approx(fmul(a_, s_hi));
-            const float e = __fmaf_rn(e2, fmul(a_, s_lo2), e2);
-            X[i] = e;
-            csum += e;
+            return __fmaf_rn(e2, fmul(a_, s_lo2), e2);
+        };
+        for (uint32_t i = c0; i < c1b; i += 4) {
+            float4 v = *reinterpret_cast<const float4*>(X + i);
+            v.x = numerator(v.x, i); v.y = numerator(v.y, i + 1); v.z = numerator(v.z, i + 2); v.w = numerator(v.w, i + 3);
+            *reinterpret_cast<float4*>(X + i) = v;
+            csum += (v.x + v.y) + (v.z + v.w);
         }
+        for (uint32_t i = c1b; i < c1; i++) { const float e = numerator(X[i], i); X[i] = e; csum += e; }
         __syncthreads();
         const uint32_t my_n = sm.cand_n;
         PGS_TICK(5);   // gather + exp
@@ -618,8 +623,15 @@ __global__ void __launch_bounds__(NT, 1) fused_row_kernel(const RowArgs a, const
         }
         // ---------- the sequential fold, chunk by chunk: first from the plain prefix sums ...
         const float start0 = (float)before0 + pre0;
-        float acc = start0;
-        for (uint32_t i = c0; i < c1; i++) acc = fadd(acc, X[i]);
+        auto fold_chunk = [&](float acc_) -> float {
+            for (uint32_t i = c0; i < c1b; i += 4) {
+                const float4 v = *reinterpret_cast<const float4*>(X + i);
+                acc_ = fadd(fadd(fadd(fadd(acc_, v.x), v.y), v.z), v.w);
+            }
+            for (uint32_t i = c1b; i < c1; i++) acc_ = fadd(acc_, X[i]);
+            return acc_;
+        };
+        float acc = fold_chunk(start0);
         const float inc1 = fsub(acc, start0);   // exact: both ends lie within a factor two or the chunk is re-folded
         const float pre1 = block_excl_scan_f32(inc1, sm.rs);
         __syncthreads();
@@ -636,18 +648,15 @@ __global__ void __launch_bounds__(NT, 1) fused_row_kernel(const RowArgs a, const
         const uint32_t e0 = f2u(start0) & 0x7f800000u;
         double inc2 = (double)inc1;
         if ((f2u(start1) & 0x7f800000u) != e0 || (f2u(acc) & 0x7f800000u) != e0) {
-            acc = start1;
-            for (uint32_t i = c0; i < c1; i++) acc = fadd(acc, X[i]);
+            acc = fold_chunk(start1);
             inc2 = (double)acc - (double)start1;
         }
-        const double tot2 = block_sum_f64(inc2, sm.dscan);
-        if (tid == 0) {
+        for (int o = 16; o; o >>= 1) inc2 += __shfl_xor_sync(FULL, inc2, o);
+        if ((tid & 31) == 0) fl.recs[row].part[rank * NW + (tid >> 5)] = inc2;   // the finish kernel adds the warps up
+        if (writer) {
             RowRec& rec = fl.recs[row];
-            rec.part[rank] = tot2;
-            if (rank == 0) {
-                rec.kind = 1; rec.n_cand = cand_total; rec.amax = amax; rec.status = status;
-                rec.m = m; rec.t = t; rec.n_parts = C;
-            }
+            rec.kind = 1; rec.n_cand = cand_total; rec.amax = amax; rec.status = status;
+            rec.m = m; rec.t = t; rec.n_parts = C * NW;
         }
         PGS_TICK(9);   // fold 2
     }
