@@ -58,7 +58,7 @@ struct FusedSmem {
     uint32_t cand_id[F_LCAP];
     float cand_x[F_LCAP];
     uint32_t cand_n;
-    unsigned long long load_bar;    // mbarrier of the bulk copy that fills the slice
+    unsigned long long load_bar[8]; // one mbarrier per 32 KB piece of the bulk copy that fills the slice
 };
 
 // Optional phase timers (clock64 deltas of thread 0, summed over the rows of each CTA), enabled
@@ -169,7 +169,7 @@ __global__ void __launch_bounds__(NT, 1) fused_row_kernel(const RowArgs a, const
     uint32_t load_phase = 0;        // parity of the next completion of load_bar
     bool poisoned = false;          // a bulk copy never landed: later rows of this CTA report that too
     if (tid == 0) {
-        mbar_init(&sm.load_bar, 1);
+        for (int b = 0; b < 8; b++) mbar_init(&sm.load_bar[b], 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
@@ -226,6 +226,7 @@ __global__ void __launch_bounds__(NT, 1) fused_row_kernel(const RowArgs a, const
         // ------------------------------- load slice: sanity + bitmask AND + per-thread max
         float tmax = -INFINITY;
         int nonfinite = 0;
+        uint32_t tq = 0;   // slice index of the 128-bit group (or, flagged, the tail element) that holds tmax
         sm.redo_max[tid] = 0;
         const uint32_t nq = len / 4;   // 128-bit groups; a ragged tail exists only in the last slice
         auto take4 = [&](uint32_t q, float4 v) {
@@ -237,21 +238,46 @@ __global__ void __launch_bounds__(NT, 1) fused_row_kernel(const RowArgs a, const
                 if (!(bits & 4u)) v.z = -INFINITY;
                 if (!(bits & 8u)) v.w = -INFINITY;
             }
-            tmax = fmaxf(tmax, fmaxf(fmaxf(v.x, v.y), fmaxf(v.z, v.w)));
+            const float m4 = fmaxf(fmaxf(v.x, v.y), fmaxf(v.z, v.w));
+            if (m4 > tmax) { tmax = m4; tq = q * 4; }
             ((float4*)X)[q] = v;
         };
         auto take1 = [&](uint32_t i, float x) {
             nonfinite |= !finite_f(x);
             if (mw && !((__ldg(mw + ((lo + i) >> 5)) >> ((lo + i) & 31)) & 1u)) x = -INFINITY;
-            tmax = fmaxf(tmax, x);
+            if (x > tmax) { tmax = x; tq = i | 0x80000000u; }
             X[i] = x;
         };
+        // history ids of this slice -> id->count table; runs while the copy below is in flight
+        const bool do_fp = !(fabsf(freq) < 1e-6f && fabsf(pres) < 1e-6f);
+        const bool do_pres = fabsf(pres) > 1e-6f;
+        const bool do_rep = rep != 1.0f;
+        const bool pen = nh > 0 && (do_fp || do_rep);
+        int spill = 0;
+        auto index_history = [&]() {
+            for (int s = tid; s < F_HASH; s += NT) { sm.pen.hkey[s] = 0xffffffffu; sm.pen.hcnt[s] = 0u; }
+            __syncthreads();
+            for (uint32_t j = tid; j < nh; j += NT) {
+                const uint32_t id = __ldg(a.hist_ids + h0 + j);
+                if (id < lo || id >= hi) continue;
+                uint32_t s = (id * 2654435761u) >> 21;   // 11 bits
+                bool placed = false;
+                for (int probe = 0; probe < 64; probe++) {
+                    const uint32_t prev = atomicCAS(&sm.pen.hkey[s], 0xffffffffu, id);
+                    if (prev == 0xffffffffu || prev == id) { atomicAdd(&sm.pen.hcnt[s], 1u); placed = true; break; }
+                    s = (s + 1) & (F_HASH - 1);
+                }
+                if (!placed) spill = 1;
+            }
+        };
         if (a.dtype == 0) {
-            // f32 rows: one thread streams the slice into shared memory with bulk asynchronous copies,
-            // everybody then checks / masks / maximises it from there.  The next row's slice is
-            // prefetched into L2 meanwhile, so HBM keeps streaming while this row is processed.
+            // f32 rows: one thread streams the slice into shared memory with bulk asynchronous copies
+            // (32 KB pieces, one mbarrier each); every warp then checks / masks / maximises each piece
+            // as soon as it has landed.  The next row's slice is prefetched into L2 meanwhile, so HBM
+            // keeps streaming while this row is processed.
             const char* gsrc = rowp + (size_t)lo * 4;
             const uint32_t body = nq * 16;
+            const uint32_t n_pieces = (body + TMA_PIECE - 1) / TMA_PIECE;   // <= 8 for any slice that fits
             if (tid == 0) {
                 if (row + n_clusters < a.rows && body) {
                     const char* nxt = (const char*)a.logits + (size_t)(row + n_clusters) * a.row_stride * 4 + (size_t)lo * 4;
@@ -261,23 +287,25 @@ __global__ void __launch_bounds__(NT, 1) fused_row_kernel(const RowArgs a, const
                 }
                 if (body && !poisoned) {
                     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // earlier generic writes to X
-                    mbar_expect_tx(&sm.load_bar, body);
-                    for (uint32_t off = 0; off < body; off += TMA_PIECE)
-                        bulk_g2s((char*)X + off, gsrc + off, min(TMA_PIECE, body - off), &sm.load_bar);
+                    for (uint32_t pc = 0; pc < n_pieces; pc++) {
+                        const uint32_t off = pc * TMA_PIECE, bytes = min(TMA_PIECE, body - off);
+                        mbar_expect_tx(&sm.load_bar[pc], bytes);
+                        bulk_g2s((char*)X + off, gsrc + off, bytes, &sm.load_bar[pc]);
+                    }
                 }
             }
-            if (body && !poisoned) {
-                // one thread polls; the CTA barrier below publishes the landed data to everybody
-                if (tid == 0 && !mbar_wait(&sm.load_bar, load_phase)) poisoned = true;
-                load_phase ^= 1u;
-            }
-            poisoned = __syncthreads_or(poisoned);
-            PGS_TICK(11);  // bulk copy landed
-            if (poisoned) {
-                nonfinite = 2;   // reported as a load timeout after the exchange
-            } else {
-                float poison = 0.0f;   // 0 * v is NaN exactly when v is infinite or NaN, and NaN sticks
-                for (uint32_t q = tid; q < nq; q += NT) {
+            if (pen) index_history();
+            PGS_TICK(11);  // copy issued, history indexed
+            float poison = 0.0f;   // 0 * v is NaN exactly when v is infinite or NaN, and NaN sticks
+            for (uint32_t pc = 0; pc < n_pieces; pc++) {
+                // every warp waits for the piece on its own: one lane polls (bounded), the rest follow
+                int ok = 1;
+                if (!poisoned && (tid & 31) == 0) ok = mbar_wait(&sm.load_bar[pc], load_phase) ? 1 : 0;
+                ok = __shfl_sync(FULL, ok, 0);
+                if (!ok) poisoned = true;
+                if (poisoned) continue;
+                const uint32_t q_end = min(nq, (pc + 1) * (TMA_PIECE / 16));
+                for (uint32_t q = pc * (TMA_PIECE / 16) + tid; q < q_end; q += NT) {
                     float4 v = ((const float4*)X)[q];
                     poison = __fmaf_rn(v.x, 0.0f, poison); poison = __fmaf_rn(v.y, 0.0f, poison);
                     poison = __fmaf_rn(v.z, 0.0f, poison); poison = __fmaf_rn(v.w, 0.0f, poison);
@@ -289,12 +317,17 @@ __global__ void __launch_bounds__(NT, 1) fused_row_kernel(const RowArgs a, const
                         if (!(bits & 8u)) v.w = -INFINITY;
                         ((float4*)X)[q] = v;
                     }
-                    tmax = fmaxf(tmax, fmaxf(fmaxf(v.x, v.y), fmaxf(v.z, v.w)));
+                    const float m4 = fmaxf(fmaxf(v.x, v.y), fmaxf(v.z, v.w));
+                    if (m4 > tmax) { tmax = m4; tq = q * 4; }
                 }
-                nonfinite |= poison != poison;
-                for (uint32_t i = nq * 4 + tid; i < len; i += NT) take1(i, __ldcs((const float*)rowp + lo + i));
             }
+            if (n_pieces) load_phase ^= 1u;
+            if (poisoned) nonfinite = 2;   // reported as a load timeout after the exchange
+            nonfinite |= poison != poison;
+            if (!poisoned)
+                for (uint32_t i = nq * 4 + tid; i < len; i += NT) take1(i, __ldcs((const float*)rowp + lo + i));
         } else {
+            if (pen) index_history();
             const uint2* src = (const uint2*)(rowp) + lo / 4;    // 4 bf16 per 8-byte load
             for (uint32_t q0 = tid; q0 < nq; q0 += 4 * NT) {
                 uint2 r[4];
@@ -317,25 +350,7 @@ __global__ void __launch_bounds__(NT, 1) fused_row_kernel(const RowArgs a, const
         PGS_TICK(0);   // load
 
         // --------------------------------------------------------------- penalties
-        const bool do_fp = !(fabsf(freq) < 1e-6f && fabsf(pres) < 1e-6f);
-        const bool do_pres = fabsf(pres) > 1e-6f;
-        const bool do_rep = rep != 1.0f;
-        int spill = 0;
-        if (nh > 0 && (do_fp || do_rep) && !nonfinite) {
-            for (int s = tid; s < F_HASH; s += NT) { sm.pen.hkey[s] = 0xffffffffu; sm.pen.hcnt[s] = 0u; }
-            __syncthreads();
-            for (uint32_t j = tid; j < nh; j += NT) {
-                const uint32_t id = __ldg(a.hist_ids + h0 + j);
-                if (id < lo || id >= hi) continue;
-                uint32_t s = (id * 2654435761u) >> 21;   // 11 bits
-                bool placed = false;
-                for (int probe = 0; probe < 64; probe++) {
-                    const uint32_t prev = atomicCAS(&sm.pen.hkey[s], 0xffffffffu, id);
-                    if (prev == 0xffffffffu || prev == id) { atomicAdd(&sm.pen.hcnt[s], 1u); placed = true; break; }
-                    s = (s + 1) & (F_HASH - 1);
-                }
-                if (!placed) spill = 1;
-            }
+        if (pen && !nonfinite) {
             spill = __syncthreads_or(spill);
             if (!spill) {
                 for (int s = tid; s < F_HASH; s += NT) {
@@ -366,33 +381,26 @@ __global__ void __launch_bounds__(NT, 1) fused_row_kernel(const RowArgs a, const
             tmax = -INFINITY;
             for (uint32_t q = tid; q < nq; q += NT) {
                 const float4 v = ((const float4*)X)[q];
-                tmax = fmaxf(tmax, fmaxf(fmaxf(v.x, v.y), fmaxf(v.z, v.w)));
+                const float m4 = fmaxf(fmaxf(v.x, v.y), fmaxf(v.z, v.w));
+                if (m4 > tmax) { tmax = m4; tq = q * 4; }
             }
-            for (uint32_t i = nq * 4 + tid; i < len; i += NT) tmax = fmaxf(tmax, X[i]);
+            for (uint32_t i = nq * 4 + tid; i < len; i += NT)
+                if (X[i] > tmax) { tmax = X[i]; tq = i | 0x80000000u; }
         }
         PGS_TICK(1);   // penalties
 
         // ------------------------------------------------- slice max / argmax, lowest id
-        // the winning thread(s) look up the lowest index holding the block maximum
-        unsigned long long best = block_max_u64((unsigned long long)order_key(tmax) << 32, sm.rs);
-        const uint32_t bkey = (uint32_t)(best >> 32);
-        best = 0ull;
-        if (bkey && order_key(tmax) == bkey) {
-            const float bval = key_to_float(bkey);
-            uint32_t first = 0xffffffffu;
-            for (uint32_t q = tid; q < nq && first == 0xffffffffu; q += NT) {
-                const float4 v = ((const float4*)X)[q];
-                if (v.x == bval) first = q * 4;
-                else if (v.y == bval) first = q * 4 + 1;
-                else if (v.z == bval) first = q * 4 + 2;
-                else if (v.w == bval) first = q * 4 + 3;
+        // each thread knows where its maximum first occurs (its groups are visited in ascending order)
+        unsigned long long best = 0ull;
+        if (tmax > -INFINITY) {
+            uint32_t idx = tq & 0x7fffffffu;
+            if (!(tq & 0x80000000u)) {
+                const float4 v = *reinterpret_cast<const float4*>(X + idx);
+                idx += v.x == tmax ? 0u : v.y == tmax ? 1u : v.z == tmax ? 2u : 3u;
             }
-            for (uint32_t i = nq * 4 + tid; i < len && first == 0xffffffffu; i += NT)
-                if (X[i] == bval) first = i;
-            if (first != 0xffffffffu)
-                best = ((unsigned long long)bkey << 32) | (unsigned long long)(0xffffffffu - (lo + first));
+            best = ((unsigned long long)order_key(tmax) << 32) | (unsigned long long)(0xffffffffu - (lo + idx));
         }
-        if (bkey) best = block_max_u64(best, sm.rs);
+        best = block_max_u64(best, sm.rs);
         PGS_TICK(2);   // argmax
         // ------------------------------------------------ cluster exchange #1
         for (uint32_t r = tid; r < C; r += NT) {
