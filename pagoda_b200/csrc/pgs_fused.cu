@@ -1,7 +1,8 @@
 // Fused cluster kernel: the hot path of the sampler.
 //
-// One thread-block cluster owns one batch row.  The row is read from HBM exactly once, with
-// 128-bit coalesced loads, into the distributed shared memory of the cluster (each CTA keeps a
+// One thread-block cluster owns one batch row.  The row is read from HBM exactly once -- bulk
+// asynchronous copies (TMA, no multicast) for f32, 64-bit coalesced loads for bf16 -- into the
+// distributed shared memory of the cluster (each CTA keeps a
 // contiguous slice of the vocabulary as f32), and every later step of the chain
 // (pagoda/src/engine.rs:1286-1314, pagoda/src/sampler.rs:28-150) works on that copy:
 //
@@ -126,19 +127,17 @@ __device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t by
                  "l"(src), "r"(bytes), "r"(smem_u32(bar))
                  : "memory");
 }
-__device__ __forceinline__ void bulk_prefetch_l2(const void* src, uint32_t bytes) {
-    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src), "r"(bytes) : "memory");
-}
-// Bounded wait for phase `parity` of the barrier: false when the copy has not landed after ~2^22 polls.
+// Bounded wait for phase `parity` of the barrier: false when the copy has not landed after 2^16 tries
+// (each try may park the thread for up to 20 us, so the bound is about a second).
 __device__ __forceinline__ bool mbar_wait(unsigned long long* bar, uint32_t parity) {
-    for (uint32_t spin = 0; spin < (1u << 22); spin++) {
+    for (uint32_t spin = 0; spin < (1u << 16); spin++) {
         uint32_t ok;
         asm volatile(
             "{\n\t.reg .pred p;\n\t"
-            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
             "selp.u32 %0, 1, 0, p;\n\t}"
             : "=r"(ok)
-            : "r"(smem_u32(bar)), "r"(parity)
+            : "r"(smem_u32(bar)), "r"(parity), "r"(20000u)   // let the hardware park the thread for up to 20 us per try
             : "memory");
         if (ok) return true;
     }
@@ -174,7 +173,6 @@ __global__ void __launch_bounds__(NT, 1) fused_row_kernel(const RowArgs a, const
     }
     __syncthreads();
     long long tick_ = clock64();
-
     for (uint32_t row = cluster_id; row < a.rows; row += n_clusters) {
         FusedXchg& xc = sm.xchg[parity];
         const uint32_t pbuf = parity;   // exchange buffer of this row; the next synced row takes the other one
@@ -273,18 +271,12 @@ __global__ void __launch_bounds__(NT, 1) fused_row_kernel(const RowArgs a, const
         if (a.dtype == 0) {
             // f32 rows: one thread streams the slice into shared memory with bulk asynchronous copies
             // (32 KB pieces, one mbarrier each); every warp then checks / masks / maximises each piece
-            // as soon as it has landed.  The next row's slice is prefetched into L2 meanwhile, so HBM
-            // keeps streaming while this row is processed.
+            // as soon as it has landed.  (Prefetching the next row's slice into L2 was measured and
+            // bought nothing: the copy is not what limits this kernel.)
             const char* gsrc = rowp + (size_t)lo * 4;
             const uint32_t body = nq * 16;
             const uint32_t n_pieces = (body + TMA_PIECE - 1) / TMA_PIECE;   // <= 8 for any slice that fits
             if (tid == 0) {
-                if (row + n_clusters < a.rows && body) {
-                    const char* nxt = (const char*)a.logits + (size_t)(row + n_clusters) * a.row_stride * 4 + (size_t)lo * 4;
-                    if (((uintptr_t)nxt & 15) == 0)
-                        for (uint32_t off = 0; off < body; off += TMA_PIECE)
-                            bulk_prefetch_l2(nxt + off, min(TMA_PIECE, body - off));
-                }
                 if (body && !poisoned) {
                     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // earlier generic writes to X
                     for (uint32_t pc = 0; pc < n_pieces; pc++) {
