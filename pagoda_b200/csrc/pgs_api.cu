@@ -21,6 +21,8 @@ cudaError_t launch_general(const RowArgs& a, uint32_t grid, cudaStream_t stream)
 size_t general_smem_bytes();
 
 size_t fused_smem_bytes(uint32_t slice_len);
+uint32_t fused_threads();
+cudaError_t fused_ctas_per_sm(size_t smem, int* out);
 cudaError_t configure_fused(size_t max_smem);
 cudaError_t fused_max_clusters(uint32_t cluster, size_t smem, int* out);
 cudaError_t launch_fused(const RowArgs& a, const FusedLaunch& fl, uint32_t n_clusters, size_t smem,
@@ -310,26 +312,32 @@ extern "C" int pgs_mask_table_free(pgs_handle* h, int32_t table_id) {
 
 namespace {
 
-// Launch shape of the fused kernel for a vocabulary size: the smallest cluster whose slices fit
-// in shared memory.  Returns false when no cluster of up to 8 CTAs can hold the row.
+// Launch shape of the fused kernel for a vocabulary size: the smallest cluster whose slices are small
+// enough for two CTAs per SM (two rows then interleave on every SM and hide each other's barrier and copy
+// latency), else the smallest cluster that fits at all.  Returns false when no cluster of up to 8 CTAs can
+// hold the row.
 bool fused_shape(pgs_handle* h, uint32_t vocab) {
     if (h->fused_vocab == vocab) return h->fused_clusters > 0;
     h->fused_vocab = vocab;
     h->fused_clusters = 0;
-    for (uint32_t c = 1; c <= 8; c *= 2) {
-        const uint32_t slice = (((vocab + c - 1) / c) + 31u) & ~31u;
-        const size_t smem = pgs::fused_smem_bytes(slice);
-        if (smem > h->smem_optin) continue;
-        int n = 0;
-        if (pgs::fused_max_clusters(c, smem, &n) != cudaSuccess || n <= 0) { cudaGetLastError(); continue; }
-        // consecutive logits per thread in the sum passes: 4 * odd, so that the 128-bit shared-memory
-        // accesses of a warp (stride = chunk words) fall into distinct bank groups
-        uint32_t groups = ((slice + 1023u) / 1024u + 3u) / 4u;
-        if ((groups & 1u) == 0) groups += 1;
-        const uint32_t chunk = groups * 4u;
-        h->fused_cluster = c; h->fused_slice = slice; h->fused_chunk = chunk; h->fused_smem = smem;
-        h->fused_clusters = (uint32_t)n;
-        return true;
+    for (int want = 2; want >= 1; want--) {
+        for (uint32_t c = 1; c <= 8; c *= 2) {
+            const uint32_t slice = (((vocab + c - 1) / c) + 31u) & ~31u;
+            const size_t smem = pgs::fused_smem_bytes(slice);
+            if (smem > h->smem_optin) continue;
+            int per_sm = 0, n = 0;
+            if (pgs::fused_ctas_per_sm(smem, &per_sm) != cudaSuccess || per_sm < want) { cudaGetLastError(); continue; }
+            if (pgs::fused_max_clusters(c, smem, &n) != cudaSuccess || n <= 0) { cudaGetLastError(); continue; }
+            // consecutive logits per thread in the sum passes: 4 * odd, so that the 128-bit shared-memory
+            // accesses of a warp (stride = chunk words) fall into distinct bank groups
+            const uint32_t nt = pgs::fused_threads();
+            uint32_t groups = ((slice + nt - 1u) / nt + 3u) / 4u;
+            if ((groups & 1u) == 0) groups += 1;
+            const uint32_t chunk = groups * 4u;
+            h->fused_cluster = c; h->fused_slice = slice; h->fused_chunk = chunk; h->fused_smem = smem;
+            h->fused_clusters = (uint32_t)n;
+            return true;
+        }
     }
     return false;
 }
@@ -349,7 +357,9 @@ int launch_step(pgs_handle* h, pgs::RowArgs& a, cudaStream_t stream) {
     fl.work_rows = h->work_rows; fl.work_count = h->work_count;
     fl.prof = h->prof;
     fl.recs = h->recs; fl.cand_id = h->cand_id; fl.cand_x = h->cand_x;
-    const uint32_t nc = rows < h->fused_clusters ? rows : h->fused_clusters;
+    // as many clusters as are resident at once, evened out so that every cluster serves the same number of rows
+    const uint32_t waves = (rows + h->fused_clusters - 1) / h->fused_clusters;
+    const uint32_t nc = (rows + waves - 1) / waves;
     PGS_CUDA(h, pgs::launch_fused(a, fl, nc, h->fused_smem, stream));
     // Three independent consumers of the fused kernel's output: rows with a short candidate list
     // (the common case) finish on the caller's stream; rows with a long list and the rows on the

@@ -38,27 +38,57 @@ namespace cg = cooperative_groups;
 
 namespace pgs {
 
+// The kernel runs FNT threads per CTA and is shaped so that two CTAs (of different clusters, hence working
+// on different rows) share one SM: while one waits at a barrier or for its copy, the other one issues.
+// The per-thread maxima that bound the top-k threshold are kept for FVT "virtual threads": 128-bit group q
+// of a slice belongs to virtual thread q mod FVT, and a real thread plays VG = FVT / FNT of them (groups q
+// with q mod FVT = g * FNT + tid, g < VG).
+constexpr int FNT = 512;
+constexpr int FNW = FNT / 32;
+constexpr int FVT = 512;
+constexpr int FVW = FVT / 32;
+constexpr int VG = FVT / FNT;
+static_assert(VG == 1 || VG == 2 || VG == 4, "the bf16 loader assumes VG divides 4");
+
 struct FusedXchg {                  // peers write their slot through DSMEM
     unsigned long long best[F_MAXC];
-    int nonfinite[F_MAXC];
-    int spill[F_MAXC];
+    int flags[F_MAXC];              // non-finite / load-timeout bits, bit 8 = history table overflow
     uint32_t ncand[F_MAXC];
     float true_total[F_MAXC];       // plain sum of the slice's numerators
     double fold1[F_MAXC];           // slice increment of the fold, first estimate
 };
 
+// Everything the kernel needs to know about a row, read and validated by one thread while the CTA still works
+// on the row before it.
+struct RowCtl {
+    const char* rowp;       // first logit of the row
+    const uint32_t* mw;     // grammar mask words of the row's state, or null
+    float temp, freq, pres, rep;
+    float s_hi, s_lo;       // log2(e) / max(temp, 1e-9) as a two-float sum with s_lo > 0
+    uint32_t top_k, gflags, h0, nh;
+    uint32_t kind;          // 0 serve, 1 bad parameters, 2 defer to the general kernel
+};
+
 // Shared-memory workspace of one CTA (the vocabulary slice follows it).
 struct FusedSmem {
-    ReduceSmem rs;
-    double dscan[NW + 1];
+    RowCtl ctl[2];                  // alternates between consecutive rows of this CTA
+    uint32_t red_key[FNW], red_idx[FNW];              // one set of warp slots per reduction site
+    unsigned long long red_min[FNW];
+    uint32_t red_fin[FNW], walk[FNW];
+    float scan_sum[FNW], scan_fold[FNW];
     FusedXchg xchg[2];              // alternates between consecutive rows
-    struct { uint32_t hkey[F_HASH]; uint32_t hcnt[F_HASH]; } pen;
-    float tmax_all[F_MAXC * NT];    // every CTA's per-thread maxima
-    uint8_t redo_max[NT];
-    SelectSmem sel;
-    uint32_t cand_id[F_LCAP];
-    float cand_x[F_LCAP];
-    uint32_t cand_n;
+    union alignas(16) {             // the id -> count table is dead once the penalties are applied
+        struct { uint32_t hkey[F_HASH]; uint32_t hcnt[F_HASH]; } pen;
+        struct { SelectSmem sel; float members[F_LCAP]; } s;
+    } ua;
+    union alignas(16) {             // peers only write the next row's maxima after this row's last cluster barrier
+        float tmax_all[F_MAXC * FVT];   // every CTA's per-thread (or per-warp) maxima
+        struct { uint32_t id[F_LCAP]; float x[F_LCAP]; } c;   // this slice's top-k candidates
+    } ub;
+    float tmax_s[FVT];              // each virtual thread's maximum after the load pass
+    uint8_t redo_max[FVT];
+    uint32_t cand_n, memb_n, bound_key;
+    uint32_t hash_dirty;            // the id -> count table holds leftovers and must be reset before use
     unsigned long long load_bar[8]; // one mbarrier per 32 KB piece of the bulk copy that fills the slice
 };
 
@@ -73,44 +103,51 @@ struct FusedSmem {
         }                                                           \
     } while (0)
 
-// block sum of one double per thread
-__device__ __forceinline__ double block_sum_f64(double v, double* ws /*NW+1*/) {
-    for (int o = 16; o; o >>= 1) v += __shfl_xor_sync(FULL, v, o);
-    __syncthreads();
-    if ((threadIdx.x & 31) == 0) ws[threadIdx.x >> 5] = v;
-    __syncthreads();
-    if (threadIdx.x < 32) {
-        double w = ws[threadIdx.x];
-        for (int o = 16; o; o >>= 1) w += __shfl_xor_sync(FULL, w, o);
-        if (threadIdx.x == 0) ws[NW] = w;
+// ---- CTA-wide helpers for FNW warps with ONE barrier each: every warp leaves its partial in `slots`, and
+// after the barrier every warp combines all partials itself.  A call site owns its slots; they may be
+// written again only after another barrier (every site runs once per row, rows are barriers apart).
+__device__ __forceinline__ unsigned long long fblock_max_u64(unsigned long long v, unsigned long long* slots) {
+    const int lane = threadIdx.x & 31;
+    for (int o = 16; o; o >>= 1) {
+        const unsigned long long x = __shfl_xor_sync(FULL, v, o);
+        v = x > v ? x : v;
     }
+    if (lane == 0) slots[threadIdx.x >> 5] = v;
     __syncthreads();
-    return ws[NW];
+    v = slots[lane % FNW];
+    for (int o = FNW / 2; o; o >>= 1) {
+        const unsigned long long x = __shfl_xor_sync(FULL, v, o);
+        v = x > v ? x : v;
+    }
+    return v;
 }
-
-// exclusive scan of one double per thread; *total = block sum
-__device__ __forceinline__ double block_excl_scan_f64(double v, double* total, double* ws /*NW+1*/) {
+__device__ __forceinline__ uint32_t fblock_sum_u32(uint32_t v, uint32_t* slots) {
+    const int lane = threadIdx.x & 31;
+    for (int o = 16; o; o >>= 1) v += __shfl_xor_sync(FULL, v, o);
+    if (lane == 0) slots[threadIdx.x >> 5] = v;
+    __syncthreads();
+    v = lane < FNW ? slots[lane] : 0u;
+    for (int o = 16; o; o >>= 1) v += __shfl_xor_sync(FULL, v, o);
+    return v;
+}
+// exclusive scan of one float per thread (plain adds: only used as an estimate); *total = CTA sum
+__device__ __forceinline__ float fblock_excl_scan_f32(float v, float* total, float* slots) {
     const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
-    double inc = v;
+    float inc = v;
     for (int o = 1; o < 32; o <<= 1) {
-        double t = __shfl_up_sync(FULL, inc, o);
+        const float t = __shfl_up_sync(FULL, inc, o);
         if (lane >= o) inc += t;
     }
+    if (lane == 31) slots[w] = inc;
     __syncthreads();
-    if (lane == 31) ws[w] = inc;
-    __syncthreads();
-    if (threadIdx.x < 32) {
-        double x = ws[threadIdx.x], xi = x;
-        for (int o = 1; o < 32; o <<= 1) {
-            double t = __shfl_up_sync(FULL, xi, o);
-            if (lane >= o) xi += t;
-        }
-        ws[threadIdx.x] = xi - x;
-        if (threadIdx.x == 31) ws[NW] = xi;
+    const float x = lane < FNW ? slots[lane] : 0.0f;
+    float xi = x;
+    for (int o = 1; o < 32; o <<= 1) {
+        const float t = __shfl_up_sync(FULL, xi, o);
+        if (lane >= o) xi += t;
     }
-    __syncthreads();
-    *total = ws[NW];
-    return ws[w] + (inc - v);
+    *total = __shfl_sync(FULL, xi, 31);
+    return __shfl_sync(FULL, xi - x, w) + (inc - v);
 }
 
 // ---- bulk asynchronous copy (TMA, no tensor map, no multicast) global -> this CTA's shared memory
@@ -148,15 +185,15 @@ constexpr uint32_t TMA_PIECE = 32768;   // bytes per bulk copy
 __device__ __forceinline__ uint32_t load_owner(uint32_t i, uint32_t len) {
     // thread that loaded slice element i: 128-bit groups are dealt round-robin, then the ragged tail
     const uint32_t body = (len / 4) * 4;
-    return i < body ? ((i >> 2) & (NT - 1)) : ((i - body) & (NT - 1));
+    return i < body ? ((i >> 2) & (FVT - 1)) : ((i - body) & (FVT - 1));
 }
 
-__global__ void __launch_bounds__(NT, 1) fused_row_kernel(const RowArgs a, const FusedLaunch fl) {
+__global__ void __launch_bounds__(FNT, 2) fused_row_kernel(const RowArgs a, const FusedLaunch fl) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     FusedSmem& sm = *reinterpret_cast<FusedSmem*>(smem_raw);
     float* X = reinterpret_cast<float*>(smem_raw + ((sizeof(FusedSmem) + 15) & ~size_t(15)));
     cg::cluster_group cluster = cg::this_cluster();
-    const int tid = threadIdx.x;
+    const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
     const uint32_t C = fl.cluster;
     const uint32_t rank = cluster.block_rank();
     const uint32_t n_clusters = gridDim.x / C, cluster_id = blockIdx.x / C;
@@ -168,15 +205,13 @@ __global__ void __launch_bounds__(NT, 1) fused_row_kernel(const RowArgs a, const
     uint32_t load_phase = 0;        // parity of the next completion of load_bar
     bool poisoned = false;          // a bulk copy never landed: later rows of this CTA report that too
     if (tid == 0) {
+        sm.hash_dirty = 1u;
         for (int b = 0; b < 8; b++) mbar_init(&sm.load_bar[b], 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
-    long long tick_ = clock64();
-    for (uint32_t row = cluster_id; row < a.rows; row += n_clusters) {
-        FusedXchg& xc = sm.xchg[parity];
-        const uint32_t pbuf = parity;   // exchange buffer of this row; the next synced row takes the other one
-        // ------------------------------------------------------------------ parameters
+    // one thread reads and validates a row's parameters (same rules as the general kernel)
+    auto prepare = [&](uint32_t row, RowCtl& c) {
         const float temp = a.temperature ? a.temperature[row] : 0.0f;
         const uint32_t top_k = a.top_k ? a.top_k[row] : 0u;
         const float top_p = a.top_p ? a.top_p[row] : 1.0f;
@@ -205,29 +240,58 @@ __global__ void __launch_bounds__(NT, 1) fused_row_kernel(const RowArgs a, const
             const uint32_t h1 = a.hist_offsets[row + 1];
             if (h1 < h0 || h1 - h0 > a.max_history) bad = true; else nh = h1 - h0;
         }
-        const bool writer = rank == 0 && tid == 0;
-        if (bad) {
-            if (writer) { a.token[row] = 0; a.status[row] = ROW_BAD_PARAM; if (a.drew) a.drew[row] = 0; fl.recs[row].kind = 0; }
-            continue;
-        }
         const bool greedy = temp < 1e-5f;
         const bool use_k = top_k != 0u && top_k < V;
-        // rows this kernel does not serve go to the general kernel (decided identically by every CTA)
+        // rows this kernel does not serve go to the general kernel
         const char* rowp = (const char*)a.logits + (size_t)row * a.row_stride * (a.dtype == 0 ? 4 : 2);
         const bool aligned = (((uintptr_t)rowp & 15) == 0);
         const bool defer = !aligned || (!greedy && (!use_k || top_k > (uint32_t)F_KMAX));
-        if (defer) {
+        // log2(e) / t as a two-float sum s_hi + s_lo with s_lo > 0, so that the exponent's argument carries
+        // no systematic error and a masked entry (-inf) stays -inf through both products
+        const double scale_d = 1.4426950408889634 / (double)fmaxf(temp, 1e-9f);
+        float s_hi = (float)scale_d;
+        if ((double)s_hi >= scale_d) s_hi = u2f(f2u(s_hi) - 1u);
+        c.s_hi = s_hi; c.s_lo = (float)(scale_d - (double)s_hi);
+        c.rowp = rowp; c.mw = mw; c.temp = temp; c.freq = freq; c.pres = pres; c.rep = rep;
+        c.top_k = top_k; c.gflags = gflags; c.h0 = h0; c.nh = nh;
+        c.kind = bad ? 1u : defer ? 2u : 0u;
+    };
+    constexpr int PREP_TID = FNT - 32;   // lane 0 of the last warp
+    if (tid == PREP_TID && cluster_id < a.rows) prepare(cluster_id, sm.ctl[0]);
+    long long tick_ = clock64();
+    uint32_t it = 0;
+    for (uint32_t row = cluster_id; row < a.rows; row += n_clusters, it++) {
+        // this row's parameters are complete, and every warp is done with the slice of the row before
+        __syncthreads();
+        FusedXchg& xc = sm.xchg[parity];
+        const uint32_t pbuf = parity;   // exchange buffer of this row; the next synced row takes the other one
+        PGS_TICK(12);  // row barrier
+        const RowCtl& ctl = sm.ctl[it & 1];
+        if (tid == PREP_TID && row + n_clusters < a.rows) prepare(row + n_clusters, sm.ctl[(it + 1) & 1]);
+        const bool writer = rank == 0 && tid == 0;
+        if (ctl.kind == 1u) {
+            if (writer) { a.token[row] = 0; a.status[row] = ROW_BAD_PARAM; if (a.drew) a.drew[row] = 0; fl.recs[row].kind = 0; }
+            continue;
+        }
+        if (ctl.kind == 2u) {
             if (writer) { fl.work_rows[atomicAdd(fl.work_count, 1u)] = row; fl.recs[row].kind = 0; }
             continue;
         }
+        const float temp = ctl.temp, freq = ctl.freq, pres = ctl.pres, rep = ctl.rep;
+        const uint32_t top_k = ctl.top_k, gflags = ctl.gflags, h0 = ctl.h0, nh = ctl.nh;
+        const uint32_t* mw = ctl.mw;
+        const char* rowp = ctl.rowp;
+        const bool greedy = temp < 1e-5f;
 
         // ------------------------------- load slice: sanity + bitmask AND + per-thread max
-        float tmax = -INFINITY;
+        float tm[VG];        // running maximum of each virtual thread this thread plays
+        uint32_t tqs[VG];    // slice index of the 128-bit group (or, flagged, the tail element) that holds it
+#pragma unroll
+        for (int g = 0; g < VG; g++) { tm[g] = -INFINITY; tqs[g] = 0; sm.redo_max[g * FNT + tid] = 0; }
+        if (tid == 0) sm.cand_n = 0u;
         int nonfinite = 0;
-        uint32_t tq = 0;   // slice index of the 128-bit group (or, flagged, the tail element) that holds tmax
-        sm.redo_max[tid] = 0;
         const uint32_t nq = len / 4;   // 128-bit groups; a ragged tail exists only in the last slice
-        auto take4 = [&](uint32_t q, float4 v) {
+        auto take4 = [&](uint32_t q, float4 v, int g) {
             nonfinite |= !finite_f(v.x) | !finite_f(v.y) | !finite_f(v.z) | !finite_f(v.w);
             if (mw) {
                 const uint32_t bits = __ldg(mw + ((lo >> 5) + (q >> 3))) >> ((q & 7) * 4);
@@ -237,13 +301,13 @@ __global__ void __launch_bounds__(NT, 1) fused_row_kernel(const RowArgs a, const
                 if (!(bits & 8u)) v.w = -INFINITY;
             }
             const float m4 = fmaxf(fmaxf(v.x, v.y), fmaxf(v.z, v.w));
-            if (m4 > tmax) { tmax = m4; tq = q * 4; }
+            if (m4 > tm[g]) { tm[g] = m4; tqs[g] = q * 4; }
             ((float4*)X)[q] = v;
         };
         auto take1 = [&](uint32_t i, float x) {
             nonfinite |= !finite_f(x);
             if (mw && !((__ldg(mw + ((lo + i) >> 5)) >> ((lo + i) & 31)) & 1u)) x = -INFINITY;
-            if (x > tmax) { tmax = x; tq = i | 0x80000000u; }
+            if (x > tm[0]) { tm[0] = x; tqs[0] = i | 0x80000000u; }   // the tail has at most 3 elements: threads 0..2
             X[i] = x;
         };
         // history ids of this slice -> id->count table; runs while the copy below is in flight
@@ -252,17 +316,25 @@ __global__ void __launch_bounds__(NT, 1) fused_row_kernel(const RowArgs a, const
         const bool do_rep = rep != 1.0f;
         const bool pen = nh > 0 && (do_fp || do_rep);
         int spill = 0;
+        // the first id of every thread is requested before anything else, so that its latency hides behind the
+        // table reset and the copy's issue
+        const uint32_t hid0 = (pen && (uint32_t)tid < nh) ? __ldg(a.hist_ids + h0 + tid) : 0xffffffffu;
         auto index_history = [&]() {
-            for (int s = tid; s < F_HASH; s += NT) { sm.pen.hkey[s] = 0xffffffffu; sm.pen.hcnt[s] = 0u; }
-            __syncthreads();
-            for (uint32_t j = tid; j < nh; j += NT) {
-                const uint32_t id = __ldg(a.hist_ids + h0 + j);
+            // the penalty pass hands every slot back empty, so a reset is only needed after a row that left
+            // entries behind or used the space for something else
+            if (sm.hash_dirty) {
+                for (int s = tid; s < F_HASH; s += FNT) { sm.ua.pen.hkey[s] = 0xffffffffu; sm.ua.pen.hcnt[s] = 0u; }
+                __syncthreads();
+                if (tid == 0) sm.hash_dirty = 0u;
+            }
+            for (uint32_t j = tid; j < nh; j += FNT) {
+                const uint32_t id = j == (uint32_t)tid ? hid0 : __ldg(a.hist_ids + h0 + j);
                 if (id < lo || id >= hi) continue;
                 uint32_t s = (id * 2654435761u) >> 21;   // 11 bits
                 bool placed = false;
                 for (int probe = 0; probe < 64; probe++) {
-                    const uint32_t prev = atomicCAS(&sm.pen.hkey[s], 0xffffffffu, id);
-                    if (prev == 0xffffffffu || prev == id) { atomicAdd(&sm.pen.hcnt[s], 1u); placed = true; break; }
+                    const uint32_t prev = atomicCAS(&sm.ua.pen.hkey[s], 0xffffffffu, id);
+                    if (prev == 0xffffffffu || prev == id) { atomicAdd(&sm.ua.pen.hcnt[s], 1u); placed = true; break; }
                     s = (s + 1) & (F_HASH - 1);
                 }
                 if (!placed) spill = 1;
@@ -288,145 +360,194 @@ __global__ void __launch_bounds__(NT, 1) fused_row_kernel(const RowArgs a, const
             }
             if (pen) index_history();
             PGS_TICK(11);  // copy issued, history indexed
-            float poison = 0.0f;   // 0 * v is NaN exactly when v is infinite or NaN, and NaN sticks
+            float poison = 0.0f, poison1 = 0.0f;   // 0 * v is NaN exactly when v is infinite or NaN, and NaN sticks
             for (uint32_t pc = 0; pc < n_pieces; pc++) {
                 // every warp waits for the piece on its own: one lane polls (bounded), the rest follow
                 int ok = 1;
-                if (!poisoned && (tid & 31) == 0) ok = mbar_wait(&sm.load_bar[pc], load_phase) ? 1 : 0;
+                const long long w0_ = fl.prof ? clock64() : 0;
+                if (!poisoned && lane == 0) ok = mbar_wait(&sm.load_bar[pc], load_phase) ? 1 : 0;
                 ok = __shfl_sync(FULL, ok, 0);
+                if (fl.prof && tid == 0) fl.prof[blockIdx.x * 16 + 14] += clock64() - w0_;   // also inside slot 0
                 if (!ok) poisoned = true;
                 if (poisoned) continue;
                 const uint32_t q_end = min(nq, (pc + 1) * (TMA_PIECE / 16));
-                for (uint32_t q = pc * (TMA_PIECE / 16) + tid; q < q_end; q += NT) {
-                    float4 v = ((const float4*)X)[q];
-                    poison = __fmaf_rn(v.x, 0.0f, poison); poison = __fmaf_rn(v.y, 0.0f, poison);
-                    poison = __fmaf_rn(v.z, 0.0f, poison); poison = __fmaf_rn(v.w, 0.0f, poison);
-                    if (mw) {
-                        const uint32_t bits = __ldg(mw + ((lo >> 5) + (q >> 3))) >> ((q & 7) * 4);
-                        if (!(bits & 1u)) v.x = -INFINITY;
-                        if (!(bits & 2u)) v.y = -INFINITY;
-                        if (!(bits & 4u)) v.z = -INFINITY;
-                        if (!(bits & 8u)) v.w = -INFINITY;
-                        ((float4*)X)[q] = v;
+                const uint32_t qb = pc * (TMA_PIECE / 16) + tid;
+                constexpr int PIT = (TMA_PIECE / 16) / FNT;   // groups per thread and piece, requested two at a time
+#pragma unroll
+                for (int k0 = 0; k0 < PIT; k0 += 2) {
+                    float4 v[2];
+#pragma unroll
+                    for (int k2 = 0; k2 < 2; k2++)
+                        if (k0 + k2 < PIT && qb + (k0 + k2) * FNT < q_end) v[k2] = ((const float4*)X)[qb + (k0 + k2) * FNT];
+#pragma unroll
+                    for (int k2 = 0; k2 < 2; k2++) {
+                        const uint32_t q = qb + (k0 + k2) * FNT;
+                        if (k0 + k2 >= PIT || q >= q_end) break;
+                        const int g = (k0 + k2) % VG;   // a piece holds a whole number of FVT groups
+                        float& pz = k2 ? poison1 : poison;
+                        pz = __fmaf_rn(v[k2].x, 0.0f, pz); pz = __fmaf_rn(v[k2].y, 0.0f, pz);
+                        pz = __fmaf_rn(v[k2].z, 0.0f, pz); pz = __fmaf_rn(v[k2].w, 0.0f, pz);
+                        if (mw) {
+                            const uint32_t bits = __ldg(mw + ((lo >> 5) + (q >> 3))) >> ((q & 7) * 4);
+                            if (!(bits & 1u)) v[k2].x = -INFINITY;
+                            if (!(bits & 2u)) v[k2].y = -INFINITY;
+                            if (!(bits & 4u)) v[k2].z = -INFINITY;
+                            if (!(bits & 8u)) v[k2].w = -INFINITY;
+                            ((float4*)X)[q] = v[k2];
+                        }
+                        const float m4 = fmaxf(fmaxf(v[k2].x, v[k2].y), fmaxf(v[k2].z, v[k2].w));
+                        if (m4 > tm[g]) { tm[g] = m4; tqs[g] = q * 4; }
                     }
-                    const float m4 = fmaxf(fmaxf(v.x, v.y), fmaxf(v.z, v.w));
-                    if (m4 > tmax) { tmax = m4; tq = q * 4; }
                 }
             }
+            poison += poison1;
             if (n_pieces) load_phase ^= 1u;
             if (poisoned) nonfinite = 2;   // reported as a load timeout after the exchange
             nonfinite |= poison != poison;
             if (!poisoned)
-                for (uint32_t i = nq * 4 + tid; i < len; i += NT) take1(i, __ldcs((const float*)rowp + lo + i));
+                for (uint32_t i = nq * 4 + tid; i < len; i += FNT) take1(i, __ldcs((const float*)rowp + lo + i));
         } else {
             if (pen) index_history();
             const uint2* src = (const uint2*)(rowp) + lo / 4;    // 4 bf16 per 8-byte load
-            for (uint32_t q0 = tid; q0 < nq; q0 += 4 * NT) {
+            for (uint32_t q0 = tid; q0 < nq; q0 += 4 * FNT) {
                 uint2 r[4];
 #pragma unroll
                 for (int u = 0; u < 4; u++)
-                    if (q0 + u * NT < nq) r[u] = __ldcs(src + q0 + u * NT);
+                    if (q0 + u * FNT < nq) r[u] = __ldcs(src + q0 + u * FNT);
 #pragma unroll
                 for (int u = 0; u < 4; u++)
-                    if (q0 + u * NT < nq) {
+                    if (q0 + u * FNT < nq) {
                         float4 v;   // bf16 -> f32 is a 16-bit shift: exact
                         v.x = __uint_as_float(r[u].x << 16); v.y = __uint_as_float(r[u].x & 0xffff0000u);
                         v.z = __uint_as_float(r[u].y << 16); v.w = __uint_as_float(r[u].y & 0xffff0000u);
-                        take4(q0 + u * NT, v);
+                        take4(q0 + u * FNT, v, u % VG);   // q0 - tid is a multiple of 4 * FNT
                     }
             }
-            for (uint32_t i = nq * 4 + tid; i < len; i += NT)
+            for (uint32_t i = nq * 4 + tid; i < len; i += FNT)
                 take1(i, __uint_as_float((uint32_t)__ldcs((const unsigned short*)rowp + lo + i) << 16));
         }
-        nonfinite = __syncthreads_or(nonfinite);
+#pragma unroll
+        for (int g = 0; g < VG; g++) sm.tmax_s[g * FNT + tid] = tm[g];
+        {
+            const int both = __syncthreads_or(nonfinite | (spill << 8));
+            nonfinite = both & 0xff;
+            spill = both >> 8;
+        }
         PGS_TICK(0);   // load
 
         // --------------------------------------------------------------- penalties
+        if (pen && (nonfinite || spill) && tid == 0) sm.hash_dirty = 1u;   // the table keeps this row's entries
         if (pen && !nonfinite) {
-            spill = __syncthreads_or(spill);
             if (!spill) {
-                for (int s = tid; s < F_HASH; s += NT) {
-                    const uint32_t id = sm.pen.hkey[s];
+                for (int s = tid; s < F_HASH; s += FNT) {
+                    const uint32_t id = sm.ua.pen.hkey[s];
                     if (id == 0xffffffffu) continue;
+                    const float cnt = (float)sm.ua.pen.hcnt[s];
+                    sm.ua.pen.hkey[s] = 0xffffffffu; sm.ua.pen.hcnt[s] = 0u;   // hand the slot back empty
                     const uint32_t i = id - lo;
-                    float x = X[i];
+                    const float old = X[i];
+                    float x = old;
                     if (do_rep) x = x > 0.0f ? fdiv(x, rep) : fmul(x, rep);
                     if (do_fp) {
-                        x = fsub(x, fmul(freq, (float)sm.pen.hcnt[s]));
+                        x = fsub(x, fmul(freq, cnt));
                         if (do_pres) x = fsub(x, pres);
                     }
                     // an overflowed penalty is non-finite; the chain treats that like a masked entry
-                    X[i] = finite_f(x) ? x : -INFINITY;
-                    sm.redo_max[load_owner(i, len)] = 1;   // that thread's maximum is stale now
+                    x = finite_f(x) ? x : -INFINITY;
+                    X[i] = x;
+                    // the owner's maximum is stale only if this entry held it, or now reaches it
+                    const uint32_t ow = load_owner(i, len);
+                    const float om = sm.tmax_s[ow];
+                    if (old >= om || x >= om) sm.redo_max[ow] = 1;
                 }
             }
             __syncthreads();
         }
         // ----------------------------------------------------------------- EOS fix
-        if (mw && (gflags & 1u) && a.eos >= 0 && (uint32_t)a.eos >= lo && (uint32_t)a.eos < hi && tid == 0 &&
-            !finite_f(X[a.eos - lo])) {
-            X[a.eos - lo] = 0.0f;
-            sm.redo_max[load_owner(a.eos - lo, len)] = 1;
+        if (mw && (gflags & 1u) && a.eos >= 0 && (uint32_t)a.eos >= lo && (uint32_t)a.eos < hi) {   // CTA-uniform
+            if (tid == 0 && !finite_f(X[a.eos - lo])) {
+                X[a.eos - lo] = 0.0f;
+                sm.redo_max[load_owner(a.eos - lo, len)] = 1;
+            }
+            __syncthreads();
         }
-        __syncthreads();
-        if (sm.redo_max[tid]) {
-            tmax = -INFINITY;
-            for (uint32_t q = tid; q < nq; q += NT) {
+#pragma unroll
+        for (int g = 0; g < VG; g++) {
+            if (!sm.redo_max[g * FNT + tid]) continue;
+            tm[g] = -INFINITY;
+            for (uint32_t q = g * FNT + tid; q < nq; q += FVT) {
                 const float4 v = ((const float4*)X)[q];
                 const float m4 = fmaxf(fmaxf(v.x, v.y), fmaxf(v.z, v.w));
-                if (m4 > tmax) { tmax = m4; tq = q * 4; }
+                if (m4 > tm[g]) { tm[g] = m4; tqs[g] = q * 4; }
             }
-            for (uint32_t i = nq * 4 + tid; i < len; i += NT)
-                if (X[i] > tmax) { tmax = X[i]; tq = i | 0x80000000u; }
+            if (g == 0)
+                for (uint32_t i = nq * 4 + tid; i < len; i += FNT)
+                    if (X[i] > tm[0]) { tm[0] = X[i]; tqs[0] = i | 0x80000000u; }
         }
         PGS_TICK(1);   // penalties
 
         // ------------------------------------------------- slice max / argmax, lowest id
         // each thread knows where its maximum first occurs (its groups are visited in ascending order)
-        unsigned long long best = 0ull;
-        if (tmax > -INFINITY) {
-            uint32_t idx = tq & 0x7fffffffu;
-            if (!(tq & 0x80000000u)) {
+        uint32_t bkey = 0u, bidx = 0xffffffffu;   // largest order key, lowest id holding it
+#pragma unroll
+        for (int g = 0; g < VG; g++) {
+            if (!(tm[g] > -INFINITY)) continue;
+            uint32_t idx = tqs[g] & 0x7fffffffu;
+            if (!(tqs[g] & 0x80000000u)) {
                 const float4 v = *reinterpret_cast<const float4*>(X + idx);
-                idx += v.x == tmax ? 0u : v.y == tmax ? 1u : v.z == tmax ? 2u : 3u;
+                idx += v.x == tm[g] ? 0u : v.y == tm[g] ? 1u : v.z == tm[g] ? 2u : 3u;
             }
-            best = ((unsigned long long)order_key(tmax) << 32) | (unsigned long long)(0xffffffffu - (lo + idx));
+            const uint32_t k = order_key(tm[g]);
+            if (k > bkey || (k == bkey && lo + idx < bidx)) { bkey = k; bidx = lo + idx; }
         }
-        best = block_max_u64(best, sm.rs);
+        {
+            const uint32_t wk = __reduce_max_sync(FULL, bkey);
+            const uint32_t wi = __reduce_min_sync(FULL, bkey == wk ? bidx : 0xffffffffu);
+            if (lane == 0) { sm.red_key[w] = wk; sm.red_idx[w] = wi; }
+            __syncthreads();
+            const uint32_t k2 = sm.red_key[lane % FNW], i2 = sm.red_idx[lane % FNW];
+            bkey = __reduce_max_sync(FULL, k2);
+            bidx = __reduce_min_sync(FULL, k2 == bkey ? i2 : 0xffffffffu);
+        }
+        const unsigned long long best = bkey ? ((unsigned long long)bkey << 32) | (unsigned long long)(0xffffffffu - bidx) : 0ull;
         PGS_TICK(2);   // argmax
         // ------------------------------------------------ cluster exchange #1
-        for (uint32_t r = tid; r < C; r += NT) {
+        for (uint32_t r = tid; r < C; r += FNT) {
             FusedSmem* peer = cluster.map_shared_rank(&sm, r);
             peer->xchg[pbuf].best[rank] = best;
-            peer->xchg[pbuf].nonfinite[rank] = nonfinite;
-            peer->xchg[pbuf].spill[rank] = spill;
+            peer->xchg[pbuf].flags[rank] = nonfinite | (spill << 8);
         }
         // material for the top-k bound: the 32*C warp maxima when there are comfortably more warps than
-        // top_k, else all NT*C thread maxima
-        const bool warp_bound = !greedy && 2u * top_k <= C * NW;
+        // top_k, else all FVT*C thread maxima
+        const bool warp_bound = !greedy && 2u * top_k <= C * FVW;
         if (!greedy) {
             if (warp_bound) {
-                float wmax = tmax;
-                for (int o = 16; o; o >>= 1) wmax = fmaxf(wmax, __shfl_xor_sync(FULL, wmax, o));
-                if ((tid & 31) < (int)C)
-                    cluster.map_shared_rank(&sm, tid & 31)->tmax_all[rank * NW + (tid >> 5)] = wmax;
+#pragma unroll
+                for (int g = 0; g < VG; g++) {   // virtual warp g * FNW + w
+                    float wmax = tm[g];
+                    for (int o = 16; o; o >>= 1) wmax = fmaxf(wmax, __shfl_xor_sync(FULL, wmax, o));
+                    if (lane < (int)C) cluster.map_shared_rank(&sm, lane)->ub.tmax_all[rank * FVW + g * FNW + w] = wmax;
+                }
             } else {
-                for (uint32_t r = 0; r < C; r++) cluster.map_shared_rank(&sm, r)->tmax_all[rank * NT + tid] = tmax;
+                for (uint32_t r = 0; r < C; r++) {
+                    float* dst = cluster.map_shared_rank(&sm, r)->ub.tmax_all + rank * FVT + tid;
+#pragma unroll
+                    for (int g = 0; g < VG; g++) dst[g * FNT] = tm[g];
+                }
             }
         }
         cluster.sync();
         parity ^= 1u;
         PGS_TICK(3);   // sync 1
-        unsigned long long gbest = 0ull;
-        int any_nonfinite = 0, any_spill = 0;
-        for (uint32_t r = 0; r < C; r++) {
-            gbest = xc.best[r] > gbest ? xc.best[r] : gbest;
-            any_nonfinite |= xc.nonfinite[r];
-            any_spill |= xc.spill[r];
-        }
-        const bool any = gbest != 0ull;
-        const float m = any ? key_to_float((uint32_t)(gbest >> 32)) : -INFINITY;
-        const uint32_t amax = any ? 0xffffffffu - (uint32_t)gbest : 0u;
+        // lane r looks at CTA r's slot; warp-wide reductions combine them
+        const unsigned long long rb = (uint32_t)lane < C ? xc.best[lane] : 0ull;
+        const uint32_t gkey = __reduce_max_sync(FULL, (uint32_t)(rb >> 32));
+        const uint32_t ginv = __reduce_max_sync(FULL, (uint32_t)(rb >> 32) == gkey ? (uint32_t)rb : 0u);
+        const uint32_t gfl = __reduce_or_sync(FULL, (uint32_t)lane < C ? (uint32_t)xc.flags[lane] : 0u);
+        const int any_nonfinite = (int)(gfl & 0xffu), any_spill = (int)(gfl >> 8);
+        const bool any = gkey != 0u;
+        const float m = any ? key_to_float(gkey) : -INFINITY;
+        const uint32_t amax = any ? 0xffffffffu - ginv : 0u;
         const int status = any ? ROW_OK : ROW_EMPTY;
         if (any_nonfinite) {
             if (writer) { a.token[row] = 0; a.status[row] = (any_nonfinite & 2) ? ROW_LOAD_TIMEOUT : ROW_NONFINITE; if (a.drew) a.drew[row] = 0; fl.recs[row].kind = 0; }
@@ -455,97 +576,117 @@ __global__ void __launch_bounds__(NT, 1) fused_row_kernel(const RowArgs a, const
         }
 
         // -------------------------------- top-k bound: k-th largest per-thread maximum
-        // The C*NT maxima are spread over 2048 equal-width buckets between their smallest finite
+        // The C*FVT maxima are spread over 2048 equal-width buckets between their smallest finite
         // value and the row maximum (a monotone map), the bucket holding the k-th largest is found
         // from the histogram, and the exact value is picked among that bucket's few members.
         const float t = fmaxf(temp, 1e-9f);
         float cut = -INFINITY;
+        PGS_TICK(13);  // exchange #1 read
         if (warp_bound) {
-            // k-th largest of the 32*C warp maxima: thread j ranks maximum j against all others
-            const uint32_t nvw = C * NW;
-            if (tid == 0) sm.sel.hist[0] = 0u;
-            __syncthreads();
-            if ((uint32_t)tid < nvw) {
-                const float v = sm.tmax_all[tid];
-                uint32_t gt = 0, ge = 0;
-                for (uint32_t o = 0; o < nvw; o++) { const float u = sm.tmax_all[o]; gt += u > v; ge += u >= v; }
-                if (finite_f(v) && gt < top_k && top_k <= ge) sm.sel.hist[0] = order_key(v);
+            // k-th largest of the FVW*C warp maxima.  Their order keys are made distinct by replacing the
+            // low 8 bits with the slot number (the bound can only move down by that, so it stays a bound),
+            // so a key's rank is the number of larger keys.  Every warp holds all keys, four per lane, and
+            // ranks its share of them with warp-wide sums; exactly one key has rank top_k - 1.
+            const uint32_t nvw = C * FVW;   // <= 128, a multiple of 16
+            uint4 u = make_uint4(0u, 0u, 0u, 0u);
+            if ((uint32_t)lane * 4u < nvw) {
+                const float4 f = *reinterpret_cast<const float4*>(sm.ub.tmax_all + lane * 4);
+                u.x = (order_key(f.x) & ~0xffu) | (uint32_t)(lane * 4);
+                u.y = (order_key(f.y) & ~0xffu) | (uint32_t)(lane * 4 + 1);
+                u.z = (order_key(f.z) & ~0xffu) | (uint32_t)(lane * 4 + 2);
+                u.w = (order_key(f.w) & ~0xffu) | (uint32_t)(lane * 4 + 3);
+            }
+            constexpr int J = F_MAXC * FVW / FNW;   // keys per warp at the largest cluster
+#pragma unroll
+            for (int jj = 0; jj < J; jj++) {
+                const uint32_t j = w * ((nvw + FNW - 1) / FNW) + jj;   // warp-uniform
+                if (jj < (int)((nvw + FNW - 1) / FNW) && j < nvw) {
+                    const uint32_t sel = j & 3u;
+                    const uint32_t mine = sel == 0u ? u.x : sel == 1u ? u.y : sel == 2u ? u.z : u.w;
+                    const uint32_t kj = __shfl_sync(FULL, mine, j >> 2);
+                    const uint32_t cnt = __reduce_add_sync(FULL, (u.x > kj) + (u.y > kj) + (u.z > kj) + (u.w > kj));
+                    if (cnt == top_k - 1u && lane == 0) sm.bound_key = kj & ~0xffu;
+                }
             }
             __syncthreads();
-            const uint32_t kk = sm.sel.hist[0];
+            PGS_TICK(15);  // warp maxima ranked
+            const uint32_t kk = sm.bound_key;
             if (kk) {
                 const float bound = key_to_float(kk);
                 const float delta = 4.8e-7f * (fabsf(m - bound) + 4.0f * t) + 4.8e-7f * (fabsf(bound) + fabsf(m));
                 cut = bound - delta;
             }
         } else {
-            const uint32_t nv = C * NT;
+            if (tid == 0) sm.hash_dirty = 1u;   // the histogram below lives in the table's space
+            const uint32_t nv = C * FVT;
             uint32_t fin = 0;
             unsigned long long inv_min = 0ull;
-            for (uint32_t i = tid; i < nv; i += NT) {
-                const uint32_t key = order_key(sm.tmax_all[i]);
+            for (uint32_t i = tid; i < nv; i += FNT) {
+                const uint32_t key = order_key(sm.ub.tmax_all[i]);
                 if (key) { fin++; const unsigned long long iv = 0xffffffffull - key; inv_min = iv > inv_min ? iv : inv_min; }
             }
-            const uint32_t n_fin = block_sum_u32(fin, sm.rs);
-            inv_min = block_max_u64(inv_min, sm.rs);
+            const uint32_t n_fin = fblock_sum_u32(fin, sm.red_fin);
+            inv_min = fblock_max_u64(inv_min, sm.red_min);
             if (n_fin >= top_k) {
                 const float lo_v = key_to_float((uint32_t)(0xffffffffull - inv_min));
                 const float sc = m > lo_v ? 2047.0f / (m - lo_v) : 0.0f;
-                for (int bkt = tid; bkt < 2048; bkt += NT) sm.sel.hist[bkt] = 0u;
-                if (tid == 0) { sm.sel.prefix = 0xffffffffu; sm.sel.k = 0u; sm.cand_n = 0u; }
+                for (int bkt = tid; bkt < 2048; bkt += FNT) sm.ua.s.sel.hist[bkt] = 0u;
+                if (tid == 0) { sm.ua.s.sel.prefix = 0xffffffffu; sm.ua.s.sel.k = 0u; sm.memb_n = 0u; }
                 __syncthreads();
-                for (uint32_t i = tid; i < nv; i += NT) {
-                    const float v = sm.tmax_all[i];
-                    if (finite_f(v)) atomicAdd(&sm.sel.hist[min(2047u, (uint32_t)((v - lo_v) * sc))], 1u);
+                for (uint32_t i = tid; i < nv; i += FNT) {
+                    const float v = sm.ub.tmax_all[i];
+                    if (finite_f(v)) atomicAdd(&sm.ua.s.sel.hist[min(2047u, (uint32_t)((v - lo_v) * sc))], 1u);
                 }
                 __syncthreads();
                 {
-                    // walk from the top bucket down: warp w owns buckets 2047-64w .. 2047-64w-63 (two per lane)
-                    const int w = tid >> 5, lane = tid & 31;
-                    const uint32_t h0v = sm.sel.hist[2047 - 64 * w - 2 * lane];
-                    const uint32_t h1v = sm.sel.hist[2047 - 64 * w - 2 * lane - 1];
-                    uint32_t inc = h0v + h1v;
+                    // walk from the top bucket down: thread j owns the BPT buckets 2047 - j*BPT - u, u < BPT
+                    constexpr int BPT = 2048 / FNT;
+                    uint32_t hv[BPT], own = 0;
+#pragma unroll
+                    for (int u = 0; u < BPT; u++) { hv[u] = sm.ua.s.sel.hist[2047 - tid * BPT - u]; own += hv[u]; }
+                    uint32_t inc = own;
                     for (int o = 1; o < 32; o <<= 1) {
                         const uint32_t up = __shfl_up_sync(FULL, inc, o);
                         if (lane >= o) inc += up;
                     }
-                    if (lane == 31) sm.rs.u[w] = inc;
+                    if (lane == 31) sm.walk[w] = inc;
                     __syncthreads();
-                    uint32_t above = 0;
-                    for (int ww = 0; ww < w; ww++) above += sm.rs.u[ww];
-                    const uint32_t before_me = above + inc - h0v - h1v;   // maxima in higher buckets
-                    if (before_me < top_k && before_me + h0v >= top_k) {
-                        sm.sel.prefix = 2047 - 64 * w - 2 * lane; sm.sel.k = top_k - before_me;
-                    } else if (before_me + h0v < top_k && before_me + h0v + h1v >= top_k) {
-                        sm.sel.prefix = 2047 - 64 * w - 2 * lane - 1; sm.sel.k = top_k - before_me - h0v;
+                    uint32_t before = inc - own;   // maxima in higher buckets
+                    for (int ww = 0; ww < w; ww++) before += sm.walk[ww];
+#pragma unroll
+                    for (int u = 0; u < BPT; u++) {
+                        if (before < top_k && before + hv[u] >= top_k) {
+                            sm.ua.s.sel.prefix = 2047 - tid * BPT - u; sm.ua.s.sel.k = top_k - before;
+                        }
+                        before += hv[u];
                     }
                 }
                 __syncthreads();
-                const uint32_t bsel = sm.sel.prefix, ksel = sm.sel.k;
+                const uint32_t bsel = sm.ua.s.sel.prefix, ksel = sm.ua.s.sel.k;
                 // members of the selected bucket -> cand_x (reused as scratch, at most F_LCAP of them)
-                for (uint32_t i = tid; i < nv; i += NT) {
-                    const float v = sm.tmax_all[i];
+                for (uint32_t i = tid; i < nv; i += FNT) {
+                    const float v = sm.ub.tmax_all[i];
                     if (finite_f(v) && min(2047u, (uint32_t)((v - lo_v) * sc)) == bsel) {
-                        const uint32_t at = atomicAdd(&sm.cand_n, 1u);
-                        if (at < (uint32_t)F_LCAP) sm.cand_x[at] = v;
+                        const uint32_t at = atomicAdd(&sm.memb_n, 1u);
+                        if (at < (uint32_t)F_LCAP) sm.ua.s.members[at] = v;
                     }
                 }
-                if (tid == 0) sm.sel.hist[0] = 0u;   // reused: order key of the bound
+                if (tid == 0) sm.ua.s.sel.hist[0] = 0u;   // reused: order key of the bound
                 __syncthreads();
-                const uint32_t nm = sm.cand_n;
+                const uint32_t nm = sm.memb_n;
                 if (nm <= (uint32_t)F_LCAP) {
-                    for (uint32_t j = tid; j < nm; j += NT) {
-                        const float v = sm.cand_x[j];
+                    for (uint32_t j = tid; j < nm; j += FNT) {
+                        const float v = sm.ua.s.members[j];
                         uint32_t gt = 0, ge = 0;
-                        for (uint32_t o = 0; o < nm; o++) { gt += sm.cand_x[o] > v; ge += sm.cand_x[o] >= v; }
-                        if (gt < ksel && ksel <= ge) sm.sel.hist[0] = order_key(v);
+                        for (uint32_t o = 0; o < nm; o++) { gt += sm.ua.s.members[o] > v; ge += sm.ua.s.members[o] >= v; }
+                        if (gt < ksel && ksel <= ge) sm.ua.s.sel.hist[0] = order_key(v);
                     }
                 } else {
                     // too many equal-bucket maxima: any member bounds the k-th largest from below
-                    if (tid == 0) sm.sel.hist[0] = order_key(lo_v);
+                    if (tid == 0) sm.ua.s.sel.hist[0] = order_key(lo_v);
                 }
                 __syncthreads();
-                const uint32_t kk = sm.sel.hist[0];
+                const uint32_t kk = sm.ua.s.sel.hist[0];
                 if (kk) {
                     const float bound = key_to_float(kk);
                     // every logit whose probability could still tie with the k-th one stays above the cut
@@ -554,72 +695,74 @@ __global__ void __launch_bounds__(NT, 1) fused_row_kernel(const RowArgs a, const
                 }
             }
         }
-        PGS_TICK(4);   // select
-        __syncthreads();
-        if (tid == 0) sm.cand_n = 0;
-        __syncthreads();
+        PGS_TICK(4);   // select (no barrier needed here: the maxima were last read before a barrier above)
         // ---- one pass in chunk order: collect the candidates, then overwrite each logit with its
         //      softmax numerator (hardware exp2) and accumulate the plain chunk sum
-        // log2(e) / t as a two-float sum, so that the exponent's argument carries no systematic error
-        const double scale_d = 1.4426950408889634 / (double)t;
-        const float s_hi = (float)scale_d, s_lo2 = (float)((scale_d - (double)(float)scale_d) * 0.6931471805599453);
+        const float s_hi = ctl.s_hi, s_lo = ctl.s_lo;   // log2(e) / t as a two-float sum
         const float cut_f = fmaxf(cut, -3.4e38f);   // masked entries (-inf) are never candidates
         const uint32_t L = fl.chunk;   // 4 * odd: 128-bit shared-memory accesses of a warp do not collide
         const uint32_t c0 = min(len, tid * L), c1 = min(len, c0 + L);
         const uint32_t c1b = c0 + ((c1 - c0) & ~3u);   // whole 128-bit groups; a remainder only at the ragged end
         float csum = 0.0f;
-        // candidate test, then 2^((x - m) * log2(e) / t): hardware exp2 of the product with the rounded
-        // scale, times (1 + ln2 * the part of the scale that rounding dropped), which removes the
-        // systematic error; the clamp keeps masked entries (-inf) finite so that they come out as +0
-        auto numerator = [&](float x, uint32_t i) -> float {
+        auto candidate = [&](float x, uint32_t i) {
             if (x >= cut_f) {
                 const uint32_t at = atomicAdd(&sm.cand_n, 1u);
-                if (at < (uint32_t)F_LCAP) { sm.cand_id[at] = lo + i; sm.cand_x[at] = x; }
+                if (at < (uint32_t)F_LCAP) { sm.ub.c.id[at] = lo + i; sm.ub.c.x[at] = x; }
             }
-            const float a_ = fmaxf(fsub(x, m), -1e30f);
-            const float e2 = ex2_approx(fmul(a_, s_hi));
-            return __fmaf_rn(e2, fmul(a_, s_lo2), e2);
         };
-        for (uint32_t i = c0; i < c1b; i += 4) {
-            float4 v = *reinterpret_cast<const float4*>(X + i);
-            v.x = numerator(v.x, i); v.y = numerator(v.y, i + 1); v.z = numerator(v.z, i + 2); v.w = numerator(v.w, i + 3);
+        // 2^((x - m) * log2(e) / t) by the hardware exp2 (a few ulp; results below the normal range are
+        // flushed to zero, far below anything the sum can see)
+        auto numerator = [&](float x) -> float {
+            const float a_ = fsub(x, m);
+            return ex2_approx_ftz(__fmaf_rn(a_, s_hi, fmul(a_, s_lo)));
+        };
+        auto group = [&](float4 v, uint32_t i) -> float {
+            if (fmaxf(fmaxf(v.x, v.y), fmaxf(v.z, v.w)) >= cut_f) {
+                candidate(v.x, i); candidate(v.y, i + 1); candidate(v.z, i + 2); candidate(v.w, i + 3);
+            }
+            v.x = numerator(v.x); v.y = numerator(v.y); v.z = numerator(v.z); v.w = numerator(v.w);
             *reinterpret_cast<float4*>(X + i) = v;
-            csum += (v.x + v.y) + (v.z + v.w);
+            return (v.x + v.y) + (v.z + v.w);
+        };
+        uint32_t ib = c0;
+        for (; ib + 8 <= c1b; ib += 8) {   // two groups per round, both requested before either is used
+            const float4 v0 = *reinterpret_cast<const float4*>(X + ib);
+            const float4 v1 = *reinterpret_cast<const float4*>(X + ib + 4);
+            const float g0 = group(v0, ib), g1 = group(v1, ib + 4);
+            csum += g0 + g1;
         }
-        for (uint32_t i = c1b; i < c1; i++) { const float e = numerator(X[i], i); X[i] = e; csum += e; }
-        __syncthreads();
-        const uint32_t my_n = sm.cand_n;
+        if (ib < c1b) csum += group(*reinterpret_cast<const float4*>(X + ib), ib);
+        for (uint32_t i = c1b; i < c1; i++) { candidate(X[i], i); const float e = numerator(X[i]); X[i] = e; csum += e; }
         PGS_TICK(5);   // gather + exp
-        const float pre0 = block_excl_scan_f32(csum, sm.rs);
-        if (tid == NT - 1) sm.dscan[0] = (double)pre0 + (double)csum;
-        __syncthreads();
-        const double dtot = sm.dscan[0];
+        float ftot0;
+        const float pre0 = fblock_excl_scan_f32(csum, &ftot0, sm.scan_sum);
+        const double dtot = (double)ftot0;
+        const uint32_t my_n = sm.cand_n;   // complete: the scan's barrier is behind every thread's pass
         PGS_TICK(6);   // scan
         // ------------------------------------------------ cluster exchange #2
-        for (uint32_t r = tid; r < C; r += NT) {
+        for (uint32_t r = tid; r < C; r += FNT) {
             FusedSmem* peer = cluster.map_shared_rank(&sm, r);
             peer->xchg[pbuf].ncand[rank] = my_n;
             peer->xchg[pbuf].true_total[rank] = (float)dtot;
         }
         cluster.sync();
         PGS_TICK(7);   // sync 2
-        uint32_t cand_off = 0, cand_total = 0;
-        double before0 = 0.0;
-        bool overflow = false;
-        for (uint32_t r = 0; r < C; r++) {
-            if (r < rank) { cand_off += xc.ncand[r]; before0 += (double)xc.true_total[r]; }
-            cand_total += xc.ncand[r];
-            overflow |= xc.ncand[r] > (uint32_t)F_LCAP;
-        }
+        const uint32_t rn = (uint32_t)lane < C ? xc.ncand[lane] : 0u;
+        const uint32_t cand_total = __reduce_add_sync(FULL, rn);
+        const uint32_t cand_off = __reduce_add_sync(FULL, (uint32_t)lane < rank ? rn : 0u);
+        bool overflow = __reduce_max_sync(FULL, rn) > (uint32_t)F_LCAP;
+        // ranks below this one; every group of F_MAXC lanes adds up the same values
+        double before0 = (uint32_t)(lane % F_MAXC) < rank ? (double)xc.true_total[lane % F_MAXC] : 0.0;
+        for (int o = F_MAXC / 2; o; o >>= 1) before0 += __shfl_xor_sync(FULL, before0, o);
         overflow |= cand_total > (uint32_t)F_MCAP;
         if (overflow) {   // identical decision in every CTA
             if (writer) { fl.work_rows[atomicAdd(fl.work_count, 1u)] = row; fl.recs[row].kind = 0; }
             continue;
         }
         // candidates -> global memory, in slice order, for the finish kernel
-        for (uint32_t j = tid; j < my_n; j += NT) {
-            fl.cand_id[(size_t)row * F_MCAP + cand_off + j] = sm.cand_id[j];
-            fl.cand_x[(size_t)row * F_MCAP + cand_off + j] = sm.cand_x[j];
+        for (uint32_t j = tid; j < my_n; j += FNT) {
+            fl.cand_id[(size_t)row * F_MCAP + cand_off + j] = sm.ub.c.id[j];
+            fl.cand_x[(size_t)row * F_MCAP + cand_off + j] = sm.ub.c.x[j];
         }
         // ---------- the sequential fold, chunk by chunk: first from the plain prefix sums ...
         const float start0 = (float)before0 + pre0;
@@ -633,16 +776,14 @@ __global__ void __launch_bounds__(NT, 1) fused_row_kernel(const RowArgs a, const
         };
         float acc = fold_chunk(start0);
         const float inc1 = fsub(acc, start0);   // exact: both ends lie within a factor two or the chunk is re-folded
-        const float pre1 = block_excl_scan_f32(inc1, sm.rs);
-        __syncthreads();
-        if (tid == NT - 1) sm.dscan[0] = (double)pre1 + (double)inc1;
-        __syncthreads();
-        const double tot1 = sm.dscan[0];
+        float ftot1;
+        const float pre1 = fblock_excl_scan_f32(inc1, &ftot1, sm.scan_fold);
+        const double tot1 = (double)ftot1;
         PGS_TICK(8);   // fold 1
-        for (uint32_t r = tid; r < C; r += NT) cluster.map_shared_rank(&sm, r)->xchg[pbuf].fold1[rank] = tot1;
+        for (uint32_t r = tid; r < C; r += FNT) cluster.map_shared_rank(&sm, r)->xchg[pbuf].fold1[rank] = tot1;
         cluster.sync();   // exchange #3
-        double before1 = 0.0;
-        for (uint32_t r = 0; r < rank; r++) before1 += xc.fold1[r];
+        double before1 = (uint32_t)(lane % F_MAXC) < rank ? xc.fold1[lane % F_MAXC] : 0.0;
+        for (int o = F_MAXC / 2; o; o >>= 1) before1 += __shfl_xor_sync(FULL, before1, o);
         // ... then once more, for the chunks whose binade that first pass got wrong or crossed
         const float start1 = (float)before1 + pre1;
         const uint32_t e0 = f2u(start0) & 0x7f800000u;
@@ -652,17 +793,19 @@ __global__ void __launch_bounds__(NT, 1) fused_row_kernel(const RowArgs a, const
             inc2 = (double)acc - (double)start1;
         }
         for (int o = 16; o; o >>= 1) inc2 += __shfl_xor_sync(FULL, inc2, o);
-        if ((tid & 31) == 0) fl.recs[row].part[rank * NW + (tid >> 5)] = inc2;   // the finish kernel adds the warps up
+        if (lane == 0) fl.recs[row].part[rank * FNW + w] = inc2;   // the finish kernel adds the warps up
         if (writer) {
             RowRec& rec = fl.recs[row];
             rec.kind = 1; rec.n_cand = cand_total; rec.amax = amax; rec.status = status;
-            rec.m = m; rec.t = t; rec.n_parts = C * NW;
+            rec.m = m; rec.t = t; rec.n_parts = C * FNW;
         }
         PGS_TICK(9);   // fold 2
     }
     // no CTA may exit while a peer can still write into its shared memory
     cluster.sync();
 }
+
+uint32_t fused_threads() { return FNT; }
 
 size_t fused_smem_bytes(uint32_t slice_len) {
     return ((sizeof(FusedSmem) + 15) & ~size_t(15)) + (size_t)slice_len * sizeof(float);
@@ -671,14 +814,22 @@ size_t fused_smem_bytes(uint32_t slice_len) {
 cudaError_t configure_fused(size_t max_smem) {
     cudaError_t e = cudaFuncSetAttribute(fused_row_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)max_smem);
     if (e != cudaSuccess) return e;
+    e = cudaFuncSetAttribute(fused_row_kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
+                             cudaSharedmemCarveoutMaxShared);
+    if (e != cudaSuccess) return e;
     return cudaFuncSetAttribute(fused_row_kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 0);
+}
+
+// how many CTAs with `smem` bytes each one SM can hold
+cudaError_t fused_ctas_per_sm(size_t smem, int* out) {
+    return cudaOccupancyMaxActiveBlocksPerMultiprocessor(out, fused_row_kernel, FNT, smem);
 }
 
 // how many clusters of `cluster` CTAs with `smem` bytes each can be resident at once
 cudaError_t fused_max_clusters(uint32_t cluster, size_t smem, int* out) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(cluster, 1, 1);
-    cfg.blockDim = dim3(NT, 1, 1);
+    cfg.blockDim = dim3(FNT, 1, 1);
     cfg.dynamicSmemBytes = smem;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -691,7 +842,7 @@ cudaError_t launch_fused(const RowArgs& a, const FusedLaunch& fl, uint32_t n_clu
                          cudaStream_t stream) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(n_clusters * fl.cluster, 1, 1);
-    cfg.blockDim = dim3(NT, 1, 1);
+    cfg.blockDim = dim3(FNT, 1, 1);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = stream;
     cudaLaunchAttribute attr[1];

@@ -136,6 +136,12 @@ __device__ __forceinline__ float ex2_approx(float x) {
     asm("ex2.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
 }
+// same, results below the normal range flushed to zero: a single hardware instruction
+__device__ __forceinline__ float ex2_approx_ftz(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
 #endif
 
 // Monotone map float -> uint32 (larger float = larger key).  Non-finite values get key 0, below
