@@ -336,6 +336,7 @@ bool fused_shape(pgs_handle* h, uint32_t vocab) {
             const uint32_t chunk = groups * 4u;
             h->fused_cluster = c; h->fused_slice = slice; h->fused_chunk = chunk; h->fused_smem = smem;
             h->fused_clusters = (uint32_t)n;
+            if (const char* ev = getenv("PGS_XX_MAXC")) h->fused_clusters = atoi(ev);  // XXTMP
             return true;
         }
     }

@@ -88,17 +88,18 @@ struct FusedSmem {
     float tmax_s[FVT];              // each virtual thread's maximum after the load pass
     uint8_t redo_max[FVT];
     uint32_t cand_n, memb_n, bound_key;
+    long long prof_acc[16];         // phase timers of thread 0
     uint32_t hash_dirty;            // the id -> count table holds leftovers and must be reset before use
     unsigned long long load_bar[8]; // one mbarrier per 32 KB piece of the bulk copy that fills the slice
 };
 
-// Optional phase timers (clock64 deltas of thread 0, summed over the rows of each CTA), enabled
-// by pointing `prof` at [gridDim.x x 16] counters.
+// Optional phase timers (clock64 deltas of thread 0, summed over the rows of each CTA in shared memory and
+// written out when the CTA is done), enabled by pointing `prof` at [gridDim.x x 16] counters.
 #define PGS_TICK(slot)                                              \
     do {                                                            \
         if (fl.prof && tid == 0) {                                  \
             const long long now_ = clock64();                       \
-            fl.prof[blockIdx.x * 16 + (slot)] += now_ - tick_;      \
+            sm.prof_acc[slot] += now_ - tick_;                      \
             tick_ = now_;                                           \
         }                                                           \
     } while (0)
@@ -167,6 +168,7 @@ __device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t by
 // Bounded wait for phase `parity` of the barrier: false when the copy has not landed after 2^16 tries
 // (each try may park the thread for up to 20 us, so the bound is about a second).
 __device__ __forceinline__ bool mbar_wait(unsigned long long* bar, uint32_t parity) {
+#pragma unroll 1
     for (uint32_t spin = 0; spin < (1u << 16); spin++) {
         uint32_t ok;
         asm volatile(
@@ -182,10 +184,206 @@ __device__ __forceinline__ bool mbar_wait(unsigned long long* bar, uint32_t pari
 }
 constexpr uint32_t TMA_PIECE = 32768;   // bytes per bulk copy
 
+// Top-k bound from all per-thread maxima (used when top_k is too large for the warp maxima): the C*FVT
+// maxima are spread over 2048 equal-width buckets between their smallest finite value and the row maximum
+// (a monotone map), the bucket holding the k-th largest is found from the histogram, and the exact value
+// is picked among that bucket's few members.  Returns the bound's order key, 0 if fewer than top_k maxima
+// are finite.  Called by every thread of the CTA.
+__device__ __forceinline__ uint32_t thread_bound_key(FusedSmem& sm, uint32_t C, uint32_t top_k, float m) {
+    const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
+    if (tid == 0) sm.hash_dirty = 1u;   // the histogram below lives in the table's space
+    const uint32_t nv = C * FVT;
+    uint32_t fin = 0;
+    unsigned long long inv_min = 0ull;
+#pragma unroll 1
+    for (uint32_t i = tid; i < nv; i += FNT) {
+        const uint32_t key = order_key(sm.ub.tmax_all[i]);
+        if (key) { fin++; const unsigned long long iv = 0xffffffffull - key; inv_min = iv > inv_min ? iv : inv_min; }
+    }
+    const uint32_t n_fin = fblock_sum_u32(fin, sm.red_fin);
+    inv_min = fblock_max_u64(inv_min, sm.red_min);
+    if (n_fin < top_k) return 0u;
+    const float lo_v = key_to_float((uint32_t)(0xffffffffull - inv_min));
+    const float sc = m > lo_v ? 2047.0f / (m - lo_v) : 0.0f;
+#pragma unroll 1
+    for (int bkt = tid; bkt < 2048; bkt += FNT) sm.ua.s.sel.hist[bkt] = 0u;
+    if (tid == 0) { sm.ua.s.sel.prefix = 0xffffffffu; sm.ua.s.sel.k = 0u; sm.memb_n = 0u; }
+    __syncthreads();
+#pragma unroll 1
+    for (uint32_t i = tid; i < nv; i += FNT) {
+        const float v = sm.ub.tmax_all[i];
+        if (finite_f(v)) atomicAdd(&sm.ua.s.sel.hist[min(2047u, (uint32_t)((v - lo_v) * sc))], 1u);
+    }
+    __syncthreads();
+    {
+        // walk from the top bucket down: thread j owns the BPT buckets 2047 - j*BPT - u, u < BPT
+        constexpr int BPT = 2048 / FNT;
+        uint32_t hv[BPT], own = 0;
+#pragma unroll
+        for (int u = 0; u < BPT; u++) { hv[u] = sm.ua.s.sel.hist[2047 - tid * BPT - u]; own += hv[u]; }
+        uint32_t inc = own;
+        for (int o = 1; o < 32; o <<= 1) {
+            const uint32_t up = __shfl_up_sync(FULL, inc, o);
+            if (lane >= o) inc += up;
+        }
+        if (lane == 31) sm.walk[w] = inc;
+        __syncthreads();
+        uint32_t before = inc - own;   // maxima in higher buckets
+#pragma unroll 1
+        for (int ww = 0; ww < w; ww++) before += sm.walk[ww];
+#pragma unroll
+        for (int u = 0; u < BPT; u++) {
+            if (before < top_k && before + hv[u] >= top_k) {
+                sm.ua.s.sel.prefix = 2047 - tid * BPT - u; sm.ua.s.sel.k = top_k - before;
+            }
+            before += hv[u];
+        }
+    }
+    __syncthreads();
+    const uint32_t bsel = sm.ua.s.sel.prefix, ksel = sm.ua.s.sel.k;
+    // members of the selected bucket (at most F_LCAP of them are kept)
+#pragma unroll 1
+    for (uint32_t i = tid; i < nv; i += FNT) {
+        const float v = sm.ub.tmax_all[i];
+        if (finite_f(v) && min(2047u, (uint32_t)((v - lo_v) * sc)) == bsel) {
+            const uint32_t at = atomicAdd(&sm.memb_n, 1u);
+            if (at < (uint32_t)F_LCAP) sm.ua.s.members[at] = v;
+        }
+    }
+    if (tid == 0) sm.ua.s.sel.hist[0] = 0u;   // reused: order key of the bound
+    __syncthreads();
+    const uint32_t nm = sm.memb_n;
+    if (nm <= (uint32_t)F_LCAP) {
+#pragma unroll 1
+        for (uint32_t j = tid; j < nm; j += FNT) {
+            const float v = sm.ua.s.members[j];
+            uint32_t gt = 0, ge = 0;
+#pragma unroll 1
+            for (uint32_t o = 0; o < nm; o++) { gt += sm.ua.s.members[o] > v; ge += sm.ua.s.members[o] >= v; }
+            if (gt < ksel && ksel <= ge) sm.ua.s.sel.hist[0] = order_key(v);
+        }
+    } else {
+        // too many equal-bucket maxima: any member bounds the k-th largest from below
+        if (tid == 0) sm.ua.s.sel.hist[0] = order_key(lo_v);
+    }
+    __syncthreads();
+    return sm.ua.s.sel.hist[0];
+}
+
+// One more top-k candidate of this slice (rare next to the logits that are not)
+__device__ __forceinline__ void add_candidate(FusedSmem& sm, uint32_t id, float x) {
+    const uint32_t at = atomicAdd(&sm.cand_n, 1u);
+    if (at < (uint32_t)F_LCAP) { sm.ub.c.id[at] = id; sm.ub.c.x[at] = x; }
+}
+
+// The sequential f32 fold of one chunk of numerators from a given running value (the refinement pass;
+// the first pass has its own inlined copy)
+__device__ __forceinline__ float refold_chunk(const float* X, uint32_t c0, uint32_t c1b, uint32_t c1, float acc) {
+#pragma unroll 1
+    for (uint32_t i = c0; i < c1b; i += 4) {
+        const float4 v = *reinterpret_cast<const float4*>(X + i);
+        acc = fadd(fadd(fadd(fadd(acc, v.x), v.y), v.z), v.w);
+    }
+#pragma unroll 1
+    for (uint32_t i = c1b; i < c1; i++) acc = fadd(acc, X[i]);
+    return acc;
+}
+
+// Per-thread result of a load pass: the maximum of each virtual thread, where it sits, and the sanity bit
+struct ThreadMax { float tm[VG]; uint32_t tq[VG]; int nonfinite; };
+
+// bf16 rows: 64-bit coalesced loads, widened to f32 in shared memory (a 16-bit shift: exact), with the
+// sanity check, the grammar mask and the per-thread maxima on the way.  Covers the whole 128-bit groups of the
+// slice.
+__device__ __forceinline__ ThreadMax load_bf16_body(float* X, const char* rowp, const uint32_t* mw, uint32_t lo, uint32_t nq) {
+    const int tid = threadIdx.x;
+    ThreadMax r;
+#pragma unroll
+    for (int g = 0; g < VG; g++) { r.tm[g] = -INFINITY; r.tq[g] = 0u; }
+    r.nonfinite = 0;
+    const uint2* src = (const uint2*)(rowp) + lo / 4;    // 4 bf16 per 8-byte load
+#pragma unroll 1
+    for (uint32_t q0 = tid; q0 < nq; q0 += 4 * FNT) {
+        uint2 raw[4];
+#pragma unroll
+        for (int u = 0; u < 4; u++)
+            if (q0 + u * FNT < nq) raw[u] = __ldcs(src + q0 + u * FNT);
+#pragma unroll
+        for (int u = 0; u < 4; u++)
+            if (q0 + u * FNT < nq) {
+                const uint32_t q = q0 + u * FNT;
+                const int g = u % VG;   // q0 - tid is a multiple of 4 * FNT
+                float4 v;
+                v.x = __uint_as_float(raw[u].x << 16); v.y = __uint_as_float(raw[u].x & 0xffff0000u);
+                v.z = __uint_as_float(raw[u].y << 16); v.w = __uint_as_float(raw[u].y & 0xffff0000u);
+                r.nonfinite |= !finite_f(v.x) | !finite_f(v.y) | !finite_f(v.z) | !finite_f(v.w);
+                if (mw) {
+                    const uint32_t bits = __ldg(mw + ((lo >> 5) + (q >> 3))) >> ((q & 7) * 4);
+                    if (!(bits & 1u)) v.x = -INFINITY;
+                    if (!(bits & 2u)) v.y = -INFINITY;
+                    if (!(bits & 4u)) v.z = -INFINITY;
+                    if (!(bits & 8u)) v.w = -INFINITY;
+                }
+                const float m4 = fmaxf(fmaxf(v.x, v.y), fmaxf(v.z, v.w));
+                if (m4 > r.tm[g]) { r.tm[g] = m4; r.tq[g] = q * 4; }
+                ((float4*)X)[q] = v;
+            }
+    }
+    return r;
+}
+
 __device__ __forceinline__ uint32_t load_owner(uint32_t i, uint32_t len) {
     // thread that loaded slice element i: 128-bit groups are dealt round-robin, then the ragged tail
     const uint32_t body = (len / 4) * 4;
     return i < body ? ((i >> 2) & (FVT - 1)) : ((i - body) & (FVT - 1));
+}
+
+// One thread reads and validates a row's parameters (same rules as the general kernel).
+__device__ __forceinline__ void prepare_row(const RowArgs& a, uint32_t row, RowCtl& c) {
+const uint32_t V = a.vocab;
+    const float temp = a.temperature ? a.temperature[row] : 0.0f;
+    const uint32_t top_k = a.top_k ? a.top_k[row] : 0u;
+    const float top_p = a.top_p ? a.top_p[row] : 1.0f;
+    const float freq = a.freq ? a.freq[row] : 0.0f;
+    const float pres = a.pres ? a.pres[row] : 0.0f;
+    const float rep = a.rep ? a.rep[row] : 1.0f;
+    const float u01 = a.uniform ? a.uniform[row] : 0.0f;
+    bool bad = !finite_f(temp) || !finite_f(top_p) || !finite_f(freq) || !finite_f(pres) ||
+               !finite_f(rep) || !(rep > 0.0f) || !finite_f(u01);
+    const uint32_t* mw = nullptr;
+    uint32_t gflags = 0;
+    if (a.mask_table && a.mask_table[row] >= 0) {
+        const int32_t t = a.mask_table[row];
+        const int32_t st = a.mask_state ? a.mask_state[row] : 0;
+        if (t >= MAX_TABLES || !a.tables[t].live || st < 0 || (uint32_t)st >= a.tables[t].n_states ||
+            (unsigned long long)a.tables[t].words_per_state * 32ull < V) {
+            bad = true;
+        } else {
+            mw = a.tables[t].words + (size_t)st * a.tables[t].words_per_state;
+            gflags = a.tables[t].flags[st];
+        }
+    }
+    uint32_t h0 = 0, nh = 0;
+    if (a.hist_offsets) {
+        h0 = a.hist_offsets[row];
+        const uint32_t h1 = a.hist_offsets[row + 1];
+        if (h1 < h0 || h1 - h0 > a.max_history) bad = true; else nh = h1 - h0;
+    }
+    const bool greedy = temp < 1e-5f;
+    const bool use_k = top_k != 0u && top_k < V;
+    // rows this kernel does not serve go to the general kernel
+    const char* rowp = (const char*)a.logits + (size_t)row * a.row_stride * (a.dtype == 0 ? 4 : 2);
+    const bool aligned = (((uintptr_t)rowp & 15) == 0);
+    const bool defer = !aligned || (!greedy && (!use_k || top_k > (uint32_t)F_KMAX));
+    // log2(e) / t as a two-float sum s_hi + s_lo with s_lo > 0, so that the exponent's argument carries
+    // no systematic error and a masked entry (-inf) stays -inf through both products
+    const double scale_d = 1.4426950408889634 / (double)fmaxf(temp, 1e-9f);
+    float s_hi = (float)scale_d;
+    if ((double)s_hi >= scale_d) s_hi = u2f(f2u(s_hi) - 1u);
+    c.s_hi = s_hi; c.s_lo = (float)(scale_d - (double)s_hi);
+    c.rowp = rowp; c.mw = mw; c.temp = temp; c.freq = freq; c.pres = pres; c.rep = rep;
+    c.top_k = top_k; c.gflags = gflags; c.h0 = h0; c.nh = nh;
+    c.kind = bad ? 1u : defer ? 2u : 0u;
 }
 
 __global__ void __launch_bounds__(FNT, 2) fused_row_kernel(const RowArgs a, const FusedLaunch fl) {
@@ -205,59 +403,16 @@ __global__ void __launch_bounds__(FNT, 2) fused_row_kernel(const RowArgs a, cons
     uint32_t load_phase = 0;        // parity of the next completion of load_bar
     bool poisoned = false;          // a bulk copy never landed: later rows of this CTA report that too
     if (tid == 0) {
+#pragma unroll 1
+        for (int i = 0; i < 16; i++) sm.prof_acc[i] = 0;
         sm.hash_dirty = 1u;
+#pragma unroll 1
         for (int b = 0; b < 8; b++) mbar_init(&sm.load_bar[b], 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
-    // one thread reads and validates a row's parameters (same rules as the general kernel)
-    auto prepare = [&](uint32_t row, RowCtl& c) {
-        const float temp = a.temperature ? a.temperature[row] : 0.0f;
-        const uint32_t top_k = a.top_k ? a.top_k[row] : 0u;
-        const float top_p = a.top_p ? a.top_p[row] : 1.0f;
-        const float freq = a.freq ? a.freq[row] : 0.0f;
-        const float pres = a.pres ? a.pres[row] : 0.0f;
-        const float rep = a.rep ? a.rep[row] : 1.0f;
-        const float u01 = a.uniform ? a.uniform[row] : 0.0f;
-        bool bad = !finite_f(temp) || !finite_f(top_p) || !finite_f(freq) || !finite_f(pres) ||
-                   !finite_f(rep) || !(rep > 0.0f) || !finite_f(u01);
-        const uint32_t* mw = nullptr;
-        uint32_t gflags = 0;
-        if (a.mask_table && a.mask_table[row] >= 0) {
-            const int32_t t = a.mask_table[row];
-            const int32_t st = a.mask_state ? a.mask_state[row] : 0;
-            if (t >= MAX_TABLES || !a.tables[t].live || st < 0 || (uint32_t)st >= a.tables[t].n_states ||
-                (unsigned long long)a.tables[t].words_per_state * 32ull < V) {
-                bad = true;
-            } else {
-                mw = a.tables[t].words + (size_t)st * a.tables[t].words_per_state;
-                gflags = a.tables[t].flags[st];
-            }
-        }
-        uint32_t h0 = 0, nh = 0;
-        if (a.hist_offsets) {
-            h0 = a.hist_offsets[row];
-            const uint32_t h1 = a.hist_offsets[row + 1];
-            if (h1 < h0 || h1 - h0 > a.max_history) bad = true; else nh = h1 - h0;
-        }
-        const bool greedy = temp < 1e-5f;
-        const bool use_k = top_k != 0u && top_k < V;
-        // rows this kernel does not serve go to the general kernel
-        const char* rowp = (const char*)a.logits + (size_t)row * a.row_stride * (a.dtype == 0 ? 4 : 2);
-        const bool aligned = (((uintptr_t)rowp & 15) == 0);
-        const bool defer = !aligned || (!greedy && (!use_k || top_k > (uint32_t)F_KMAX));
-        // log2(e) / t as a two-float sum s_hi + s_lo with s_lo > 0, so that the exponent's argument carries
-        // no systematic error and a masked entry (-inf) stays -inf through both products
-        const double scale_d = 1.4426950408889634 / (double)fmaxf(temp, 1e-9f);
-        float s_hi = (float)scale_d;
-        if ((double)s_hi >= scale_d) s_hi = u2f(f2u(s_hi) - 1u);
-        c.s_hi = s_hi; c.s_lo = (float)(scale_d - (double)s_hi);
-        c.rowp = rowp; c.mw = mw; c.temp = temp; c.freq = freq; c.pres = pres; c.rep = rep;
-        c.top_k = top_k; c.gflags = gflags; c.h0 = h0; c.nh = nh;
-        c.kind = bad ? 1u : defer ? 2u : 0u;
-    };
     constexpr int PREP_TID = FNT - 32;   // lane 0 of the last warp
-    if (tid == PREP_TID && cluster_id < a.rows) prepare(cluster_id, sm.ctl[0]);
+    if (tid == PREP_TID && cluster_id < a.rows) prepare_row(a, cluster_id, sm.ctl[0]);
     long long tick_ = clock64();
     uint32_t it = 0;
     for (uint32_t row = cluster_id; row < a.rows; row += n_clusters, it++) {
@@ -267,7 +422,7 @@ __global__ void __launch_bounds__(FNT, 2) fused_row_kernel(const RowArgs a, cons
         const uint32_t pbuf = parity;   // exchange buffer of this row; the next synced row takes the other one
         PGS_TICK(12);  // row barrier
         const RowCtl& ctl = sm.ctl[it & 1];
-        if (tid == PREP_TID && row + n_clusters < a.rows) prepare(row + n_clusters, sm.ctl[(it + 1) & 1]);
+        if (tid == PREP_TID && row + n_clusters < a.rows) prepare_row(a, row + n_clusters, sm.ctl[(it + 1) & 1]);
         const bool writer = rank == 0 && tid == 0;
         if (ctl.kind == 1u) {
             if (writer) { a.token[row] = 0; a.status[row] = ROW_BAD_PARAM; if (a.drew) a.drew[row] = 0; fl.recs[row].kind = 0; }
@@ -291,19 +446,6 @@ __global__ void __launch_bounds__(FNT, 2) fused_row_kernel(const RowArgs a, cons
         if (tid == 0) sm.cand_n = 0u;
         int nonfinite = 0;
         const uint32_t nq = len / 4;   // 128-bit groups; a ragged tail exists only in the last slice
-        auto take4 = [&](uint32_t q, float4 v, int g) {
-            nonfinite |= !finite_f(v.x) | !finite_f(v.y) | !finite_f(v.z) | !finite_f(v.w);
-            if (mw) {
-                const uint32_t bits = __ldg(mw + ((lo >> 5) + (q >> 3))) >> ((q & 7) * 4);
-                if (!(bits & 1u)) v.x = -INFINITY;
-                if (!(bits & 2u)) v.y = -INFINITY;
-                if (!(bits & 4u)) v.z = -INFINITY;
-                if (!(bits & 8u)) v.w = -INFINITY;
-            }
-            const float m4 = fmaxf(fmaxf(v.x, v.y), fmaxf(v.z, v.w));
-            if (m4 > tm[g]) { tm[g] = m4; tqs[g] = q * 4; }
-            ((float4*)X)[q] = v;
-        };
         auto take1 = [&](uint32_t i, float x) {
             nonfinite |= !finite_f(x);
             if (mw && !((__ldg(mw + ((lo + i) >> 5)) >> ((lo + i) & 31)) & 1u)) x = -INFINITY;
@@ -323,15 +465,18 @@ __global__ void __launch_bounds__(FNT, 2) fused_row_kernel(const RowArgs a, cons
             // the penalty pass hands every slot back empty, so a reset is only needed after a row that left
             // entries behind or used the space for something else
             if (sm.hash_dirty) {
+#pragma unroll 1
                 for (int s = tid; s < F_HASH; s += FNT) { sm.ua.pen.hkey[s] = 0xffffffffu; sm.ua.pen.hcnt[s] = 0u; }
                 __syncthreads();
                 if (tid == 0) sm.hash_dirty = 0u;
             }
+#pragma unroll 1
             for (uint32_t j = tid; j < nh; j += FNT) {
                 const uint32_t id = j == (uint32_t)tid ? hid0 : __ldg(a.hist_ids + h0 + j);
                 if (id < lo || id >= hi) continue;
                 uint32_t s = (id * 2654435761u) >> 21;   // 11 bits
                 bool placed = false;
+#pragma unroll 1
                 for (int probe = 0; probe < 64; probe++) {
                     const uint32_t prev = atomicCAS(&sm.ua.pen.hkey[s], 0xffffffffu, id);
                     if (prev == 0xffffffffu || prev == id) { atomicAdd(&sm.ua.pen.hcnt[s], 1u); placed = true; break; }
@@ -340,17 +485,18 @@ __global__ void __launch_bounds__(FNT, 2) fused_row_kernel(const RowArgs a, cons
                 if (!placed) spill = 1;
             }
         };
+        // f32 rows: one thread streams the slice into shared memory with bulk asynchronous copies
+        // (32 KB pieces, one mbarrier each); every warp then checks / masks / maximises each piece
+        // as soon as it has landed.  (Prefetching the next row's slice into L2 was measured and
+        // bought nothing: the copy is not what limits this kernel.)
+        const uint32_t body = nq * 16;
+        const uint32_t n_pieces = a.dtype == 0 ? (body + TMA_PIECE - 1) / TMA_PIECE : 0u;   // <= 8 for any slice that fits
         if (a.dtype == 0) {
-            // f32 rows: one thread streams the slice into shared memory with bulk asynchronous copies
-            // (32 KB pieces, one mbarrier each); every warp then checks / masks / maximises each piece
-            // as soon as it has landed.  (Prefetching the next row's slice into L2 was measured and
-            // bought nothing: the copy is not what limits this kernel.)
             const char* gsrc = rowp + (size_t)lo * 4;
-            const uint32_t body = nq * 16;
-            const uint32_t n_pieces = (body + TMA_PIECE - 1) / TMA_PIECE;   // <= 8 for any slice that fits
             if (tid == 0) {
                 if (body && !poisoned) {
                     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // earlier generic writes to X
+#pragma unroll 1
                     for (uint32_t pc = 0; pc < n_pieces; pc++) {
                         const uint32_t off = pc * TMA_PIECE, bytes = min(TMA_PIECE, body - off);
                         mbar_expect_tx(&sm.load_bar[pc], bytes);
@@ -358,8 +504,10 @@ __global__ void __launch_bounds__(FNT, 2) fused_row_kernel(const RowArgs a, cons
                     }
                 }
             }
-            if (pen) index_history();
-            PGS_TICK(11);  // copy issued, history indexed
+        }
+        if (pen) index_history();
+        PGS_TICK(11);  // copy issued, history indexed
+        if (a.dtype == 0) {
             float poison = 0.0f, poison1 = 0.0f;   // 0 * v is NaN exactly when v is infinite or NaN, and NaN sticks
             for (uint32_t pc = 0; pc < n_pieces; pc++) {
                 // every warp waits for the piece on its own: one lane polls (bounded), the rest follow
@@ -367,7 +515,6 @@ __global__ void __launch_bounds__(FNT, 2) fused_row_kernel(const RowArgs a, cons
                 const long long w0_ = fl.prof ? clock64() : 0;
                 if (!poisoned && lane == 0) ok = mbar_wait(&sm.load_bar[pc], load_phase) ? 1 : 0;
                 ok = __shfl_sync(FULL, ok, 0);
-                if (fl.prof && tid == 0) fl.prof[blockIdx.x * 16 + 14] += clock64() - w0_;   // also inside slot 0
                 if (!ok) poisoned = true;
                 if (poisoned) continue;
                 const uint32_t q_end = min(nq, (pc + 1) * (TMA_PIECE / 16));
@@ -405,24 +552,14 @@ __global__ void __launch_bounds__(FNT, 2) fused_row_kernel(const RowArgs a, cons
             if (poisoned) nonfinite = 2;   // reported as a load timeout after the exchange
             nonfinite |= poison != poison;
             if (!poisoned)
+#pragma unroll 1
                 for (uint32_t i = nq * 4 + tid; i < len; i += FNT) take1(i, __ldcs((const float*)rowp + lo + i));
         } else {
-            if (pen) index_history();
-            const uint2* src = (const uint2*)(rowp) + lo / 4;    // 4 bf16 per 8-byte load
-            for (uint32_t q0 = tid; q0 < nq; q0 += 4 * FNT) {
-                uint2 r[4];
+            const ThreadMax r = load_bf16_body(X, rowp, mw, lo, nq);
 #pragma unroll
-                for (int u = 0; u < 4; u++)
-                    if (q0 + u * FNT < nq) r[u] = __ldcs(src + q0 + u * FNT);
-#pragma unroll
-                for (int u = 0; u < 4; u++)
-                    if (q0 + u * FNT < nq) {
-                        float4 v;   // bf16 -> f32 is a 16-bit shift: exact
-                        v.x = __uint_as_float(r[u].x << 16); v.y = __uint_as_float(r[u].x & 0xffff0000u);
-                        v.z = __uint_as_float(r[u].y << 16); v.w = __uint_as_float(r[u].y & 0xffff0000u);
-                        take4(q0 + u * FNT, v, u % VG);   // q0 - tid is a multiple of 4 * FNT
-                    }
-            }
+            for (int g = 0; g < VG; g++) { tm[g] = r.tm[g]; tqs[g] = r.tq[g]; }
+            nonfinite |= r.nonfinite;
+#pragma unroll 1
             for (uint32_t i = nq * 4 + tid; i < len; i += FNT)
                 take1(i, __uint_as_float((uint32_t)__ldcs((const unsigned short*)rowp + lo + i) << 16));
         }
@@ -439,6 +576,7 @@ __global__ void __launch_bounds__(FNT, 2) fused_row_kernel(const RowArgs a, cons
         if (pen && (nonfinite || spill) && tid == 0) sm.hash_dirty = 1u;   // the table keeps this row's entries
         if (pen && !nonfinite) {
             if (!spill) {
+#pragma unroll
                 for (int s = tid; s < F_HASH; s += FNT) {
                     const uint32_t id = sm.ua.pen.hkey[s];
                     if (id == 0xffffffffu) continue;
@@ -475,12 +613,14 @@ __global__ void __launch_bounds__(FNT, 2) fused_row_kernel(const RowArgs a, cons
         for (int g = 0; g < VG; g++) {
             if (!sm.redo_max[g * FNT + tid]) continue;
             tm[g] = -INFINITY;
+#pragma unroll 1
             for (uint32_t q = g * FNT + tid; q < nq; q += FVT) {
                 const float4 v = ((const float4*)X)[q];
                 const float m4 = fmaxf(fmaxf(v.x, v.y), fmaxf(v.z, v.w));
                 if (m4 > tm[g]) { tm[g] = m4; tqs[g] = q * 4; }
             }
             if (g == 0)
+#pragma unroll 1
                 for (uint32_t i = nq * 4 + tid; i < len; i += FNT)
                     if (X[i] > tm[0]) { tm[0] = X[i]; tqs[0] = i | 0x80000000u; }
         }
@@ -512,6 +652,7 @@ __global__ void __launch_bounds__(FNT, 2) fused_row_kernel(const RowArgs a, cons
         const unsigned long long best = bkey ? ((unsigned long long)bkey << 32) | (unsigned long long)(0xffffffffu - bidx) : 0ull;
         PGS_TICK(2);   // argmax
         // ------------------------------------------------ cluster exchange #1
+#pragma unroll 1
         for (uint32_t r = tid; r < C; r += FNT) {
             FusedSmem* peer = cluster.map_shared_rank(&sm, r);
             peer->xchg[pbuf].best[rank] = best;
@@ -524,11 +665,12 @@ __global__ void __launch_bounds__(FNT, 2) fused_row_kernel(const RowArgs a, cons
             if (warp_bound) {
 #pragma unroll
                 for (int g = 0; g < VG; g++) {   // virtual warp g * FNW + w
-                    float wmax = tm[g];
-                    for (int o = 16; o; o >>= 1) wmax = fmaxf(wmax, __shfl_xor_sync(FULL, wmax, o));
+                    const uint32_t wk = __reduce_max_sync(FULL, order_key(tm[g]));
+                    const float wmax = wk ? key_to_float(wk) : -INFINITY;
                     if (lane < (int)C) cluster.map_shared_rank(&sm, lane)->ub.tmax_all[rank * FVW + g * FNW + w] = wmax;
                 }
             } else {
+#pragma unroll 1
                 for (uint32_t r = 0; r < C; r++) {
                     float* dst = cluster.map_shared_rank(&sm, r)->ub.tmax_all + rank * FVT + tid;
 #pragma unroll
@@ -582,6 +724,7 @@ __global__ void __launch_bounds__(FNT, 2) fused_row_kernel(const RowArgs a, cons
         const float t = fmaxf(temp, 1e-9f);
         float cut = -INFINITY;
         PGS_TICK(13);  // exchange #1 read
+        uint32_t kk;   // order key of a value that at least top_k logits reach, 0 if there is none
         if (warp_bound) {
             // k-th largest of the FVW*C warp maxima.  Their order keys are made distinct by replacing the
             // low 8 bits with the slot number (the bound can only move down by that, so it stays a bound),
@@ -596,104 +739,28 @@ __global__ void __launch_bounds__(FNT, 2) fused_row_kernel(const RowArgs a, cons
                 u.z = (order_key(f.z) & ~0xffu) | (uint32_t)(lane * 4 + 2);
                 u.w = (order_key(f.w) & ~0xffu) | (uint32_t)(lane * 4 + 3);
             }
-            constexpr int J = F_MAXC * FVW / FNW;   // keys per warp at the largest cluster
-#pragma unroll
-            for (int jj = 0; jj < J; jj++) {
-                const uint32_t j = w * ((nvw + FNW - 1) / FNW) + jj;   // warp-uniform
-                if (jj < (int)((nvw + FNW - 1) / FNW) && j < nvw) {
-                    const uint32_t sel = j & 3u;
-                    const uint32_t mine = sel == 0u ? u.x : sel == 1u ? u.y : sel == 2u ? u.z : u.w;
-                    const uint32_t kj = __shfl_sync(FULL, mine, j >> 2);
-                    const uint32_t cnt = __reduce_add_sync(FULL, (u.x > kj) + (u.y > kj) + (u.z > kj) + (u.w > kj));
-                    if (cnt == top_k - 1u && lane == 0) sm.bound_key = kj & ~0xffu;
-                }
+            const uint32_t per = (nvw + FNW - 1) / FNW;
+            uint32_t found = 0u;
+#pragma unroll 1
+            for (uint32_t j = w * per; j < min(nvw, (w + 1) * per); j++) {   // warp-uniform
+                const uint32_t sel = j & 3u;
+                const uint32_t mine = sel == 0u ? u.x : sel == 1u ? u.y : sel == 2u ? u.z : u.w;
+                const uint32_t kj = __shfl_sync(FULL, mine, j >> 2);
+                const uint32_t cnt = __reduce_add_sync(FULL, (u.x > kj) + (u.y > kj) + (u.z > kj) + (u.w > kj));
+                if (cnt == top_k - 1u) found = kj;
             }
+            if (found && lane == 0) sm.bound_key = found & ~0xffu;
             __syncthreads();
             PGS_TICK(15);  // warp maxima ranked
-            const uint32_t kk = sm.bound_key;
-            if (kk) {
-                const float bound = key_to_float(kk);
-                const float delta = 4.8e-7f * (fabsf(m - bound) + 4.0f * t) + 4.8e-7f * (fabsf(bound) + fabsf(m));
-                cut = bound - delta;
-            }
+            kk = sm.bound_key;
         } else {
-            if (tid == 0) sm.hash_dirty = 1u;   // the histogram below lives in the table's space
-            const uint32_t nv = C * FVT;
-            uint32_t fin = 0;
-            unsigned long long inv_min = 0ull;
-            for (uint32_t i = tid; i < nv; i += FNT) {
-                const uint32_t key = order_key(sm.ub.tmax_all[i]);
-                if (key) { fin++; const unsigned long long iv = 0xffffffffull - key; inv_min = iv > inv_min ? iv : inv_min; }
-            }
-            const uint32_t n_fin = fblock_sum_u32(fin, sm.red_fin);
-            inv_min = fblock_max_u64(inv_min, sm.red_min);
-            if (n_fin >= top_k) {
-                const float lo_v = key_to_float((uint32_t)(0xffffffffull - inv_min));
-                const float sc = m > lo_v ? 2047.0f / (m - lo_v) : 0.0f;
-                for (int bkt = tid; bkt < 2048; bkt += FNT) sm.ua.s.sel.hist[bkt] = 0u;
-                if (tid == 0) { sm.ua.s.sel.prefix = 0xffffffffu; sm.ua.s.sel.k = 0u; sm.memb_n = 0u; }
-                __syncthreads();
-                for (uint32_t i = tid; i < nv; i += FNT) {
-                    const float v = sm.ub.tmax_all[i];
-                    if (finite_f(v)) atomicAdd(&sm.ua.s.sel.hist[min(2047u, (uint32_t)((v - lo_v) * sc))], 1u);
-                }
-                __syncthreads();
-                {
-                    // walk from the top bucket down: thread j owns the BPT buckets 2047 - j*BPT - u, u < BPT
-                    constexpr int BPT = 2048 / FNT;
-                    uint32_t hv[BPT], own = 0;
-#pragma unroll
-                    for (int u = 0; u < BPT; u++) { hv[u] = sm.ua.s.sel.hist[2047 - tid * BPT - u]; own += hv[u]; }
-                    uint32_t inc = own;
-                    for (int o = 1; o < 32; o <<= 1) {
-                        const uint32_t up = __shfl_up_sync(FULL, inc, o);
-                        if (lane >= o) inc += up;
-                    }
-                    if (lane == 31) sm.walk[w] = inc;
-                    __syncthreads();
-                    uint32_t before = inc - own;   // maxima in higher buckets
-                    for (int ww = 0; ww < w; ww++) before += sm.walk[ww];
-#pragma unroll
-                    for (int u = 0; u < BPT; u++) {
-                        if (before < top_k && before + hv[u] >= top_k) {
-                            sm.ua.s.sel.prefix = 2047 - tid * BPT - u; sm.ua.s.sel.k = top_k - before;
-                        }
-                        before += hv[u];
-                    }
-                }
-                __syncthreads();
-                const uint32_t bsel = sm.ua.s.sel.prefix, ksel = sm.ua.s.sel.k;
-                // members of the selected bucket -> cand_x (reused as scratch, at most F_LCAP of them)
-                for (uint32_t i = tid; i < nv; i += FNT) {
-                    const float v = sm.ub.tmax_all[i];
-                    if (finite_f(v) && min(2047u, (uint32_t)((v - lo_v) * sc)) == bsel) {
-                        const uint32_t at = atomicAdd(&sm.memb_n, 1u);
-                        if (at < (uint32_t)F_LCAP) sm.ua.s.members[at] = v;
-                    }
-                }
-                if (tid == 0) sm.ua.s.sel.hist[0] = 0u;   // reused: order key of the bound
-                __syncthreads();
-                const uint32_t nm = sm.memb_n;
-                if (nm <= (uint32_t)F_LCAP) {
-                    for (uint32_t j = tid; j < nm; j += FNT) {
-                        const float v = sm.ua.s.members[j];
-                        uint32_t gt = 0, ge = 0;
-                        for (uint32_t o = 0; o < nm; o++) { gt += sm.ua.s.members[o] > v; ge += sm.ua.s.members[o] >= v; }
-                        if (gt < ksel && ksel <= ge) sm.ua.s.sel.hist[0] = order_key(v);
-                    }
-                } else {
-                    // too many equal-bucket maxima: any member bounds the k-th largest from below
-                    if (tid == 0) sm.ua.s.sel.hist[0] = order_key(lo_v);
-                }
-                __syncthreads();
-                const uint32_t kk = sm.ua.s.sel.hist[0];
-                if (kk) {
-                    const float bound = key_to_float(kk);
-                    // every logit whose probability could still tie with the k-th one stays above the cut
-                    const float delta = 4.8e-7f * (fabsf(m - bound) + 4.0f * t) + 4.8e-7f * (fabsf(bound) + fabsf(m));
-                    cut = bound - delta;
-                }
-            }
+            kk = thread_bound_key(sm, C, top_k, m);
+        }
+        if (kk) {
+            const float bound = key_to_float(kk);
+            // every logit whose probability could still tie with the k-th one stays above the cut
+            const float delta = 4.8e-7f * (fabsf(m - bound) + 4.0f * t) + 4.8e-7f * (fabsf(bound) + fabsf(m));
+            cut = bound - delta;
         }
         PGS_TICK(4);   // select (no barrier needed here: the maxima were last read before a barrier above)
         // ---- one pass in chunk order: collect the candidates, then overwrite each logit with its
@@ -705,10 +772,7 @@ __global__ void __launch_bounds__(FNT, 2) fused_row_kernel(const RowArgs a, cons
         const uint32_t c1b = c0 + ((c1 - c0) & ~3u);   // whole 128-bit groups; a remainder only at the ragged end
         float csum = 0.0f;
         auto candidate = [&](float x, uint32_t i) {
-            if (x >= cut_f) {
-                const uint32_t at = atomicAdd(&sm.cand_n, 1u);
-                if (at < (uint32_t)F_LCAP) { sm.ub.c.id[at] = lo + i; sm.ub.c.x[at] = x; }
-            }
+            if (x >= cut_f) add_candidate(sm, lo + i, x);
         };
         // 2^((x - m) * log2(e) / t) by the hardware exp2 (a few ulp; results below the normal range are
         // flushed to zero, far below anything the sum can see)
@@ -732,6 +796,7 @@ __global__ void __launch_bounds__(FNT, 2) fused_row_kernel(const RowArgs a, cons
             csum += g0 + g1;
         }
         if (ib < c1b) csum += group(*reinterpret_cast<const float4*>(X + ib), ib);
+#pragma unroll 1
         for (uint32_t i = c1b; i < c1; i++) { candidate(X[i], i); const float e = numerator(X[i]); X[i] = e; csum += e; }
         PGS_TICK(5);   // gather + exp
         float ftot0;
@@ -740,6 +805,7 @@ __global__ void __launch_bounds__(FNT, 2) fused_row_kernel(const RowArgs a, cons
         const uint32_t my_n = sm.cand_n;   // complete: the scan's barrier is behind every thread's pass
         PGS_TICK(6);   // scan
         // ------------------------------------------------ cluster exchange #2
+#pragma unroll 1
         for (uint32_t r = tid; r < C; r += FNT) {
             FusedSmem* peer = cluster.map_shared_rank(&sm, r);
             peer->xchg[pbuf].ncand[rank] = my_n;
@@ -760,6 +826,7 @@ __global__ void __launch_bounds__(FNT, 2) fused_row_kernel(const RowArgs a, cons
             continue;
         }
         // candidates -> global memory, in slice order, for the finish kernel
+#pragma unroll 1
         for (uint32_t j = tid; j < my_n; j += FNT) {
             fl.cand_id[(size_t)row * F_MCAP + cand_off + j] = sm.ub.c.id[j];
             fl.cand_x[(size_t)row * F_MCAP + cand_off + j] = sm.ub.c.x[j];
@@ -771,6 +838,7 @@ __global__ void __launch_bounds__(FNT, 2) fused_row_kernel(const RowArgs a, cons
                 const float4 v = *reinterpret_cast<const float4*>(X + i);
                 acc_ = fadd(fadd(fadd(fadd(acc_, v.x), v.y), v.z), v.w);
             }
+#pragma unroll 1
             for (uint32_t i = c1b; i < c1; i++) acc_ = fadd(acc_, X[i]);
             return acc_;
         };
@@ -780,6 +848,7 @@ __global__ void __launch_bounds__(FNT, 2) fused_row_kernel(const RowArgs a, cons
         const float pre1 = fblock_excl_scan_f32(inc1, &ftot1, sm.scan_fold);
         const double tot1 = (double)ftot1;
         PGS_TICK(8);   // fold 1
+#pragma unroll 1
         for (uint32_t r = tid; r < C; r += FNT) cluster.map_shared_rank(&sm, r)->xchg[pbuf].fold1[rank] = tot1;
         cluster.sync();   // exchange #3
         double before1 = (uint32_t)(lane % F_MAXC) < rank ? xc.fold1[lane % F_MAXC] : 0.0;
@@ -789,7 +858,7 @@ __global__ void __launch_bounds__(FNT, 2) fused_row_kernel(const RowArgs a, cons
         const uint32_t e0 = f2u(start0) & 0x7f800000u;
         double inc2 = (double)inc1;
         if ((f2u(start1) & 0x7f800000u) != e0 || (f2u(acc) & 0x7f800000u) != e0) {
-            acc = fold_chunk(start1);
+            acc = refold_chunk(X, c0, c1b, c1, start1);
             inc2 = (double)acc - (double)start1;
         }
         for (int o = 16; o; o >>= 1) inc2 += __shfl_xor_sync(FULL, inc2, o);
@@ -801,6 +870,9 @@ __global__ void __launch_bounds__(FNT, 2) fused_row_kernel(const RowArgs a, cons
         }
         PGS_TICK(9);   // fold 2
     }
+    if (fl.prof && tid == 0)
+#pragma unroll 1
+        for (int i = 0; i < 16; i++) fl.prof[blockIdx.x * 16 + i] += sm.prof_acc[i];
     // no CTA may exit while a peer can still write into its shared memory
     cluster.sync();
 }
