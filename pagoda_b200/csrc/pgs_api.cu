@@ -20,7 +20,7 @@ cudaError_t configure_general();
 cudaError_t launch_general(const RowArgs& a, uint32_t grid, cudaStream_t stream);
 size_t general_smem_bytes();
 
-size_t fused_smem_bytes(uint32_t slice_len);
+size_t fused_smem_bytes(uint32_t slice_len, uint32_t cluster);
 uint32_t fused_threads();
 cudaError_t fused_ctas_per_sm(size_t smem, int* out);
 cudaError_t configure_fused(size_t max_smem);
@@ -90,7 +90,7 @@ struct pgs_handle {
     size_t aux_bytes = 0;
     // fused cluster kernel: launch shape for the last vocabulary size seen, and its work list
     size_t smem_optin = 0;
-    uint32_t fused_vocab = 0, fused_cluster = 0, fused_slice = 0, fused_chunk = 0, fused_clusters = 0;
+    uint32_t fused_rows = 0, fused_vocab = 0, fused_cluster = 0, fused_slice = 0, fused_chunk = 0, fused_clusters = 0;
     size_t fused_smem = 0;
     uint32_t* work_rows = nullptr;
     uint32_t* work_count = nullptr;   // [2]
@@ -312,35 +312,37 @@ extern "C" int pgs_mask_table_free(pgs_handle* h, int32_t table_id) {
 
 namespace {
 
-// Launch shape of the fused kernel for a vocabulary size: the smallest cluster whose slices are small
-// enough for two CTAs per SM (two rows then interleave on every SM and hide each other's barrier and copy
-// latency), else the smallest cluster that fits at all.  Returns false when no cluster of up to 8 CTAs can
-// hold the row.
-bool fused_shape(pgs_handle* h, uint32_t vocab) {
-    if (h->fused_vocab == vocab) return h->fused_clusters > 0;
+// Launch shape of the fused kernel for a vocabulary size and a batch size.  A row lives in the shared memory
+// of one cluster from its copy to its last fold, so the rows in flight are bounded by shared memory: smaller
+// clusters keep more rows in flight but give every thread more logits.  The cluster size is the one with the
+// smallest estimated batch time: waves of resident clusters times a row time made of a fixed part (barriers,
+// exchanges, reductions: measured about 23 k cycles) and a streaming part (about 0.26 cycles per logit of a
+// slice).  Returns false when no cluster of up to 8 CTAs can hold the row.
+bool fused_shape(pgs_handle* h, uint32_t vocab, uint32_t rows) {
+    if (h->fused_vocab == vocab && h->fused_rows == rows) return h->fused_clusters > 0;
     h->fused_vocab = vocab;
+    h->fused_rows = rows;
     h->fused_clusters = 0;
-    for (int want = 2; want >= 1; want--) {
-        for (uint32_t c = 1; c <= 8; c *= 2) {
-            const uint32_t slice = (((vocab + c - 1) / c) + 31u) & ~31u;
-            const size_t smem = pgs::fused_smem_bytes(slice);
-            if (smem > h->smem_optin) continue;
-            int per_sm = 0, n = 0;
-            if (pgs::fused_ctas_per_sm(smem, &per_sm) != cudaSuccess || per_sm < want) { cudaGetLastError(); continue; }
-            if (pgs::fused_max_clusters(c, smem, &n) != cudaSuccess || n <= 0) { cudaGetLastError(); continue; }
-            // consecutive logits per thread in the sum passes: 4 * odd, so that the 128-bit shared-memory
-            // accesses of a warp (stride = chunk words) fall into distinct bank groups
-            const uint32_t nt = pgs::fused_threads();
-            uint32_t groups = ((slice + nt - 1u) / nt + 3u) / 4u;
-            if ((groups & 1u) == 0) groups += 1;
-            const uint32_t chunk = groups * 4u;
-            h->fused_cluster = c; h->fused_slice = slice; h->fused_chunk = chunk; h->fused_smem = smem;
-            h->fused_clusters = (uint32_t)n;
-            if (const char* ev = getenv("PGS_XX_MAXC")) h->fused_clusters = atoi(ev);  // XXTMP
-            return true;
-        }
+    double best_cost = 0.0;
+    for (uint32_t c = 1; c <= (uint32_t)pgs::F_MAXC; c++) {
+        const uint32_t slice = (((vocab + c - 1) / c) + 31u) & ~31u;
+        const size_t smem = pgs::fused_smem_bytes(slice, c);
+        if (smem > h->smem_optin || (slice * 4u + 32767u) / 32768u > 8u) continue;
+        int n = 0;
+        if (pgs::fused_max_clusters(c, smem, &n) != cudaSuccess || n <= 0) { cudaGetLastError(); continue; }
+        const uint32_t waves = (rows + (uint32_t)n - 1) / (uint32_t)n;
+        const double cost = (double)waves * (23000.0 + 0.26 * (double)slice);
+        if (h->fused_clusters && cost >= best_cost) continue;
+        best_cost = cost;
+        // consecutive logits per thread in the sum passes: 4 * odd, so that the 128-bit shared-memory
+        // accesses of a warp (stride = chunk words) fall into distinct bank groups
+        const uint32_t nt = pgs::fused_threads();
+        uint32_t groups = ((slice + nt - 1u) / nt + 3u) / 4u;
+        if ((groups & 1u) == 0) groups += 1;
+        h->fused_cluster = c; h->fused_slice = slice; h->fused_chunk = groups * 4u; h->fused_smem = smem;
+        h->fused_clusters = (uint32_t)n;
     }
-    return false;
+    return h->fused_clusters > 0;
 }
 
 // One step: the fused cluster kernel serves every row it can hold and lists the others, which
@@ -348,7 +350,7 @@ bool fused_shape(pgs_handle* h, uint32_t vocab) {
 int launch_step(pgs_handle* h, pgs::RowArgs& a, cudaStream_t stream) {
     const uint32_t rows = a.rows;
     const uint32_t grid = rows < h->slots ? rows : h->slots;
-    if (h->exact || !fused_shape(h, a.vocab)) {
+    if (h->exact || !fused_shape(h, a.vocab, rows)) {
         PGS_CUDA(h, pgs::launch_general(a, grid, stream));
         h->counters.kernel_launches += 1;
         return PGS_OK;

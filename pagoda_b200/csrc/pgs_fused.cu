@@ -43,11 +43,12 @@ namespace pgs {
 // The per-thread maxima that bound the top-k threshold are kept for FVT "virtual threads": 128-bit group q
 // of a slice belongs to virtual thread q mod FVT, and a real thread plays VG = FVT / FNT of them (groups q
 // with q mod FVT = g * FNT + tid, g < VG).
-constexpr int FNT = 512;
+constexpr int FNT = 1024;
 constexpr int FNW = FNT / 32;
-constexpr int FVT = 512;
+constexpr int FVT = 1024;
 constexpr int FVW = FVT / 32;
 constexpr int VG = FVT / FNT;
+static_assert(F_MAXC * FVW <= 256, "a warp-maximum slot number fits the low 8 bits of its key");
 static_assert(VG == 1 || VG == 2 || VG == 4, "the bf16 loader assumes VG divides 4");
 
 struct FusedXchg {                  // peers write their slot through DSMEM
@@ -69,7 +70,14 @@ struct RowCtl {
     uint32_t kind;          // 0 serve, 1 bad parameters, 2 defer to the general kernel
 };
 
-// Shared-memory workspace of one CTA (the vocabulary slice follows it).
+constexpr int F_NB = 1024;          // buckets of the per-thread-maxima histogram
+static_assert(F_NB % FNT == 0, "every thread walks F_NB / FNT buckets");
+struct BoundSmem { uint32_t hist[F_NB]; uint32_t prefix, k; };
+
+// Shared-memory workspace of one CTA.  Two more regions follow it: the exchange region -- every CTA's
+// per-thread (or per-warp) maxima, C * FVT floats, written by the peers; once the top-k bound is known the
+// same space holds this slice's candidate list (peers only write the next row's maxima after this row's last
+// cluster barrier) -- and then the vocabulary slice.
 struct FusedSmem {
     RowCtl ctl[2];                  // alternates between consecutive rows of this CTA
     uint32_t red_key[FNW], red_idx[FNW];              // one set of warp slots per reduction site
@@ -79,12 +87,8 @@ struct FusedSmem {
     FusedXchg xchg[2];              // alternates between consecutive rows
     union alignas(16) {             // the id -> count table is dead once the penalties are applied
         struct { uint32_t hkey[F_HASH]; uint32_t hcnt[F_HASH]; } pen;
-        struct { SelectSmem sel; float members[F_LCAP]; } s;
+        struct { BoundSmem sel; float members[F_LCAP]; } s;
     } ua;
-    union alignas(16) {             // peers only write the next row's maxima after this row's last cluster barrier
-        float tmax_all[F_MAXC * FVT];   // every CTA's per-thread (or per-warp) maxima
-        struct { uint32_t id[F_LCAP]; float x[F_LCAP]; } c;   // this slice's top-k candidates
-    } ub;
     float tmax_s[FVT];              // each virtual thread's maximum after the load pass
     uint8_t redo_max[FVT];
     uint32_t cand_n, memb_n, bound_key;
@@ -185,11 +189,11 @@ __device__ __forceinline__ bool mbar_wait(unsigned long long* bar, uint32_t pari
 constexpr uint32_t TMA_PIECE = 32768;   // bytes per bulk copy
 
 // Top-k bound from all per-thread maxima (used when top_k is too large for the warp maxima): the C*FVT
-// maxima are spread over 2048 equal-width buckets between their smallest finite value and the row maximum
+// maxima are spread over F_NB equal-width buckets between their smallest finite value and the row maximum
 // (a monotone map), the bucket holding the k-th largest is found from the histogram, and the exact value
 // is picked among that bucket's few members.  Returns the bound's order key, 0 if fewer than top_k maxima
 // are finite.  Called by every thread of the CTA.
-__device__ __forceinline__ uint32_t thread_bound_key(FusedSmem& sm, uint32_t C, uint32_t top_k, float m) {
+__device__ __forceinline__ uint32_t thread_bound_key(FusedSmem& sm, const float* TM, uint32_t C, uint32_t top_k, float m) {
     const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
     if (tid == 0) sm.hash_dirty = 1u;   // the histogram below lives in the table's space
     const uint32_t nv = C * FVT;
@@ -197,30 +201,30 @@ __device__ __forceinline__ uint32_t thread_bound_key(FusedSmem& sm, uint32_t C, 
     unsigned long long inv_min = 0ull;
 #pragma unroll 1
     for (uint32_t i = tid; i < nv; i += FNT) {
-        const uint32_t key = order_key(sm.ub.tmax_all[i]);
+        const uint32_t key = order_key(TM[i]);
         if (key) { fin++; const unsigned long long iv = 0xffffffffull - key; inv_min = iv > inv_min ? iv : inv_min; }
     }
     const uint32_t n_fin = fblock_sum_u32(fin, sm.red_fin);
     inv_min = fblock_max_u64(inv_min, sm.red_min);
     if (n_fin < top_k) return 0u;
     const float lo_v = key_to_float((uint32_t)(0xffffffffull - inv_min));
-    const float sc = m > lo_v ? 2047.0f / (m - lo_v) : 0.0f;
+    const float sc = m > lo_v ? (float)(F_NB - 1) / (m - lo_v) : 0.0f;
 #pragma unroll 1
-    for (int bkt = tid; bkt < 2048; bkt += FNT) sm.ua.s.sel.hist[bkt] = 0u;
+    for (int bkt = tid; bkt < F_NB; bkt += FNT) sm.ua.s.sel.hist[bkt] = 0u;
     if (tid == 0) { sm.ua.s.sel.prefix = 0xffffffffu; sm.ua.s.sel.k = 0u; sm.memb_n = 0u; }
     __syncthreads();
 #pragma unroll 1
     for (uint32_t i = tid; i < nv; i += FNT) {
-        const float v = sm.ub.tmax_all[i];
-        if (finite_f(v)) atomicAdd(&sm.ua.s.sel.hist[min(2047u, (uint32_t)((v - lo_v) * sc))], 1u);
+        const float v = TM[i];
+        if (finite_f(v)) atomicAdd(&sm.ua.s.sel.hist[min((uint32_t)(F_NB - 1), (uint32_t)((v - lo_v) * sc))], 1u);
     }
     __syncthreads();
     {
-        // walk from the top bucket down: thread j owns the BPT buckets 2047 - j*BPT - u, u < BPT
-        constexpr int BPT = 2048 / FNT;
+        // walk from the top bucket down: thread j owns the BPT buckets F_NB-1 - j*BPT - u, u < BPT
+        constexpr int BPT = F_NB / FNT;
         uint32_t hv[BPT], own = 0;
 #pragma unroll
-        for (int u = 0; u < BPT; u++) { hv[u] = sm.ua.s.sel.hist[2047 - tid * BPT - u]; own += hv[u]; }
+        for (int u = 0; u < BPT; u++) { hv[u] = sm.ua.s.sel.hist[(F_NB - 1) - tid * BPT - u]; own += hv[u]; }
         uint32_t inc = own;
         for (int o = 1; o < 32; o <<= 1) {
             const uint32_t up = __shfl_up_sync(FULL, inc, o);
@@ -234,7 +238,7 @@ __device__ __forceinline__ uint32_t thread_bound_key(FusedSmem& sm, uint32_t C, 
 #pragma unroll
         for (int u = 0; u < BPT; u++) {
             if (before < top_k && before + hv[u] >= top_k) {
-                sm.ua.s.sel.prefix = 2047 - tid * BPT - u; sm.ua.s.sel.k = top_k - before;
+                sm.ua.s.sel.prefix = (F_NB - 1) - tid * BPT - u; sm.ua.s.sel.k = top_k - before;
             }
             before += hv[u];
         }
@@ -244,8 +248,8 @@ __device__ __forceinline__ uint32_t thread_bound_key(FusedSmem& sm, uint32_t C, 
     // members of the selected bucket (at most F_LCAP of them are kept)
 #pragma unroll 1
     for (uint32_t i = tid; i < nv; i += FNT) {
-        const float v = sm.ub.tmax_all[i];
-        if (finite_f(v) && min(2047u, (uint32_t)((v - lo_v) * sc)) == bsel) {
+        const float v = TM[i];
+        if (finite_f(v) && min((uint32_t)(F_NB - 1), (uint32_t)((v - lo_v) * sc)) == bsel) {
             const uint32_t at = atomicAdd(&sm.memb_n, 1u);
             if (at < (uint32_t)F_LCAP) sm.ua.s.members[at] = v;
         }
@@ -271,9 +275,9 @@ __device__ __forceinline__ uint32_t thread_bound_key(FusedSmem& sm, uint32_t C, 
 }
 
 // One more top-k candidate of this slice (rare next to the logits that are not)
-__device__ __forceinline__ void add_candidate(FusedSmem& sm, uint32_t id, float x) {
+__device__ __forceinline__ void add_candidate(FusedSmem& sm, uint32_t* CID, float* CX, uint32_t id, float x) {
     const uint32_t at = atomicAdd(&sm.cand_n, 1u);
-    if (at < (uint32_t)F_LCAP) { sm.ub.c.id[at] = id; sm.ub.c.x[at] = x; }
+    if (at < (uint32_t)F_LCAP) { CID[at] = id; CX[at] = x; }
 }
 
 // The sequential f32 fold of one chunk of numerators from a given running value (the refinement pass;
@@ -386,10 +390,19 @@ const uint32_t V = a.vocab;
     c.kind = bad ? 1u : defer ? 2u : 0u;
 }
 
-__global__ void __launch_bounds__(FNT, 2) fused_row_kernel(const RowArgs a, const FusedLaunch fl) {
+__host__ __device__ constexpr size_t fused_fixed_bytes() { return (sizeof(FusedSmem) + 15) & ~size_t(15); }
+__host__ __device__ inline size_t fused_exchange_bytes(uint32_t cluster) {
+    const size_t maxima = (size_t)cluster * FVT * sizeof(float), cands = (size_t)F_LCAP * 8;
+    return maxima > cands ? maxima : cands;
+}
+
+__global__ void __launch_bounds__(FNT, FNT <= 512 ? 2 : 1) fused_row_kernel(const RowArgs a, const FusedLaunch fl) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     FusedSmem& sm = *reinterpret_cast<FusedSmem*>(smem_raw);
-    float* X = reinterpret_cast<float*>(smem_raw + ((sizeof(FusedSmem) + 15) & ~size_t(15)));
+    float* TM = reinterpret_cast<float*>(smem_raw + fused_fixed_bytes());   // maxima of all CTAs, later the candidates
+    uint32_t* CID = reinterpret_cast<uint32_t*>(TM);
+    float* CX = TM + F_LCAP;
+    float* X = reinterpret_cast<float*>(smem_raw + fused_fixed_bytes() + fused_exchange_bytes(fl.cluster));
     cg::cluster_group cluster = cg::this_cluster();
     const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
     const uint32_t C = fl.cluster;
@@ -474,7 +487,7 @@ __global__ void __launch_bounds__(FNT, 2) fused_row_kernel(const RowArgs a, cons
             for (uint32_t j = tid; j < nh; j += FNT) {
                 const uint32_t id = j == (uint32_t)tid ? hid0 : __ldg(a.hist_ids + h0 + j);
                 if (id < lo || id >= hi) continue;
-                uint32_t s = (id * 2654435761u) >> 21;   // 11 bits
+                uint32_t s = (id * 2654435761u) >> (32 - F_HASH_BITS);
                 bool placed = false;
 #pragma unroll 1
                 for (int probe = 0; probe < 64; probe++) {
@@ -660,19 +673,19 @@ __global__ void __launch_bounds__(FNT, 2) fused_row_kernel(const RowArgs a, cons
         }
         // material for the top-k bound: the 32*C warp maxima when there are comfortably more warps than
         // top_k, else all FVT*C thread maxima
-        const bool warp_bound = !greedy && 2u * top_k <= C * FVW;
+        const bool warp_bound = !greedy && 8u * top_k <= 7u * C * FVW;
         if (!greedy) {
             if (warp_bound) {
 #pragma unroll
                 for (int g = 0; g < VG; g++) {   // virtual warp g * FNW + w
                     const uint32_t wk = __reduce_max_sync(FULL, order_key(tm[g]));
                     const float wmax = wk ? key_to_float(wk) : -INFINITY;
-                    if (lane < (int)C) cluster.map_shared_rank(&sm, lane)->ub.tmax_all[rank * FVW + g * FNW + w] = wmax;
+                    if (lane < (int)C) cluster.map_shared_rank(TM, lane)[rank * FVW + g * FNW + w] = wmax;
                 }
             } else {
 #pragma unroll 1
                 for (uint32_t r = 0; r < C; r++) {
-                    float* dst = cluster.map_shared_rank(&sm, r)->ub.tmax_all + rank * FVT + tid;
+                    float* dst = cluster.map_shared_rank(TM, r) + rank * FVT + tid;
 #pragma unroll
                     for (int g = 0; g < VG; g++) dst[g * FNT] = tm[g];
                 }
@@ -718,7 +731,7 @@ __global__ void __launch_bounds__(FNT, 2) fused_row_kernel(const RowArgs a, cons
         }
 
         // -------------------------------- top-k bound: k-th largest per-thread maximum
-        // The C*FVT maxima are spread over 2048 equal-width buckets between their smallest finite
+        // The C*FVT maxima are spread over F_NB equal-width buckets between their smallest finite
         // value and the row maximum (a monotone map), the bucket holding the k-th largest is found
         // from the histogram, and the exact value is picked among that bucket's few members.
         const float t = fmaxf(temp, 1e-9f);
@@ -728,33 +741,32 @@ __global__ void __launch_bounds__(FNT, 2) fused_row_kernel(const RowArgs a, cons
         if (warp_bound) {
             // k-th largest of the FVW*C warp maxima.  Their order keys are made distinct by replacing the
             // low 8 bits with the slot number (the bound can only move down by that, so it stays a bound),
-            // so a key's rank is the number of larger keys.  Every warp holds all keys, four per lane, and
+            // so a key's rank is the number of larger keys.  Every warp holds all keys, a few per lane, and
             // ranks its share of them with warp-wide sums; exactly one key has rank top_k - 1.
-            const uint32_t nvw = C * FVW;   // <= 128, a multiple of 16
-            uint4 u = make_uint4(0u, 0u, 0u, 0u);
-            if ((uint32_t)lane * 4u < nvw) {
-                const float4 f = *reinterpret_cast<const float4*>(sm.ub.tmax_all + lane * 4);
-                u.x = (order_key(f.x) & ~0xffu) | (uint32_t)(lane * 4);
-                u.y = (order_key(f.y) & ~0xffu) | (uint32_t)(lane * 4 + 1);
-                u.z = (order_key(f.z) & ~0xffu) | (uint32_t)(lane * 4 + 2);
-                u.w = (order_key(f.w) & ~0xffu) | (uint32_t)(lane * 4 + 3);
+            const uint32_t nvw = C * FVW;   // <= 256
+            constexpr int KPL = F_MAXC * FVW / 32;   // keys per lane at the largest cluster
+            uint32_t u[KPL];
+#pragma unroll
+            for (int q = 0; q < KPL; q++) {
+                const uint32_t slot = q * 32 + lane;
+                u[q] = slot < nvw ? ((order_key(TM[slot]) & ~0xffu) | slot) : 0u;
             }
             const uint32_t per = (nvw + FNW - 1) / FNW;
             uint32_t found = 0u;
 #pragma unroll 1
             for (uint32_t j = w * per; j < min(nvw, (w + 1) * per); j++) {   // warp-uniform
-                const uint32_t sel = j & 3u;
-                const uint32_t mine = sel == 0u ? u.x : sel == 1u ? u.y : sel == 2u ? u.z : u.w;
-                const uint32_t kj = __shfl_sync(FULL, mine, j >> 2);
-                const uint32_t cnt = __reduce_add_sync(FULL, (u.x > kj) + (u.y > kj) + (u.z > kj) + (u.w > kj));
-                if (cnt == top_k - 1u) found = kj;
+                const uint32_t kj = (order_key(TM[j]) & ~0xffu) | j;
+                uint32_t above = 0;
+#pragma unroll
+                for (int q = 0; q < KPL; q++) above += u[q] > kj;
+                if (__reduce_add_sync(FULL, above) == top_k - 1u) found = kj;
             }
             if (found && lane == 0) sm.bound_key = found & ~0xffu;
             __syncthreads();
             PGS_TICK(15);  // warp maxima ranked
             kk = sm.bound_key;
         } else {
-            kk = thread_bound_key(sm, C, top_k, m);
+            kk = thread_bound_key(sm, TM, C, top_k, m);
         }
         if (kk) {
             const float bound = key_to_float(kk);
@@ -772,7 +784,7 @@ __global__ void __launch_bounds__(FNT, 2) fused_row_kernel(const RowArgs a, cons
         const uint32_t c1b = c0 + ((c1 - c0) & ~3u);   // whole 128-bit groups; a remainder only at the ragged end
         float csum = 0.0f;
         auto candidate = [&](float x, uint32_t i) {
-            if (x >= cut_f) add_candidate(sm, lo + i, x);
+            if (x >= cut_f) add_candidate(sm, CID, CX, lo + i, x);
         };
         // 2^((x - m) * log2(e) / t) by the hardware exp2 (a few ulp; results below the normal range are
         // flushed to zero, far below anything the sum can see)
@@ -828,8 +840,8 @@ __global__ void __launch_bounds__(FNT, 2) fused_row_kernel(const RowArgs a, cons
         // candidates -> global memory, in slice order, for the finish kernel
 #pragma unroll 1
         for (uint32_t j = tid; j < my_n; j += FNT) {
-            fl.cand_id[(size_t)row * F_MCAP + cand_off + j] = sm.ub.c.id[j];
-            fl.cand_x[(size_t)row * F_MCAP + cand_off + j] = sm.ub.c.x[j];
+            fl.cand_id[(size_t)row * F_MCAP + cand_off + j] = CID[j];
+            fl.cand_x[(size_t)row * F_MCAP + cand_off + j] = CX[j];
         }
         // ---------- the sequential fold, chunk by chunk: first from the plain prefix sums ...
         const float start0 = (float)before0 + pre0;
@@ -879,8 +891,8 @@ __global__ void __launch_bounds__(FNT, 2) fused_row_kernel(const RowArgs a, cons
 
 uint32_t fused_threads() { return FNT; }
 
-size_t fused_smem_bytes(uint32_t slice_len) {
-    return ((sizeof(FusedSmem) + 15) & ~size_t(15)) + (size_t)slice_len * sizeof(float);
+size_t fused_smem_bytes(uint32_t slice_len, uint32_t cluster) {
+    return fused_fixed_bytes() + fused_exchange_bytes(cluster) + (size_t)slice_len * sizeof(float);
 }
 
 cudaError_t configure_fused(size_t max_smem) {

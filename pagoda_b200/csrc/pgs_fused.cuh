@@ -8,7 +8,8 @@ namespace pgs {
 constexpr int F_MAXC = 8;          // largest cluster
 constexpr int F_LCAP = 1024;       // candidates per CTA
 constexpr int F_MCAP = 2048;       // candidates per row
-constexpr int F_HASH = 2048;       // id->count slots per CTA
+constexpr int F_HASH_BITS = 10;
+constexpr int F_HASH = 1 << F_HASH_BITS;   // id->count slots per CTA
 constexpr int F_KMAX = 1024;       // largest top-k served by the fused path
 
 // What the fused kernel leaves behind for a stochastic row; the finish kernel turns it into a token.
