@@ -528,6 +528,7 @@ __global__ void __launch_bounds__(FNT, FNT <= 512 ? 2 : 1) fused_row_kernel(cons
                 const long long w0_ = fl.prof ? clock64() : 0;
                 if (!poisoned && lane == 0) ok = mbar_wait(&sm.load_bar[pc], load_phase) ? 1 : 0;
                 ok = __shfl_sync(FULL, ok, 0);
+                if (fl.prof && tid == 0) sm.prof_acc[14] += clock64() - w0_;   // waiting for the copy (also inside slot 0)
                 if (!ok) poisoned = true;
                 if (poisoned) continue;
                 const uint32_t q_end = min(nq, (pc + 1) * (TMA_PIECE / 16));
