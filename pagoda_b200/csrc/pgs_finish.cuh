@@ -28,25 +28,31 @@ struct FinishSmem {
     int bcast_i;
 };
 
-// Exact left fold of n <= 128 shared-memory floats by one warp (values travel by shuffle, so the
-// dependent chain is add + shuffle instead of add + shared-memory load).  mode/target as in
+// Exact left fold of n <= 128 shared-memory floats, called by one warp.  One lane does the additions: the
+// loads do not depend on the running value, so they are requested eight at a time and the dependent chain
+// is the additions alone (warp shuffles would put tens of cycles between two of them).  mode/target as in
 // seq_scan; returns the running value, *found = first index where the predicate holds or -1.
 __device__ __forceinline__ float warp_fold(const float* v, int n, int mode, float target, int* found) {
     const int lane = threadIdx.x & 31;
-    float reg[4];
-#pragma unroll
-    for (int u = 0; u < 4; u++) reg[u] = (lane + 32 * u < n) ? v[lane + 32 * u] : 0.0f;
     float acc = 0.0f;
     int f = -1;
+    if (lane == 0) {
+#pragma unroll 1
+        for (int j0 = 0; j0 < n && f < 0; j0 += 8) {
+            float x[8];
 #pragma unroll
-    for (int u = 0; u < 4; u++) {
-        for (int l = 0; l < 32; l++) {
-            const int j = u * 32 + l;
-            if (j >= n || f >= 0) break;
-            acc = fadd(acc, __shfl_sync(FULL, reg[u], l));
-            if (mode != SEQ_SUM && seq_pred(mode, acc, target)) f = j;
+            for (int u = 0; u < 8; u++) x[u] = (j0 + u < n) ? v[j0 + u] : 0.0f;
+#pragma unroll
+            for (int u = 0; u < 8; u++) {
+                if (j0 + u < n && f < 0) {
+                    acc = fadd(acc, x[u]);
+                    if (mode != SEQ_SUM && seq_pred(mode, acc, target)) f = j0 + u;
+                }
+            }
         }
     }
+    acc = __shfl_sync(FULL, acc, 0);
+    f = __shfl_sync(FULL, f, 0);
     if (found) *found = f;
     return acc;
 }

@@ -1,10 +1,14 @@
 // Fused cluster kernel: the hot path of the sampler.
 //
-// One thread-block cluster owns one batch row.  The row is read from HBM exactly once -- bulk
-// asynchronous copies (TMA, no multicast) for f32, 64-bit coalesced loads for bf16 -- into the
-// distributed shared memory of the cluster (each CTA keeps a
-// contiguous slice of the vocabulary as f32), and every later step of the chain
-// (pagoda/src/engine.rs:1286-1314, pagoda/src/sampler.rs:28-150) works on that copy:
+// One thread-block cluster (1 to 8 CTAs of 1024 threads, one CTA per SM) owns one batch row at a time and
+// walks through its share of the batch.  The row is read from HBM exactly once -- bulk asynchronous copies
+// (TMA, no multicast) for f32, 64-bit coalesced loads for bf16 -- into the distributed shared memory of the
+// cluster (each CTA keeps a contiguous slice of the vocabulary as f32), and every later step of the chain
+// (pagoda/src/engine.rs:1286-1314, pagoda/src/sampler.rs:28-150) works on that copy.  Rows in flight are
+// bounded by shared memory (a row occupies its cluster from the copy to the last fold), so the host picks
+// the cluster size that minimises waves x row time for the batch (3 CTAs at 256 x 151936 f32).
+//
+// Per row:
 //
 //   load + sanity + grammar bitmask AND + per-thread max      (one pass, from HBM)
 //   penalties scattered from a shared-memory id->count table   (history ids of this slice only)
@@ -38,8 +42,11 @@ namespace cg = cooperative_groups;
 
 namespace pgs {
 
-// The kernel runs FNT threads per CTA and is shaped so that two CTAs (of different clusters, hence working
-// on different rows) share one SM: while one waits at a barrier or for its copy, the other one issues.
+// The kernel runs FNT threads per CTA.  (Measured alternatives on 256 x 151936: 512 threads with two CTAs
+// per SM and clusters of 8, 141 us; 256 threads, 146 us; 1024 threads with clusters of 4, 135 us, of 3,
+// 128 us.  Warp collectives -- shuffles, votes, redux -- run at about one per cycle and SM and cost 30 to
+// 130 cycles of latency each here, function calls cost more than the code they save, and straight-line code
+// that is executed once per row runs at 20 to 30 cycles per instruction and warp, so cold loops stay rolled.)
 // The per-thread maxima that bound the top-k threshold are kept for FVT "virtual threads": 128-bit group q
 // of a slice belongs to virtual thread q mod FVT, and a real thread plays VG = FVT / FNT of them (groups q
 // with q mod FVT = g * FNT + tid, g < VG).
@@ -522,43 +529,55 @@ __global__ void __launch_bounds__(FNT, FNT <= 512 ? 2 : 1) fused_row_kernel(cons
         PGS_TICK(11);  // copy issued, history indexed
         if (a.dtype == 0) {
             float poison = 0.0f, poison1 = 0.0f;   // 0 * v is NaN exactly when v is infinite or NaN, and NaN sticks
-            for (uint32_t pc = 0; pc < n_pieces; pc++) {
-                // every warp waits for the piece on its own: one lane polls (bounded), the rest follow
+            // The slice is checked in two halves, each in one tight loop once its pieces have landed (a loop per
+            // piece spends more on waiting and set-up than on the few groups a thread has in it).  Every warp
+            // waits on its own: one lane polls (bounded), the rest follow.
+            constexpr uint32_t PQ = TMA_PIECE / 16;   // 128-bit groups per piece, a whole number of FVT groups
+            const uint32_t split = (n_pieces + 1u) / 2u;
+#pragma unroll 1
+            for (uint32_t half = 0; half < 2u; half++) {
+                const uint32_t p0 = half ? split : 0u, p1 = half ? n_pieces : split;
                 int ok = 1;
                 const long long w0_ = fl.prof ? clock64() : 0;
-                if (!poisoned && lane == 0) ok = mbar_wait(&sm.load_bar[pc], load_phase) ? 1 : 0;
+                if (!poisoned && lane == 0)
+                    for (uint32_t pc = p0; pc < p1 && ok; pc++) ok = mbar_wait(&sm.load_bar[pc], load_phase) ? 1 : 0;
                 ok = __shfl_sync(FULL, ok, 0);
                 if (fl.prof && tid == 0) sm.prof_acc[14] += clock64() - w0_;   // waiting for the copy (also inside slot 0)
                 if (!ok) poisoned = true;
                 if (poisoned) continue;
-                const uint32_t q_end = min(nq, (pc + 1) * (TMA_PIECE / 16));
-                const uint32_t qb = pc * (TMA_PIECE / 16) + tid;
-                constexpr int PIT = (TMA_PIECE / 16) / FNT;   // groups per thread and piece, requested two at a time
-#pragma unroll
-                for (int k0 = 0; k0 < PIT; k0 += 2) {
-                    float4 v[2];
-#pragma unroll
-                    for (int k2 = 0; k2 < 2; k2++)
-                        if (k0 + k2 < PIT && qb + (k0 + k2) * FNT < q_end) v[k2] = ((const float4*)X)[qb + (k0 + k2) * FNT];
-#pragma unroll
-                    for (int k2 = 0; k2 < 2; k2++) {
-                        const uint32_t q = qb + (k0 + k2) * FNT;
-                        if (k0 + k2 >= PIT || q >= q_end) break;
-                        const int g = (k0 + k2) % VG;   // a piece holds a whole number of FVT groups
-                        float& pz = k2 ? poison1 : poison;
-                        pz = __fmaf_rn(v[k2].x, 0.0f, pz); pz = __fmaf_rn(v[k2].y, 0.0f, pz);
-                        pz = __fmaf_rn(v[k2].z, 0.0f, pz); pz = __fmaf_rn(v[k2].w, 0.0f, pz);
-                        if (mw) {
-                            const uint32_t bits = __ldg(mw + ((lo >> 5) + (q >> 3))) >> ((q & 7) * 4);
-                            if (!(bits & 1u)) v[k2].x = -INFINITY;
-                            if (!(bits & 2u)) v[k2].y = -INFINITY;
-                            if (!(bits & 4u)) v[k2].z = -INFINITY;
-                            if (!(bits & 8u)) v[k2].w = -INFINITY;
-                            ((float4*)X)[q] = v[k2];
+                const uint32_t q_end = min(nq, p1 * PQ);
+#pragma unroll 1
+                for (uint32_t q0 = p0 * PQ + tid; q0 < q_end; q0 += 2 * FNT) {   // two groups per round, both requested first
+                    const bool has1 = q0 + FNT < q_end;
+                    float4 v0 = ((const float4*)X)[q0];
+                    float4 v1 = has1 ? ((const float4*)X)[q0 + FNT] : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                    poison = __fmaf_rn(v0.x, 0.0f, poison); poison = __fmaf_rn(v0.y, 0.0f, poison);
+                    poison = __fmaf_rn(v0.z, 0.0f, poison); poison = __fmaf_rn(v0.w, 0.0f, poison);
+                    poison1 = __fmaf_rn(v1.x, 0.0f, poison1); poison1 = __fmaf_rn(v1.y, 0.0f, poison1);
+                    poison1 = __fmaf_rn(v1.z, 0.0f, poison1); poison1 = __fmaf_rn(v1.w, 0.0f, poison1);
+                    if (mw) {
+                        const uint32_t b0 = __ldg(mw + ((lo >> 5) + (q0 >> 3))) >> ((q0 & 7) * 4);
+                        if (!(b0 & 1u)) v0.x = -INFINITY;
+                        if (!(b0 & 2u)) v0.y = -INFINITY;
+                        if (!(b0 & 4u)) v0.z = -INFINITY;
+                        if (!(b0 & 8u)) v0.w = -INFINITY;
+                        ((float4*)X)[q0] = v0;
+                        if (has1) {
+                            const uint32_t q1 = q0 + FNT;
+                            const uint32_t b1 = __ldg(mw + ((lo >> 5) + (q1 >> 3))) >> ((q1 & 7) * 4);
+                            if (!(b1 & 1u)) v1.x = -INFINITY;
+                            if (!(b1 & 2u)) v1.y = -INFINITY;
+                            if (!(b1 & 4u)) v1.z = -INFINITY;
+                            if (!(b1 & 8u)) v1.w = -INFINITY;
+                            ((float4*)X)[q1] = v1;
                         }
-                        const float m4 = fmaxf(fmaxf(v[k2].x, v[k2].y), fmaxf(v[k2].z, v[k2].w));
-                        if (m4 > tm[g]) { tm[g] = m4; tqs[g] = q * 4; }
                     }
+                    // the round's groups belong to virtual threads (q0 / FNT) % VG and the next one
+                    const int g0 = (int)((q0 / FNT) % VG), g1 = (int)((q0 / FNT + 1) % VG);
+                    const float m0 = fmaxf(fmaxf(v0.x, v0.y), fmaxf(v0.z, v0.w));
+                    if (m0 > tm[g0]) { tm[g0] = m0; tqs[g0] = q0 * 4; }
+                    const float m1 = fmaxf(fmaxf(v1.x, v1.y), fmaxf(v1.z, v1.w));
+                    if (has1 && m1 > tm[g1]) { tm[g1] = m1; tqs[g1] = (q0 + FNT) * 4; }
                 }
             }
             poison += poison1;
