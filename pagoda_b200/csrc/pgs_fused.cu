@@ -506,9 +506,10 @@ __global__ void __launch_bounds__(FNT, FNT <= 512 ? 2 : 1) fused_row_kernel(cons
             }
         };
         // f32 rows: one thread streams the slice into shared memory with bulk asynchronous copies
-        // (32 KB pieces, one mbarrier each); every warp then checks / masks / maximises each piece
-        // as soon as it has landed.  (Prefetching the next row's slice into L2 was measured and
-        // bought nothing: the copy is not what limits this kernel.)
+        // (32 KB pieces, one mbarrier each); every warp then checks / masks / maximises it in two halves
+        // as they land.  All clusters reach this point at about the same time, so the copies of a whole wave
+        // of rows compete for HBM; once this row has landed the next row's slice is therefore prefetched into
+        // L2, where the memory system is idle, and the next copy is then served from L2.
         const uint32_t body = nq * 16;
         const uint32_t n_pieces = a.dtype == 0 ? (body + TMA_PIECE - 1) / TMA_PIECE : 0u;   // <= 8 for any slice that fits
         if (a.dtype == 0) {
@@ -578,6 +579,14 @@ __global__ void __launch_bounds__(FNT, FNT <= 512 ? 2 : 1) fused_row_kernel(cons
                     if (m0 > tm[g0]) { tm[g0] = m0; tqs[g0] = q0 * 4; }
                     const float m1 = fmaxf(fmaxf(v1.x, v1.y), fmaxf(v1.z, v1.w));
                     if (has1 && m1 > tm[g1]) { tm[g1] = m1; tqs[g1] = (q0 + FNT) * 4; }
+                }
+            }
+            if (tid == 0 && !poisoned && row + n_clusters < a.rows) {   // next row of this cluster -> L2
+                const char* nsrc = (const char*)a.logits + (size_t)(row + n_clusters) * a.row_stride * 4 + (size_t)lo * 4;
+                if (((uintptr_t)nsrc & 15) == 0) {
+#pragma unroll 1
+                    for (uint32_t off = 0; off < body; off += TMA_PIECE)
+                        asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(nsrc + off), "r"(min(TMA_PIECE, body - off)) : "memory");
                 }
             }
             poison += poison1;
