@@ -21,7 +21,7 @@ __global__ void __launch_bounds__(NT, 1) finish_kernel(const RowArgs a, const Fu
 }
 
 // ---- small rows: at most 128 candidates (top-k 50 leaves about 60).  Four warps per row are enough,
-// every row of the batch is resident at once, and the three exact folds run in one warp by shuffles.
+// every row of the batch is resident at once, and the exact folds are short serial chains of one lane.
 
 struct FinishSmallSmem {
     unsigned long long exp_tab[32];
@@ -87,15 +87,15 @@ __global__ void __launch_bounds__(FS_NT) finish_small_kernel(const RowArgs a, co
     const uint32_t n_live = sm.n_live;
     uint32_t keep = n_live;
     if (!(top_p >= 1.0f) && n_live > 0) {
-        int found = -1;
-        warp_fold(sm.rp, (int)n_live, SEQ_FIND_GE, top_p, &found);
+        warp_prefix(sm.rp, (int)n_live, sm.p);   // sm.p is free once the candidates are ranked
+        const int found = warp_find(sm.p, (int)n_live, SEQ_FIND_GE, top_p);
         if (found >= 0) keep = (uint32_t)found + 1;
     }
     for (uint32_t j = keep + lane; j < n; j += 32) sm.sp[sm.rpos[j]] = 0.0f;
     __syncwarp();
-    const float total = warp_fold(sm.sp, (int)n, SEQ_SUM, 0.0f, nullptr);
+    const float total = warp_prefix(sm.sp, (int)n, sm.p);
     int pick = -1;
-    if (total > 1e-9f) warp_fold(sm.sp, (int)n, SEQ_FIND_GT, fmul(u01, total), &pick);
+    if (total > 1e-9f) pick = warp_find(sm.p, (int)n, SEQ_FIND_GT, fmul(u01, total));
     if (lane == 0) {
         uint32_t token = rec.amax;
         int drew = 0;

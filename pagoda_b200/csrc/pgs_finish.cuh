@@ -28,33 +28,40 @@ struct FinishSmem {
     int bcast_i;
 };
 
-// Exact left fold of n <= 128 shared-memory floats, called by one warp.  One lane does the additions: the
-// loads do not depend on the running value, so they are requested eight at a time and the dependent chain
-// is the additions alone (warp shuffles would put tens of cycles between two of them).  mode/target as in
-// seq_scan; returns the running value, *found = first index where the predicate holds or -1.
-__device__ __forceinline__ float warp_fold(const float* v, int n, int mode, float target, int* found) {
+// Exact left fold of n <= 128 shared-memory floats, called by one warp: returns the total and leaves every
+// running value in pre[0..n).  One lane does the additions: the loads do not depend on the running value, so
+// they are requested eight at a time and the dependent chain is the additions alone (warp shuffles would put
+// tens of cycles between two of them).
+__device__ __forceinline__ float warp_prefix(const float* v, int n, float* pre) {
     const int lane = threadIdx.x & 31;
     float acc = 0.0f;
-    int f = -1;
     if (lane == 0) {
 #pragma unroll 1
-        for (int j0 = 0; j0 < n && f < 0; j0 += 8) {
+        for (int j0 = 0; j0 < n; j0 += 8) {
             float x[8];
 #pragma unroll
             for (int u = 0; u < 8; u++) x[u] = (j0 + u < n) ? v[j0 + u] : 0.0f;
 #pragma unroll
             for (int u = 0; u < 8; u++) {
-                if (j0 + u < n && f < 0) {
-                    acc = fadd(acc, x[u]);
-                    if (mode != SEQ_SUM && seq_pred(mode, acc, target)) f = j0 + u;
-                }
+                acc = fadd(acc, x[u]);
+                if (j0 + u < n) pre[j0 + u] = acc;
             }
         }
     }
-    acc = __shfl_sync(FULL, acc, 0);
-    f = __shfl_sync(FULL, f, 0);
-    if (found) *found = f;
-    return acc;
+    __syncwarp();
+    return __shfl_sync(FULL, acc, 0);
+}
+
+// First index whose running value satisfies the predicate (mode/target as in seq_scan), or -1; one warp.
+__device__ __forceinline__ int warp_find(const float* pre, int n, int mode, float target) {
+    const int lane = threadIdx.x & 31;
+#pragma unroll 1
+    for (int base = 0; base < n; base += 32) {
+        const int j = base + lane;
+        const unsigned hit = __ballot_sync(FULL, j < n && seq_pred(mode, pre[j], target));
+        if (hit) return base + __ffs(hit) - 1;
+    }
+    return -1;
 }
 
 
@@ -110,7 +117,8 @@ __device__ __forceinline__ void finish_row(FinishSmem& sm, const RowArgs& a, uin
         int found = -1;
         if (n_live <= 128) {
             if (tid < 32) {
-                warp_fold(sm.rp, (int)n_live, SEQ_FIND_GE, top_p, &found);
+                warp_prefix(sm.rp, (int)n_live, sm.p);   // sm.p is free once the candidates are ranked
+                found = warp_find(sm.p, (int)n_live, SEQ_FIND_GE, top_p);
                 if (tid == 0) sm.bcast_i = found;
             }
             __syncthreads();
@@ -128,9 +136,9 @@ __device__ __forceinline__ void finish_row(FinishSmem& sm, const RowArgs& a, uin
     int pick = -1;
     if (n <= 128) {
         if (tid < 32) {
-            const float tt = warp_fold(sm.sp, (int)n, SEQ_SUM, 0.0f, nullptr);
+            const float tt = warp_prefix(sm.sp, (int)n, sm.p);
             int f = -1;
-            if (tt > 1e-9f) warp_fold(sm.sp, (int)n, SEQ_FIND_GT, fmul(u01, tt), &f);
+            if (tt > 1e-9f) f = warp_find(sm.p, (int)n, SEQ_FIND_GT, fmul(u01, tt));
             if (tid == 0) { sm.bcast_f = tt; sm.bcast_i = f; }
         }
         __syncthreads();
