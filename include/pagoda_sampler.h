@@ -208,6 +208,32 @@ typedef struct pgs_tp_out {
 } pgs_tp_out;
 PGS_API int pgs_tp_merge(pgs_handle *h, const pgs_tp_desc *desc, const void *records_all,
                          const pgs_tp_out *out, void *cuda_stream);
+/* The same exchange without a collective between the two kernels (no reference counterpart): the emitting
+ * kernel stores each finished record into slot [shard_rank][row] of EVERY rank's gather buffer -- peer
+ * memory over NVLink, mapped by the caller (CUDA IPC or symmetric memory) -- and, when its last row is out,
+ * raises flag [shard_rank] in every rank's flag array to `epoch` (system-scope release).  pgs_tp_merge_wait
+ * is pgs_tp_merge preceded by a bounded wait (about one second) for all n_shards flags of this rank to
+ * reach `epoch`; when a shard never answers, the rows get status PGS_ROW_LOAD_TIMEOUT instead of a hang.
+ *   peer_records[p]  rank p's gather buffer, [n_shards][rows][pgs_tp_record_bytes(cand)], p = 0..n_shards-1
+ *   peer_flags[p]    rank p's flag array, [n_shards] uint32, zero before the first step
+ *   epoch            1, 2, 3, ... one per step, the same on every rank
+ * Both pointer arrays live in host memory.  Buffers and flags must be double-buffered by the caller
+ * (epoch parity): a rank may start step k+1 while a peer still merges step k, never step k+2.  Run at most
+ * one push per handle at a time. */
+/* Buffers for that exchange.  pgs_peer_alloc: zeroed device memory on the handle's device plus the 64-byte
+ * CUDA IPC handle a peer process needs to map it.  pgs_peer_open: maps a peer's buffer into this process
+ * for the handle's device (peer access is enabled on the way) and proves the mapping with a 4-byte copy, so
+ * that an unreachable peer is an error code here and not a fault in a kernel later.  Close what was opened
+ * and free what was allocated before pgs_destroy. */
+PGS_API int pgs_peer_alloc(pgs_handle *h, size_t bytes, void **dev_ptr, unsigned char ipc_handle_out[64]);
+PGS_API int pgs_peer_open(pgs_handle *h, const unsigned char ipc_handle[64], void **dev_ptr);
+PGS_API int pgs_peer_close(pgs_handle *h, void *dev_ptr);
+PGS_API int pgs_peer_free(pgs_handle *h, void *dev_ptr);
+PGS_API int pgs_tp_partial_push(pgs_handle *h, const pgs_tp_desc *desc, void *const *peer_records,
+                                uint32_t *const *peer_flags, uint32_t epoch, void *cuda_stream);
+PGS_API int pgs_tp_merge_wait(pgs_handle *h, const pgs_tp_desc *desc, const void *records_all,
+                              const uint32_t *flags, uint32_t epoch, const pgs_tp_out *out, void *cuda_stream);
+
 /* Draft verification over per-position argmax ids (pagoda-hf/src/qwen3_5.rs:663-755 produces
  * them; the reference leaves the accept rule open): accepted[s] = length of the longest prefix
  * with row_argmax[s][j] == draft[s][j]; next[s] = the argmax at the first mismatch, or of the

@@ -24,7 +24,8 @@ EXPORTS = ["pgs_create", "pgs_destroy", "pgs_last_error", "pgs_mask_table_upload
            "pgs_grammar_regex", "pgs_grammar_json", "pgs_grammar_free", "pgs_grammar_n_states",
            "pgs_grammar_build_table", "pgs_grammar_state_new", "pgs_grammar_state_reset", "pgs_grammar_state_free",
            "pgs_grammar_advance", "pgs_grammar_mask_state", "pgs_grammar_state_info",
-           "pgs_log_softmax", "pgs_tp_record_bytes", "pgs_tp_partial", "pgs_tp_merge", "pgs_draft_accept"]
+           "pgs_log_softmax", "pgs_tp_record_bytes", "pgs_tp_partial", "pgs_tp_merge", "pgs_tp_partial_push",
+           "pgs_tp_merge_wait", "pgs_peer_alloc", "pgs_peer_open", "pgs_peer_close", "pgs_peer_free", "pgs_draft_accept"]
 
 
 class SamplerError(RuntimeError):
@@ -116,6 +117,14 @@ def load_library():
     L.pgs_tp_record_bytes.argtypes = [C.c_uint32]
     L.pgs_tp_partial.argtypes = [C.c_void_p, C.POINTER(TpDesc), C.c_void_p, C.c_void_p]
     L.pgs_tp_merge.argtypes = [C.c_void_p, C.POINTER(TpDesc), C.c_void_p, C.POINTER(TpOut), C.c_void_p]
+    L.pgs_tp_partial_push.argtypes = [C.c_void_p, C.POINTER(TpDesc), C.POINTER(C.c_void_p), C.POINTER(C.c_void_p),
+                                      C.c_uint32, C.c_void_p]
+    L.pgs_peer_alloc.argtypes = [C.c_void_p, C.c_size_t, C.POINTER(C.c_void_p), C.c_char_p]
+    L.pgs_peer_open.argtypes = [C.c_void_p, C.c_char_p, C.POINTER(C.c_void_p)]
+    L.pgs_peer_close.argtypes = [C.c_void_p, C.c_void_p]
+    L.pgs_peer_free.argtypes = [C.c_void_p, C.c_void_p]
+    L.pgs_tp_merge_wait.argtypes = [C.c_void_p, C.POINTER(TpDesc), C.c_void_p, C.c_void_p, C.c_uint32,
+                                    C.POINTER(TpOut), C.c_void_p]
     L.pgs_draft_accept.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_uint32, C.c_uint32, C.c_void_p,
                                    C.c_void_p, C.c_void_p]
     L.pgs_stream.restype = C.c_void_p
@@ -470,6 +479,59 @@ class Sampler:
         d = self._tp_desc(rows, vocab, n_shards, rank, cand, None, temperature, top_p, uniform)
         self._check(self._lib.pgs_tp_merge(self._h, C.byref(d), records_all.data_ptr(), C.byref(o),
                                            self._stream(stream_ptr)))
+        return out
+
+    def peer_alloc(self, nbytes: int):
+        """Zeroed device memory that peers can map: -> (device address, 64-byte IPC handle)."""
+        ptr = C.c_void_p()
+        handle = C.create_string_buffer(64)
+        self._check(self._lib.pgs_peer_alloc(self._h, nbytes, C.byref(ptr), handle))
+        return int(ptr.value), handle.raw
+
+    def peer_open(self, ipc_handle: bytes) -> int:
+        """Map a peer's buffer for this sampler's device: -> device address."""
+        ptr = C.c_void_p()
+        self._check(self._lib.pgs_peer_open(self._h, C.create_string_buffer(ipc_handle, 64), C.byref(ptr)))
+        return int(ptr.value)
+
+    def peer_close(self, addr: int):
+        self._check(self._lib.pgs_peer_close(self._h, C.c_void_p(addr)))
+
+    def peer_free(self, addr: int):
+        self._check(self._lib.pgs_peer_free(self._h, C.c_void_p(addr)))
+
+    def tp_partial_push(self, shard_logits, vocab, n_shards, rank, cand, peer_record_ptrs, peer_flag_ptrs, epoch,
+                        temperature=None, stream_ptr=None):
+        """Emit this rank's records straight into every rank's gather buffer (peer stores) and raise this
+        shard's flag there.  peer_record_ptrs / peer_flag_ptrs: device addresses (ints), one per rank, of the
+        [n_shards, rows, record_bytes] gather buffers and the [n_shards] uint32 flag arrays of this epoch."""
+        rows = shard_logits.shape[0]
+        d = self._tp_desc(rows, vocab, n_shards, rank, cand, shard_logits, temperature)
+        recs = (C.c_void_p * n_shards)(*[int(p) for p in peer_record_ptrs])
+        flags = (C.c_void_p * n_shards)(*[int(p) for p in peer_flag_ptrs])
+        self._check(self._lib.pgs_tp_partial_push(self._h, C.byref(d), recs, flags, C.c_uint32(epoch),
+                                                  self._stream(stream_ptr)))
+
+    def tp_merge_wait(self, records_all, flags, epoch, vocab, n_shards, rank, cand, temperature=None, top_p=None,
+                      uniform=None, stream_ptr=None):
+        """tp_merge preceded, on the device, by a bounded wait until all n_shards flags of this rank have
+        reached `epoch`.  records_all [n_shards, rows, record_bytes] uint8, flags [n_shards] int32/uint32."""
+        import torch
+        rows = records_all.shape[1]
+        dev = records_all.device
+        out = dict(token=torch.zeros(rows, dtype=torch.int32, device=dev),
+                   status=torch.full((rows,), -1, dtype=torch.int32, device=dev),
+                   drew=torch.zeros(rows, dtype=torch.uint8, device=dev),
+                   argmax=torch.zeros(rows, dtype=torch.int32, device=dev),
+                   gmax=torch.zeros(rows, dtype=torch.float32, device=dev),
+                   gsum=torch.zeros(rows, dtype=torch.float32, device=dev),
+                   total=torch.zeros(rows, dtype=torch.float32, device=dev),
+                   n_kept=torch.zeros(rows, dtype=torch.int32, device=dev))
+        o = TpOut(**{k: v.data_ptr() for k, v in out.items()})
+        d = self._tp_desc(rows, vocab, n_shards, rank, cand, None, temperature, top_p, uniform)
+        self._check(self._lib.pgs_tp_merge_wait(self._h, C.byref(d), C.c_void_p(records_all.data_ptr()),
+                                                C.c_void_p(flags.data_ptr()), C.c_uint32(epoch), C.byref(o),
+                                                self._stream(stream_ptr)))
         return out
 
     def draft_accept(self, row_argmax, draft, stream_ptr=None):

@@ -14,6 +14,7 @@
 
 #include "pgs_args.cuh"
 #include "pgs_fused.cuh"
+#include "pgs_tp.cuh"
 
 namespace pgs {
 cudaError_t configure_general();
@@ -27,20 +28,6 @@ cudaError_t configure_fused(size_t max_smem);
 cudaError_t fused_max_clusters(uint32_t cluster, size_t smem, int* out);
 cudaError_t launch_fused(const RowArgs& a, const FusedLaunch& fl, uint32_t n_clusters, size_t smem,
                          cudaStream_t stream);
-struct TpArgs {
-    const float* logits;
-    unsigned long long row_stride;
-    uint32_t rows, vocab, shard_vocab, shard_lo, n_shards, cand;
-    const float* temperature;
-    const float* top_p;
-    const float* uniform;
-    unsigned char* records;
-    uint32_t rec_bytes;
-};
-struct TpOut {
-    uint32_t* token; int32_t* status; uint8_t* drew; uint32_t* argmax;
-    float* gmax; float* gsum; float* total; uint32_t* n_kept;
-};
 struct ScoreArgs {
     const float* logits;
     unsigned long long row_stride;
@@ -94,6 +81,7 @@ struct pgs_handle {
     size_t fused_smem = 0;
     uint32_t* work_rows = nullptr;
     uint32_t* work_count = nullptr;   // [2]
+    uint32_t* tp_done = nullptr;      // CTAs finished in the current peer-store push
     pgs::RowRec* recs = nullptr;      // [max_rows]
     uint32_t* cand_id = nullptr;      // [max_rows x F_MCAP]
     float* cand_x = nullptr;
@@ -154,7 +142,7 @@ static int destroy_impl(pgs_handle* h) {
     }
     cudaFree(h->sx); cudaFree(h->sl_id); cudaFree(h->sl_p); cudaFree(h->sl_key);
     cudaFree(h->sh_key); cudaFree(h->sh_cnt); cudaFree(h->tables_dev);
-    cudaFree(h->logits_stage); cudaFree(h->aux_dev); cudaFree(h->work_rows); cudaFree(h->work_count); cudaFree(h->prof);
+    cudaFree(h->logits_stage); cudaFree(h->aux_dev); cudaFree(h->work_rows); cudaFree(h->work_count); cudaFree(h->tp_done); cudaFree(h->prof);
     cudaFree(h->recs); cudaFree(h->cand_id); cudaFree(h->cand_x);
     if (h->aux_host) cudaFreeHost(h->aux_host);
     if (h->side) { cudaStreamSynchronize(h->side); cudaStreamDestroy(h->side); }
@@ -208,6 +196,8 @@ extern "C" int pgs_create(int device, uint32_t max_rows, uint32_t max_vocab, uin
         PGS_CUDA(nullptr, cudaMalloc(&h->work_rows, (size_t)max_rows * sizeof(uint32_t)));
         PGS_CUDA(nullptr, cudaMalloc(&h->work_count, 2 * sizeof(uint32_t)));
         PGS_CUDA(nullptr, cudaMemsetAsync(h->work_count, 0, 2 * sizeof(uint32_t), h->stream));
+        PGS_CUDA(nullptr, cudaMalloc(&h->tp_done, sizeof(uint32_t)));
+        PGS_CUDA(nullptr, cudaMemsetAsync(h->tp_done, 0, sizeof(uint32_t), h->stream));
         if (const char* ev = getenv("PGS_EXACT")) h->exact = atoi(ev);
         if (const char* ev = getenv("PGS_PROFILE")) {
             if (atoi(ev)) {
@@ -596,6 +586,9 @@ static int tp_args(pgs_handle* h, const pgs_tp_desc* d, pgs::TpArgs* a) {
     a->shard_lo = d->shard_rank * a->shard_vocab; a->n_shards = d->n_shards; a->cand = d->cand;
     a->temperature = d->temperature; a->top_p = d->top_p; a->uniform = d->uniform;
     a->rec_bytes = (uint32_t)pgs_tp_record_bytes(d->cand);
+    memset(a->peer_records, 0, sizeof a->peer_records);
+    memset(a->peer_flags, 0, sizeof a->peer_flags);
+    a->flags = nullptr; a->done = nullptr; a->epoch = 0; a->shard_rank = d->shard_rank;
     return PGS_OK;
 }
 
@@ -623,6 +616,116 @@ extern "C" int pgs_tp_merge(pgs_handle* h, const pgs_tp_desc* d, const void* rec
         return fail(h, PGS_ERR_INVALID, "records_all, out->token and out->status are required");
     DeviceGuard g(h->device);
     a.records = (unsigned char*)records_all;
+    pgs::TpOut o{out->token, out->status, out->drew, out->argmax, out->gmax, out->gsum, out->total, out->n_kept};
+    PGS_CUDA(h, pgs::launch_tp_merge(a, o, cuda_stream ? (cudaStream_t)cuda_stream : h->stream));
+    h->counters.kernel_launches += 1;
+    h->counters.rows += a.rows;
+    return PGS_OK;
+}
+
+extern "C" int pgs_peer_alloc(pgs_handle* h, size_t bytes, void** dev_ptr, unsigned char ipc_handle_out[64]) {
+    if (!h || !dev_ptr || !ipc_handle_out || bytes == 0) return PGS_ERR_INVALID;
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "the IPC handle is exchanged as 64 bytes");
+    DeviceGuard g(h->device);
+    void* p = nullptr;
+    PGS_CUDA(h, cudaMalloc(&p, bytes));
+    cudaError_t e = cudaMemset(p, 0, bytes);
+    cudaIpcMemHandle_t ih;
+    if (e == cudaSuccess) e = cudaIpcGetMemHandle(&ih, p);
+    if (e != cudaSuccess) {
+        cudaFree(p);
+        return fail(h, PGS_ERR_CUDA, "pgs_peer_alloc: %s", cudaGetErrorString(e));
+    }
+    memcpy(ipc_handle_out, &ih, sizeof ih);
+    *dev_ptr = p;
+    return PGS_OK;
+}
+
+extern "C" int pgs_peer_open(pgs_handle* h, const unsigned char ipc_handle[64], void** dev_ptr) {
+    if (!h || !dev_ptr || !ipc_handle) return PGS_ERR_INVALID;
+    DeviceGuard g(h->device);
+    cudaIpcMemHandle_t ih;
+    memcpy(&ih, ipc_handle, sizeof ih);
+    void* p = nullptr;
+    PGS_CUDA(h, cudaIpcOpenMemHandle(&p, ih, cudaIpcMemLazyEnablePeerAccess));
+    // prove that this device reaches the mapping before any kernel is pointed at it
+    uint32_t probe = 0;
+    const cudaError_t e = cudaMemcpy(&probe, p, sizeof probe, cudaMemcpyDeviceToHost);
+    if (e != cudaSuccess) {
+        cudaIpcCloseMemHandle(p);
+        return fail(h, PGS_ERR_CUDA, "pgs_peer_open: the mapped buffer is not readable from device %d: %s", h->device,
+                    cudaGetErrorString(e));
+    }
+    *dev_ptr = p;
+    return PGS_OK;
+}
+
+extern "C" int pgs_peer_close(pgs_handle* h, void* dev_ptr) {
+    if (!h || !dev_ptr) return PGS_ERR_INVALID;
+    DeviceGuard g(h->device);
+    PGS_CUDA(h, cudaIpcCloseMemHandle(dev_ptr));
+    return PGS_OK;
+}
+
+extern "C" int pgs_peer_free(pgs_handle* h, void* dev_ptr) {
+    if (!h || !dev_ptr) return PGS_ERR_INVALID;
+    DeviceGuard g(h->device);
+    PGS_CUDA(h, cudaFree(dev_ptr));
+    return PGS_OK;
+}
+
+extern "C" int pgs_tp_partial_push(pgs_handle* h, const pgs_tp_desc* d, void* const* peer_records,
+                                   uint32_t* const* peer_flags, uint32_t epoch, void* cuda_stream) {
+    if (!h) return PGS_ERR_INVALID;
+    pgs::TpArgs a;
+    int rc = tp_args(h, d, &a);
+    if (rc != PGS_OK) return rc;
+    if (!d->logits || !peer_records || !peer_flags) return fail(h, PGS_ERR_INVALID, "logits, peer_records and peer_flags are required");
+    for (uint32_t p = 0; p < d->n_shards; p++) {
+        if (!peer_records[p] || !peer_flags[p]) return fail(h, PGS_ERR_INVALID, "peer %u: NULL gather buffer or flag array", p);
+        // this shard's block inside rank p's [n_shards][rows][record] buffer
+        a.peer_records[p] = (unsigned char*)peer_records[p] + (size_t)d->shard_rank * a.rows * a.rec_bytes;
+        a.peer_flags[p] = peer_flags[p];
+    }
+    DeviceGuard g(h->device);
+    // every buffer must be device memory this GPU can reach: its own, or a peer's with peer access enabled
+    // (enabled here when it is not yet; an IPC mapping alone does not do that for this device)
+    for (uint32_t p = 0; p < d->n_shards; p++) {
+        const void* ptrs[2] = {peer_records[p], peer_flags[p]};
+        for (const void* ptr : ptrs) {
+            cudaPointerAttributes at;
+            PGS_CUDA(h, cudaPointerGetAttributes(&at, ptr));
+            if (at.type != cudaMemoryTypeDevice) return fail(h, PGS_ERR_INVALID, "peer %u: not device memory", p);
+            if (at.device == h->device) continue;
+            int can = 0;
+            PGS_CUDA(h, cudaDeviceCanAccessPeer(&can, h->device, at.device));
+            if (!can) return fail(h, PGS_ERR_INVALID, "device %d cannot access memory of device %d", h->device, at.device);
+            const cudaError_t e = cudaDeviceEnablePeerAccess(at.device, 0);
+            if (e == cudaErrorPeerAccessAlreadyEnabled) cudaGetLastError();
+            else if (e != cudaSuccess) return fail(h, PGS_ERR_CUDA, "cudaDeviceEnablePeerAccess(%d): %s", at.device, cudaGetErrorString(e));
+        }
+    }
+    a.records = a.peer_records[d->shard_rank];   // built in this rank's own buffer, then copied out
+    a.done = h->tp_done;                         // zero between launches
+    a.epoch = epoch;
+    const uint32_t grid = a.rows < (uint32_t)h->sm_count ? a.rows : (uint32_t)h->sm_count;
+    PGS_CUDA(h, pgs::launch_tp_partial(a, grid, cuda_stream ? (cudaStream_t)cuda_stream : h->stream));
+    h->counters.kernel_launches += 1;
+    return PGS_OK;
+}
+
+extern "C" int pgs_tp_merge_wait(pgs_handle* h, const pgs_tp_desc* d, const void* records_all, const uint32_t* flags,
+                                 uint32_t epoch, const pgs_tp_out* out, void* cuda_stream) {
+    if (!h) return PGS_ERR_INVALID;
+    pgs::TpArgs a;
+    int rc = tp_args(h, d, &a);
+    if (rc != PGS_OK) return rc;
+    if (!records_all || !flags || !out || !out->token || !out->status)
+        return fail(h, PGS_ERR_INVALID, "records_all, flags, out->token and out->status are required");
+    DeviceGuard g(h->device);
+    a.records = (unsigned char*)records_all;
+    a.flags = (uint32_t*)flags;
+    a.epoch = epoch;
     pgs::TpOut o{out->token, out->status, out->drew, out->argmax, out->gmax, out->gsum, out->total, out->n_kept};
     PGS_CUDA(h, pgs::launch_tp_merge(a, o, cuda_stream ? (cudaStream_t)cuda_stream : h->stream));
     h->counters.kernel_launches += 1;

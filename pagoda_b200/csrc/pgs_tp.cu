@@ -5,7 +5,10 @@
 //   fixed-size record: its max m_r, its own sequential f32 sum s_r = sum exp((x - m_r) / t) (same
 //   arithmetic as pagoda/src/sampler.rs:92-114 on the shard), its argmax and its `cand` largest
 //   logits by (value descending, id ascending) with their global ids;
-//   the records of all shards are all-gathered (NCCL, or peer stores) and merged on every GPU:
+//   the records of all shards are gathered on every GPU -- by an NCCL all-gather between the two kernels,
+//   or by the emitting kernel itself, which stores its records into every peer's gather buffer over
+//   NVLink and then raises a per-shard flag there that the peer's merge kernel waits for (bounded) --
+//   and merged on every GPU:
 //   M = max m_r, S = sum_r s_r * exp((m_r - M) / t) folded in shard order, candidate probability
 //   exp((x - M) / t) / S, then the reference's top-p rule, total and inverse-CDF walk over the
 //   union of the candidates; greedy rows take the best candidate, lowest id on ties, which is the
@@ -14,21 +17,22 @@
 // Draft verification (pagoda-hf/src/qwen3_5.rs:663-755 returns per-position argmax ids; the accept
 // rule itself is defined here): accept while argmax(row j) == draft[j].
 #include "pgs_finish.cuh"
+#include "pgs_tp.cuh"
 
 namespace pgs {
 
 constexpr int TP_LIST = 1024;
 
-struct TpArgs {
-    const float* logits;            // [rows x row_stride] this rank's columns
-    unsigned long long row_stride;
-    uint32_t rows, vocab, shard_vocab, shard_lo, n_shards, cand;
-    const float* temperature;
-    const float* top_p;
-    const float* uniform;
-    unsigned char* records;         // partial: out [rows x rec_bytes]; merge: in [n_shards x rows x rec_bytes]
-    uint32_t rec_bytes;
-};
+// system-scope flag accesses: the store publishes everything this GPU wrote before it (records in peer
+// memory included), the load makes it visible to the reader
+__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
+    uint32_t v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
 
 struct TpRecHead { float m; float s; uint32_t n; uint32_t argmax; };   // then float x[cand], uint32 id[cand]
 
@@ -41,6 +45,19 @@ struct TpPartialSmem {
     uint32_t lid[TP_LIST];
     uint32_t ln;
 };
+
+// Copies the finished record of `row` from this rank's gather buffer into the same slot of every other
+// rank's (plain stores into peer memory).  Called by the whole CTA after a barrier.
+__device__ __forceinline__ void push_record(const TpArgs& a, uint32_t row) {
+    if (!a.done) return;
+    const uint32_t words = a.rec_bytes / 4u;
+    const uint32_t* src = reinterpret_cast<const uint32_t*>(a.records + (size_t)row * a.rec_bytes);
+    for (uint32_t w = threadIdx.x; w < words; w += NT) {
+        const uint32_t v = src[w];
+        for (uint32_t p = 0; p < a.n_shards; p++)
+            if (p != a.shard_rank) reinterpret_cast<uint32_t*>(a.peer_records[p] + (size_t)row * a.rec_bytes)[w] = v;
+    }
+}
 
 __global__ void __launch_bounds__(NT, 1) tp_partial_kernel(const TpArgs a) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -71,6 +88,8 @@ __global__ void __launch_bounds__(NT, 1) tp_partial_kernel(const TpArgs a) {
         best = block_max_u64(best, sm.rs);
         if (nonfinite) {   // the merge reports the row as faulted when any shard saw a non-finite logit
             if (tid == 0) { head->m = NAN; head->s = 0.0f; head->n = 0; head->argmax = 0; }
+            __syncthreads();
+            push_record(a, row);
             continue;
         }
         const float m = best ? key_to_float((uint32_t)(best >> 32)) : -INFINITY;
@@ -114,6 +133,16 @@ __global__ void __launch_bounds__(NT, 1) tp_partial_kernel(const TpArgs a) {
         }
         if (tid == 0) { head->m = m; head->s = s; head->n = want; head->argmax = amax; }
         __syncthreads();
+        push_record(a, row);
+    }
+    if (a.done) {   // peer-store exchange: the last CTA of the launch raises this shard's flag on every rank
+        __threadfence_system();
+        __syncthreads();
+        if (tid == 0 && atomicAdd(a.done, 1u) == gridDim.x - 1u) {
+            *a.done = 0u;
+            __threadfence_system();
+            for (uint32_t p = 0; p < a.n_shards; p++) st_release_sys(a.peer_flags[p] + a.shard_rank, a.epoch);
+        }
     }
 }
 
@@ -126,10 +155,6 @@ struct TpMergeSmem {
     int fault;
 };
 
-struct TpOut {
-    uint32_t* token; int32_t* status; uint8_t* drew; uint32_t* argmax;
-    float* gmax; float* gsum; float* total; uint32_t* n_kept;
-};
 
 __global__ void __launch_bounds__(NT, 1) tp_merge_kernel(const TpArgs a, const TpOut o) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -139,6 +164,24 @@ __global__ void __launch_bounds__(NT, 1) tp_merge_kernel(const TpArgs a, const T
     const float temp = a.temperature ? a.temperature[row] : 0.0f;
     const float t = fmaxf(temp, 1e-9f);
     if (tid < 32) sm.fin.exp_tab[tid] = kExp2TableDev[tid];
+    if (a.flags) {   // peer-store exchange: wait (bounded, about a second) until every shard has raised its flag
+        if (tid == 0) {
+            int late = 0;
+            for (uint32_t r = 0; r < a.n_shards && !late; r++) {
+                uint32_t spin = 0;
+                while ((int32_t)(ld_acquire_sys(a.flags + r) - a.epoch) < 0) {
+                    if (++spin > (1u << 21)) { late = 1; break; }
+                    __nanosleep(500);
+                }
+            }
+            sm.fault = late;
+        }
+        __syncthreads();
+        if (sm.fault) {
+            if (tid == 0) { o.token[row] = 0; o.status[row] = ROW_LOAD_TIMEOUT; if (o.drew) o.drew[row] = 0; }
+            return;
+        }
+    }
     __syncthreads();
     auto rec = [&](uint32_t r) {
         return reinterpret_cast<const TpRecHead*>(a.records + ((size_t)r * a.rows + row) * a.rec_bytes);

@@ -36,6 +36,39 @@ def _run_tp(sampler, x, n_shards, cand, temp, top_p, uniform):
     return {k: v.cpu().numpy() for k, v in out.items()}
 
 
+def test_tp_peer_store_path_on_one_device(sampler, oracle):
+    """The peer-store exchange with every 'peer' on this device: each shard pushes its records into the one
+    gather buffer and raises its flag, the waiting merge finds all flags up.  (Across GPUs: tp_worker.py.)"""
+    import torch
+    from pagoda_b200 import synth
+    dev = torch.device("cuda:0")
+    rows, vocab, n_shards, cand = 12, 151936, 4, 64
+    x = synth.normal_f32(61, rows * vocab, 2.0).reshape(rows, vocab)
+    temp = np.array([1.0, 1.0, 0.7, 0.0, 0.3, 1.5, 1.0, 0.0, 2.0, 1.0, 0.5, 1.0], np.float32)
+    top_p = np.array([0.95, 1.0, 0.5, 1.0, 0.95, 0.95, 0.2, 0.9, 0.95, 0.01, 0.95, 0.6], np.float32)
+    u = synth.uniform_f32(9, rows)
+    xt, t = torch.from_numpy(x).to(dev), torch.from_numpy(temp).to(dev)
+    tp, tu = torch.from_numpy(top_p).to(dev), torch.from_numpy(u).to(dev)
+    per = vocab // n_shards
+    buf = torch.zeros((2, n_shards, rows, sampler.tp_record_bytes(cand)), dtype=torch.uint8, device=dev)
+    flags = torch.zeros((2, n_shards), dtype=torch.int32, device=dev)
+    st = torch.cuda.current_stream().cuda_stream
+    for epoch in (1, 2, 3):
+        par = epoch & 1
+        for r in range(n_shards):
+            sampler.tp_partial_push(xt[:, r * per:(r + 1) * per], vocab, n_shards, r, cand,
+                                    [buf[par].data_ptr()] * n_shards, [flags[par].data_ptr()] * n_shards, epoch,
+                                    temperature=t, stream_ptr=st)
+        out = sampler.tp_merge_wait(buf[par], flags[par], epoch, vocab, n_shards, 0, cand, temperature=t, top_p=tp,
+                                    uniform=tu, stream_ptr=st)
+        torch.cuda.synchronize()
+        assert flags[par].cpu().tolist() == [epoch] * n_shards
+        tok, status = out["token"].cpu().numpy(), out["status"].cpu().numpy()
+        for r in range(rows):
+            want = oracle.tp_sample_row(x[r], n_shards, cand, float(temp[r]), float(top_p[r]), float(u[r]))
+            assert status[r] == want.status and tok[r] == want.token, (epoch, r, tok[r], want.token)
+
+
 @pytest.mark.parametrize("n_shards,vocab", [(2, 151936), (4, 151936), (8, 151936), (4, 4096), (1, 1000)])
 def test_tp_matches_oracle(sampler, oracle, n_shards, vocab):
     from pagoda_b200 import synth
@@ -91,5 +124,5 @@ def test_tp_two_ranks_over_nccl():
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
            "127.0.0.1", "--master-port", "29517", os.path.join(root, "tests", "tp_worker.py")]
     out = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
-    assert out.returncode == 0, out.stdout[-2000:] + out.stderr[-2000:]
+    assert out.returncode == 0, out.stdout[-3000:] + out.stderr[-6000:]
     assert "TP_OK" in out.stdout

@@ -45,7 +45,50 @@ def main():
     ref = out["token"].clone()
     dist.broadcast(ref, 0)
     assert torch.equal(ref, out["token"])
+    # the same steps without a collective: records stored straight into the peers' gather buffers, flags
+    # raised there, and the merge kernel waiting (bounded) for them; three steps exercise both buffer parities
+    from pagoda_b200.parallel import PeerExchange
+    px = PeerExchange(s, rows, s.tp_record_bytes(cand), dev)
+    shard = torch.from_numpy(np.ascontiguousarray(x[:, lo:hi])).to(dev)
+    for step in range(3):
+        epoch, par, rec_ptrs, flag_ptrs = px.next_step()
+        s.tp_partial_push(shard, vocab, world, rank, cand, rec_ptrs, flag_ptrs, epoch, temperature=t, stream_ptr=stream)
+        out2 = s.tp_merge_wait(px.buf[par], px.flags[par], epoch, vocab, world, rank, cand, temperature=t, top_p=tp,
+                               uniform=tu, stream_ptr=stream)
+        torch.cuda.synchronize()
+        assert int(out2["status"].max()) <= 3, out2["status"]   # no load timeout
+        for k in ("token", "status", "argmax", "n_kept"):
+            assert torch.equal(out2[k], out[k]), (step, k)
+        for k in ("gmax", "gsum", "total"):
+            assert torch.equal(out2[k].view(torch.int32), out[k].view(torch.int32)), (step, k)
+    # rough cost of the exchange itself (CUDA events on this rank's stream, both paths back to back)
+    def timed(fn, n=30):
+        for _ in range(5):
+            fn()
+        torch.cuda.synchronize(); dist.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(n):
+            fn()
+        e1.record(); torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / n * 1e3
+
+    def step_nccl():
+        r = s.tp_partial(shard, vocab, world, rank, cand, temperature=t, stream_ptr=stream)
+        s.tp_merge(all_gather_records(r), vocab, world, rank, cand, temperature=t, top_p=tp, uniform=tu, stream_ptr=stream)
+
+    def step_peer():
+        epoch, par, rec_ptrs, flag_ptrs = px.next_step()
+        s.tp_partial_push(shard, vocab, world, rank, cand, rec_ptrs, flag_ptrs, epoch, temperature=t, stream_ptr=stream)
+        s.tp_merge_wait(px.buf[par], px.flags[par], epoch, vocab, world, rank, cand, temperature=t, top_p=tp,
+                        uniform=tu, stream_ptr=stream)
+
+    us_nccl, us_peer = timed(step_nccl), timed(step_peer)
+    if rank == 0:
+        print(f"TP_TIMING rows={rows} vocab={vocab} ranks={world}: nccl all-gather path {us_nccl:.1f} us/step, "
+              f"peer-store path {us_peer:.1f} us/step")
     dist.barrier()
+    px.close()
     if rank == 0:
         print("TP_OK")
     s.close()
