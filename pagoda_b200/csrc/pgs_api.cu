@@ -103,9 +103,11 @@ static int fail(pgs_handle* h, int code, const char* fmt, ...) {
 #define PGS_CUDA(h, call)                                                                  \
     do {                                                                                   \
         cudaError_t e_ = (call);                                                           \
-        if (e_ != cudaSuccess)                                                             \
+        if (e_ != cudaSuccess) {                                                           \
+            cudaGetLastError(); /* a reported error must not resurface at the next launch */ \
             return fail(h, e_ == cudaErrorMemoryAllocation ? PGS_ERR_NOMEM : PGS_ERR_CUDA, \
                         "%s: %s", #call, cudaGetErrorString(e_));                          \
+        }                                                                                  \
     } while (0)
 
 namespace {

@@ -36,6 +36,20 @@ def _run_tp(sampler, x, n_shards, cand, temp, top_p, uniform):
     return {k: v.cpu().numpy() for k, v in out.items()}
 
 
+def test_peer_buffers_alloc_zeroed_and_bad_handle_is_an_error(sampler):
+    import torch
+    import pagoda_b200
+    from pagoda_b200.parallel import _DeviceView
+    addr, handle = sampler.peer_alloc(4096)
+    assert addr % 256 == 0 and len(handle) == 64
+    view = torch.as_tensor(_DeviceView(addr, (4096,), "|u1"), device="cuda:0")
+    assert int(view.sum().item()) == 0
+    with pytest.raises(pagoda_b200.SamplerError):
+        sampler.peer_open(bytes(64))      # not a handle: an error code, nothing is mapped
+    del view
+    sampler.peer_free(addr)
+
+
 def test_tp_peer_store_path_on_one_device(sampler, oracle):
     """The peer-store exchange with every 'peer' on this device: each shard pushes its records into the one
     gather buffer and raises its flag, the waiting merge finds all flags up.  (Across GPUs: tp_worker.py.)"""
