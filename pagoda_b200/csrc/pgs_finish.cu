@@ -23,10 +23,10 @@ __global__ void __launch_bounds__(NT, 1) finish_kernel(const RowArgs a, const Fu
 // ---- small rows: at most 128 candidates (top-k 50 leaves about 60).  Four warps per row are enough,
 // every row of the batch is resident at once, and the exact folds are short serial chains of one lane.
 
-struct FinishSmallSmem {
+struct alignas(16) FinishSmallSmem {
     unsigned long long exp_tab[32];
-    uint32_t m_id[FS_NT];
-    float p[FS_NT];
+    unsigned long long key[FS_NT];   // (probability bits << 32) | ~id: one comparison ranks by (p descending, id ascending)
+    float p[FS_NT];                  // scratch of the folds
     uint32_t sid[FS_NT];
     float sp[FS_NT];
     float rp[FS_NT];
@@ -39,40 +39,51 @@ __global__ void __launch_bounds__(FS_NT) finish_small_kernel(const RowArgs a, co
     __shared__ FinishSmallSmem sm;
     const int tid = threadIdx.x, lane = tid & 31;
     const uint32_t row = blockIdx.x;
-    if (fl.recs[row].kind != 1u || fl.recs[row].n_cand > (uint32_t)FS_NT) return;
     const RowRec& rec = fl.recs[row];
+    // the record's header first (one cache line); everything else the row needs is then requested at once, so
+    // that the kernel pays two round trips to memory, not one per item
     const uint32_t n = rec.n_cand, V = a.vocab;
+    if (rec.kind != 1u || n > (uint32_t)FS_NT) return;
+    const uint32_t n_parts = rec.n_parts;
     const float m = rec.m, t = rec.t;
     const uint32_t top_k = a.top_k ? a.top_k[row] : 0u;
     const float top_p = a.top_p ? a.top_p[row] : 1.0f;
     const float u01 = a.uniform ? a.uniform[row] : 0.0f;
+    const uint32_t my_id = (uint32_t)tid < n ? fl.cand_id[(size_t)row * F_MCAP + tid] : 0u;
+    const float my_x = (uint32_t)tid < n ? fl.cand_x[(size_t)row * F_MCAP + tid] : 0.0f;
     if (tid < 32) {
         sm.exp_tab[tid] = kExp2TableDev[tid];
         double s2 = 0.0;
-        for (uint32_t r = lane; r < rec.n_parts; r += 32) s2 += rec.part[r];
+#pragma unroll 1
+        for (uint32_t r0 = 0; r0 < n_parts; r0 += 128) {   // four independent loads per lane and round
+            double q[4];
+#pragma unroll
+            for (int u = 0; u < 4; u++) q[u] = r0 + u * 32 + lane < n_parts ? rec.part[r0 + u * 32 + lane] : 0.0;
+            s2 += (q[0] + q[1]) + (q[2] + q[3]);
+        }
         for (int o = 16; o; o >>= 1) s2 += __shfl_xor_sync(FULL, s2, o);
         if (tid == 0) { sm.S = (float)s2; sm.n_live = 0; }
     }
     __syncthreads();
     const float S = sm.S;
     const bool norm = S > 1e-9f;
+    float my_p = 0.0f;
     if ((uint32_t)tid < n) {
-        sm.m_id[tid] = fl.cand_id[(size_t)row * F_MCAP + tid];
-        const float e = softmax_num(fl.cand_x[(size_t)row * F_MCAP + tid], m, t, sm.exp_tab);   // exact expf
-        sm.p[tid] = norm ? fdiv(e, S) : e;
+        const float e = softmax_num(my_x, m, t, sm.exp_tab);   // exact expf
+        my_p = norm ? fdiv(e, S) : e;
+        sm.key[tid] = ((unsigned long long)f2u(my_p) << 32) | (unsigned long long)(0xffffffffu - my_id);   // p >= 0
     }
     __syncthreads();
     if ((uint32_t)tid < n) {   // rank by id and by (probability descending, id ascending)
-        const uint32_t idj = sm.m_id[tid];
-        const float pj = sm.p[tid];
+        const unsigned long long kj = sm.key[tid];
         uint32_t r_id = 0, r_p = 0;
-        for (uint32_t o = 0; o < n; o++) {
-            const uint32_t ido = sm.m_id[o];
-            const float po = sm.p[o];
-            r_id += ido < idj;
-            r_p += (po > pj) || (po == pj && ido < idj);
+#pragma unroll 8
+        for (uint32_t o = 0; o < n; o++) {   // broadcast loads, independent of one another: requested in batches
+            const unsigned long long ko = sm.key[o];
+            r_p += ko > kj;
+            r_id += (uint32_t)ko > (uint32_t)kj;   // larger ~id = smaller id
         }
-        sm.sid[r_id] = idj; sm.sp[r_id] = pj; sm.rp[r_p] = pj; sm.rpos[r_p] = r_id;
+        sm.sid[r_id] = my_id; sm.sp[r_id] = my_p; sm.rp[r_p] = my_p; sm.rpos[r_p] = r_id;
     }
     __syncthreads();
     if ((uint32_t)tid < n) {   // top-k: every tie at the k-th probability survives; zeros never matter

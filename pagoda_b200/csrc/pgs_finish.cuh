@@ -30,22 +30,24 @@ struct FinishSmem {
 
 // Exact left fold of n <= 128 shared-memory floats, called by one warp: returns the total and leaves every
 // running value in pre[0..n).  One lane does the additions: the loads do not depend on the running value, so
-// they are requested eight at a time and the dependent chain is the additions alone (warp shuffles would put
-// tens of cycles between two of them).
+// they are requested eight at a time (two 128-bit loads) and the dependent chain is the additions alone
+// (warp shuffles would put tens of cycles between two of them).  v and pre: 16-byte aligned arrays of at
+// least 128 floats (entries past n are read and written, not used).
 __device__ __forceinline__ float warp_prefix(const float* v, int n, float* pre) {
     const int lane = threadIdx.x & 31;
     float acc = 0.0f;
     if (lane == 0) {
 #pragma unroll 1
         for (int j0 = 0; j0 < n; j0 += 8) {
-            float x[8];
-#pragma unroll
-            for (int u = 0; u < 8; u++) x[u] = (j0 + u < n) ? v[j0 + u] : 0.0f;
+            const float4 lo4 = *reinterpret_cast<const float4*>(v + j0), hi4 = *reinterpret_cast<const float4*>(v + j0 + 4);
+            float x[8] = {lo4.x, lo4.y, lo4.z, lo4.w, hi4.x, hi4.y, hi4.z, hi4.w};
 #pragma unroll
             for (int u = 0; u < 8; u++) {
-                acc = fadd(acc, x[u]);
-                if (j0 + u < n) pre[j0 + u] = acc;
+                acc = fadd(acc, j0 + u < n ? x[u] : 0.0f);
+                x[u] = acc;
             }
+            *reinterpret_cast<float4*>(pre + j0) = make_float4(x[0], x[1], x[2], x[3]);
+            *reinterpret_cast<float4*>(pre + j0 + 4) = make_float4(x[4], x[5], x[6], x[7]);
         }
     }
     __syncwarp();
@@ -87,7 +89,8 @@ __device__ __forceinline__ void finish_row(FinishSmem& sm, const RowArgs& a, uin
         const uint32_t idj = sm.m_id[j];
         const float pj = sm.p[j];
         uint32_t r_id = 0, r_p = 0;
-        for (uint32_t o = 0; o < n; o++) {
+#pragma unroll 8
+        for (uint32_t o = 0; o < n; o++) {   // broadcast loads, independent of one another: requested in batches
             const uint32_t ido = sm.m_id[o];
             const float po = sm.p[o];
             r_id += ido < idj;
