@@ -7,17 +7,28 @@ namespace pgs {
 
 constexpr int FS_NT = 128;   // rows with at most this many candidates take finish_small_kernel
 
-__global__ void __launch_bounds__(NT, 1) finish_kernel(const RowArgs a, const FusedLaunch fl) {
+// (At most 48 registers per thread: a CTA of this kernel must fit on an SM beside the CTAs of
+// finish_small_kernel, or the usually empty pass would queue behind them and lengthen every step.)
+__global__ void __maxnreg__(48) finish_kernel(const RowArgs a, const FusedLaunch fl) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     FinishSmem& sm = *reinterpret_cast<FinishSmem*>(smem_raw);
-    const uint32_t row = blockIdx.x;
-    if (fl.recs[row].kind != 1u || fl.recs[row].n_cand <= (uint32_t)FS_NT) return;   // small rows: finish_small_kernel
-    const RowRec& rec = fl.recs[row];
-    double s2 = 0.0;
-    for (uint32_t r = 0; r < rec.n_parts; r++) s2 += rec.part[r];
-    finish_row(sm, a, row, a.vocab, fl.cand_id + (size_t)row * F_MCAP, fl.cand_x + (size_t)row * F_MCAP, rec.n_cand,
-               rec.m, rec.t, (float)s2, a.top_k ? a.top_k[row] : 0u, a.top_p ? a.top_p[row] : 1.0f,
-               a.uniform ? a.uniform[row] : 0.0f, rec.amax, rec.status);
+    // a small grid walks the rows: usually none of them has a long list, and the pass must then cost next to nothing
+    for (uint32_t row = blockIdx.x; row < a.rows; row += gridDim.x) {
+        if (fl.recs[row].kind != 1u || fl.recs[row].n_cand <= (uint32_t)FS_NT) continue;   // small rows: finish_small_kernel
+        const RowRec& rec = fl.recs[row];
+        if (threadIdx.x < 32) {   // the partial folds of the row, added up by one warp
+            double s2 = 0.0;
+            for (uint32_t r = threadIdx.x; r < rec.n_parts; r += 32) s2 += rec.part[r];
+            for (int o = 16; o; o >>= 1) s2 += __shfl_xor_sync(FULL, s2, o);
+            if (threadIdx.x == 0) sm.bcast_f = (float)s2;
+        }
+        __syncthreads();
+        const float S = sm.bcast_f;   // finish_row opens with a barrier before anything reuses the slot
+        finish_row(sm, a, row, a.vocab, fl.cand_id + (size_t)row * F_MCAP, fl.cand_x + (size_t)row * F_MCAP, rec.n_cand,
+                   rec.m, rec.t, S, a.top_k ? a.top_k[row] : 0u, a.top_p ? a.top_p[row] : 1.0f,
+                   a.uniform ? a.uniform[row] : 0.0f, rec.amax, rec.status);
+        __syncthreads();
+    }
 }
 
 // ---- small rows: at most 128 candidates (top-k 50 leaves about 60).  Four warps per row are enough,
@@ -145,7 +156,7 @@ cudaError_t configure_finish() {
 }
 
 cudaError_t launch_finish(const RowArgs& a, const FusedLaunch& fl, cudaStream_t stream) {
-    finish_kernel<<<a.rows, NT, sizeof(FinishSmem), stream>>>(a, fl);
+    finish_kernel<<<a.rows < 128u ? a.rows : 128u, NT, sizeof(FinishSmem), stream>>>(a, fl);
     return cudaGetLastError();
 }
 

@@ -6,6 +6,7 @@
 #pragma once
 
 #include <cuda_runtime.h>
+#include <cstddef>
 
 #include "pgs_args.cuh"
 #include "pgs_block.cuh"
@@ -28,11 +29,11 @@ struct FinishSmem {
     int bcast_i;
 };
 
-// Exact left fold of n <= 128 shared-memory floats, called by one warp: returns the total and leaves every
+// Exact left fold of n shared-memory floats, called by one warp: returns the total and leaves every
 // running value in pre[0..n).  One lane does the additions: the loads do not depend on the running value, so
 // they are requested eight at a time (two 128-bit loads) and the dependent chain is the additions alone
-// (warp shuffles would put tens of cycles between two of them).  v and pre: 16-byte aligned arrays of at
-// least 128 floats (entries past n are read and written, not used).
+// (warp shuffles would put tens of cycles between two of them).  v and pre: 16-byte aligned arrays whose
+// length is a multiple of 8 and at least n (entries past n are read and written, not used).
 __device__ __forceinline__ float warp_prefix(const float* v, int n, float* pre) {
     const int lane = threadIdx.x & 31;
     float acc = 0.0f;
@@ -85,21 +86,56 @@ __device__ __forceinline__ void finish_row(FinishSmem& sm, const RowArgs& a, uin
     }
     __syncthreads();
     // rank every candidate by id and by (probability descending, id ascending)
-    for (uint32_t j = tid; j < n; j += NT) {
-        const uint32_t idj = sm.m_id[j];
-        const float pj = sm.p[j];
-        uint32_t r_id = 0, r_p = 0;
+    if (n <= 256u) {
+        for (uint32_t j = tid; j < n; j += NT) {
+            const uint32_t idj = sm.m_id[j];
+            const float pj = sm.p[j];
+            uint32_t r_id = 0, r_p = 0;
 #pragma unroll 8
-        for (uint32_t o = 0; o < n; o++) {   // broadcast loads, independent of one another: requested in batches
-            const uint32_t ido = sm.m_id[o];
-            const float po = sm.p[o];
-            r_id += ido < idj;
-            r_p += (po > pj) || (po == pj && ido < idj);
+            for (uint32_t o = 0; o < n; o++) {   // broadcast loads, independent of one another: requested in batches
+                const uint32_t ido = sm.m_id[o];
+                const float po = sm.p[o];
+                r_id += ido < idj;
+                r_p += (po > pj) || (po == pj && ido < idj);
+            }
+            sm.sid[r_id] = idj;
+            sm.sp[r_id] = pj;
+            sm.rp[r_p] = pj;
+            sm.rpos[r_p] = r_id;
         }
-        sm.sid[r_id] = idj;
-        sm.sp[r_id] = pj;
-        sm.rp[r_p] = pj;
-        sm.rpos[r_p] = r_id;
+    } else {
+        // long lists: two bitonic sorts of 64-bit keys in place of the quadratic counting.  m_id and p are
+        // adjacent and together hold F_MCAP keys.
+        static_assert(offsetof(FinishSmem, p) == offsetof(FinishSmem, m_id) + sizeof(uint32_t) * F_MCAP, "key space");
+        unsigned long long* keys = reinterpret_cast<unsigned long long*>(sm.m_id);
+        uint32_t npad = 512;
+        while (npad < n) npad <<= 1;
+        uint32_t idr[F_MCAP / NT];
+        float pr[F_MCAP / NT];
+#pragma unroll
+        for (int u = 0; u < F_MCAP / NT; u++) {
+            const uint32_t j = tid + u * NT;
+            idr[u] = j < n ? sm.m_id[j] : 0u;
+            pr[u] = j < n ? sm.p[j] : 0.0f;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int u = 0; u < F_MCAP / NT; u++) {   // by id ascending; the padding sorts to the end
+            const uint32_t j = tid + u * NT;
+            if (j < npad) keys[j] = j < n ? ((unsigned long long)idr[u] << 32) | f2u(pr[u]) : ~0ull;
+        }
+        bitonic_sort(keys, (int)npad, keys);
+        for (uint32_t j = tid; j < n; j += NT) { sm.sid[j] = (uint32_t)(keys[j] >> 32); sm.sp[j] = u2f((uint32_t)keys[j]); }
+        __syncthreads();
+        for (uint32_t j = tid; j < npad; j += NT)   // by (p, position descending) ascending = rank descending; padding first
+            keys[j] = j < n ? ((unsigned long long)f2u(sm.sp[j]) << 32) | (0xffffffffu - j) : 0ull;
+        bitonic_sort(keys, (int)npad, keys);
+        for (uint32_t r = tid; r < n; r += NT) {
+            const unsigned long long k = keys[npad - 1u - r];
+            sm.rp[r] = u2f((uint32_t)(k >> 32));
+            sm.rpos[r] = 0xffffffffu - (uint32_t)k;
+        }
+        __syncthreads();
     }
     if (tid == 0) sm.n_live = 0;
     __syncthreads();
@@ -118,17 +154,13 @@ __device__ __forceinline__ void finish_row(FinishSmem& sm, const RowArgs& a, uin
     uint32_t keep = n_live;
     if (use_p && n_live > 0) {
         int found = -1;
-        if (n_live <= 128) {
-            if (tid < 32) {
-                warp_prefix(sm.rp, (int)n_live, sm.p);   // sm.p is free once the candidates are ranked
-                found = warp_find(sm.p, (int)n_live, SEQ_FIND_GE, top_p);
-                if (tid == 0) sm.bcast_i = found;
-            }
-            __syncthreads();
-            found = sm.bcast_i;
-        } else {
-            seq_scan([&](int j) { return sm.rp[j]; }, (int)n_live, 0.0f, SEQ_FIND_GE, top_p, &found, sm.seq, sm.rs);
+        if (tid < 32) {   // one lane folds, at four cycles per term; the parallel emulation only pays beyond this size
+            warp_prefix(sm.rp, (int)n_live, sm.p);   // sm.p is free once the candidates are ranked
+            found = warp_find(sm.p, (int)n_live, SEQ_FIND_GE, top_p);
+            if (tid == 0) sm.bcast_i = found;
         }
+        __syncthreads();
+        found = sm.bcast_i;
         if (found >= 0) keep = (uint32_t)found + 1;
     }
     __syncthreads();
@@ -137,21 +169,15 @@ __device__ __forceinline__ void finish_row(FinishSmem& sm, const RowArgs& a, uin
     // total and inverse-CDF pick in id order
     float total;
     int pick = -1;
-    if (n <= 128) {
-        if (tid < 32) {
-            const float tt = warp_prefix(sm.sp, (int)n, sm.p);
-            int f = -1;
-            if (tt > 1e-9f) f = warp_find(sm.p, (int)n, SEQ_FIND_GT, fmul(u01, tt));
-            if (tid == 0) { sm.bcast_f = tt; sm.bcast_i = f; }
-        }
-        __syncthreads();
-        total = sm.bcast_f;
-        pick = sm.bcast_i;
-    } else {
-        total = seq_scan([&](int j) { return sm.sp[j]; }, (int)n, 0.0f, SEQ_SUM, 0.0f, nullptr, sm.seq, sm.rs);
-        if (total > 1e-9f)
-            seq_scan([&](int j) { return sm.sp[j]; }, (int)n, 0.0f, SEQ_FIND_GT, fmul(u01, total), &pick, sm.seq, sm.rs);
+    if (tid < 32) {
+        const float tt = warp_prefix(sm.sp, (int)n, sm.p);
+        int f = -1;
+        if (tt > 1e-9f) f = warp_find(sm.p, (int)n, SEQ_FIND_GT, fmul(u01, tt));
+        if (tid == 0) { sm.bcast_f = tt; sm.bcast_i = f; }
     }
+    __syncthreads();
+    total = sm.bcast_f;
+    pick = sm.bcast_i;
     if (tid == 0) {
         uint32_t token = amax;
         int drew = 0;
