@@ -156,7 +156,11 @@ def main():
     ap.add_argument("--impl", default="native", choices=["native", "reference"])
     ap.add_argument("--e2e-steps", type=int, default=10)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--phases", action="store_true",
+                    help="print the fused kernel's in-kernel phase timers (cycles per row) for a few steps and exit")
     args = ap.parse_args()
+    if args.phases:
+        os.environ["PGS_PROFILE"] = "1"   # read when the sampler is created
 
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -213,6 +217,21 @@ def main():
     step(0)
     torch.cuda.synchronize()
     assert (status.cpu().numpy() == 0).all(), "rows failed"
+    if args.phases:
+        sampler.read_phase_timers()       # clear what the warm-up left
+        n = 6
+        for i in range(n):
+            step(i)
+        t = sampler.read_phase_timers()
+        act = t[t.sum(1) > 0]
+        names = {12: "row barrier", 11: "parameters, copy issue, history table", 0: "slice check", 14: "  of which waiting for the copy",
+                 1: "penalties", 2: "argmax", 3: "exchange 1", 13: "exchange 1 read", 15: "warp maxima ranked", 4: "bound -> cut",
+                 5: "candidates + exponent pass", 6: "scan", 7: "exchange 2", 8: "fold", 9: "exchange 3 + refinement"}
+        per_step = act.mean(0) / n
+        print(f"{len(act)} CTAs active, {ROWS} rows per step; cycles per step and CTA (thread 0), mean over CTAs:", file=sys.stderr)
+        for slot, name in names.items():
+            print(f"  {name:42s} {per_step[slot]:9.0f}", file=sys.stderr)
+        return
     if rank == 0:
         from oracle import oracle
         chk = 4

@@ -260,6 +260,14 @@ typedef struct pgs_counters {
 } pgs_counters;
 PGS_API int pgs_get_counters(const pgs_handle *h, pgs_counters *out);
 
+/* Phase timers of the fused kernel, a diagnostic: only handles created with PGS_PROFILE=1 in the environment
+ * keep them.  out[cta * 16 + slot] receives the cycles thread 0 of CTA `cta` spent in each phase since the last
+ * read (summed over its rows), then the timers are cleared.  Slots: 12 row barrier, 11 parameters + copy issue +
+ * history table, 0 slice check (14: of which waiting for the copy), 1 penalties, 2 argmax, 3 exchange #1,
+ * 13 + 15 + 4 top-k bound, 5 candidates + exponent pass, 6 scan, 7 exchange #2, 8 fold, 9 exchange #3 + refinement.
+ * n_ctas <= 1024.  Synchronises the handle's stream. */
+PGS_API int pgs_debug_read_profile(pgs_handle *h, long long *out, uint32_t n_ctas);
+
 /* The handle's stream as a cudaStream_t, for callers that time or order work on it. */
 PGS_API void *pgs_stream(pgs_handle *h);
 

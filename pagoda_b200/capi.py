@@ -25,7 +25,7 @@ EXPORTS = ["pgs_create", "pgs_destroy", "pgs_last_error", "pgs_mask_table_upload
            "pgs_grammar_build_table", "pgs_grammar_state_new", "pgs_grammar_state_reset", "pgs_grammar_state_free",
            "pgs_grammar_advance", "pgs_grammar_mask_state", "pgs_grammar_state_info",
            "pgs_log_softmax", "pgs_tp_record_bytes", "pgs_tp_partial", "pgs_tp_merge", "pgs_tp_partial_push",
-           "pgs_tp_merge_wait", "pgs_peer_alloc", "pgs_peer_open", "pgs_peer_close", "pgs_peer_free", "pgs_draft_accept"]
+           "pgs_tp_merge_wait", "pgs_debug_read_profile", "pgs_peer_alloc", "pgs_peer_open", "pgs_peer_close", "pgs_peer_free", "pgs_draft_accept"]
 
 
 class SamplerError(RuntimeError):
@@ -119,6 +119,7 @@ def load_library():
     L.pgs_tp_merge.argtypes = [C.c_void_p, C.POINTER(TpDesc), C.c_void_p, C.POINTER(TpOut), C.c_void_p]
     L.pgs_tp_partial_push.argtypes = [C.c_void_p, C.POINTER(TpDesc), C.POINTER(C.c_void_p), C.POINTER(C.c_void_p),
                                       C.c_uint32, C.c_void_p]
+    L.pgs_debug_read_profile.argtypes = [C.c_void_p, C.c_void_p, C.c_uint32]
     L.pgs_peer_alloc.argtypes = [C.c_void_p, C.c_size_t, C.POINTER(C.c_void_p), C.c_char_p]
     L.pgs_peer_open.argtypes = [C.c_void_p, C.c_char_p, C.POINTER(C.c_void_p)]
     L.pgs_peer_close.argtypes = [C.c_void_p, C.c_void_p]
@@ -289,6 +290,13 @@ class Sampler:
         c = Counters()
         self._check(self._lib.pgs_get_counters(self._h, C.byref(c)))
         return {k: getattr(c, k) for k, _ in Counters._fields_}
+
+    def read_phase_timers(self, n_ctas: int = 1024):
+        """Cycles per CTA and phase of the fused kernel since the last read ([n_ctas, 16] int64; needs
+        PGS_PROFILE=1 in the environment when the sampler is created)."""
+        out = np.zeros((n_ctas, 16), dtype=np.int64)
+        self._check(self._lib.pgs_debug_read_profile(self._h, out.ctypes.data_as(C.c_void_p), C.c_uint32(n_ctas)))
+        return out
 
     def upload_mask_table(self, words, state_flags=None) -> int:
         words = np.ascontiguousarray(words, dtype=np.uint32)
