@@ -48,11 +48,12 @@ __global__ void __launch_bounds__(NT, 1) general_row_kernel(const RowArgs a) {
     const int tid = threadIdx.x;
     const uint32_t V = a.vocab;
     const uint32_t slot = blockIdx.x;
+    const uint32_t n_work = a.work_rows ? *a.work_count : a.rows;
+    if (n_work == 0u) return;   // the usual case of the work-list pass: nothing listed, nothing to reset
     if (tid < 32) sm.exp_tab[tid] = kExp2TableDev[tid];
     __syncthreads();
     const unsigned long long* tab = sm.exp_tab;
 
-    const uint32_t n_work = a.work_rows ? *a.work_count : a.rows;
     for (uint32_t w = blockIdx.x; w < n_work; w += gridDim.x) {
         const uint32_t row = a.work_rows ? a.work_rows[w] : w;
         __syncthreads();
