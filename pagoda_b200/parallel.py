@@ -56,11 +56,25 @@ class PeerExchange:
         everyone = [None] * self.world
         dist.all_gather_object(everyone, handle, group=group)
         self.peer_base = [self.base if r == self.rank else sampler.peer_open(everyone[r]) for r in range(self.world)]
-        import torch
-        self.buf = torch.as_tensor(_DeviceView(self.base, (2, self.world, rows, record_bytes), "|u1"), device=device)
-        self.flags = torch.as_tensor(_DeviceView(self.base + self.flag_off, (2, self.world), "<i4"), device=device)
+        self.device = device
+        self._buf = self._flags = None
         self.epoch = 0
         dist.barrier(group=group)   # every rank has mapped every buffer before anyone stores
+
+    @property
+    def buf(self):
+        """This rank's gather buffers as a uint8 tensor [2, world, rows, record_bytes] (a view, made on first use)."""
+        if self._buf is None:
+            self._buf = torch.as_tensor(_DeviceView(self.base, (2, self.world, self.rows, self.record_bytes), "|u1"),
+                                        device=self.device)
+        return self._buf
+
+    @property
+    def flags(self):
+        """This rank's flag arrays as an int32 tensor [2, world]."""
+        if self._flags is None:
+            self._flags = torch.as_tensor(_DeviceView(self.base + self.flag_off, (2, self.world), "<i4"), device=self.device)
+        return self._flags
 
     def next_step(self):
         """-> (epoch, parity, gather-buffer addresses per rank, flag-array addresses per rank) of the next step."""
@@ -71,9 +85,9 @@ class PeerExchange:
 
     def close(self, group=None):
         """Unmap the peers' buffers, then (after everyone has) free this rank's."""
-        import torch
-        torch.cuda.synchronize()
-        self.buf = self.flags = None
+        if torch.cuda.is_available():
+            torch.cuda.synchronize()
+        self._buf = self._flags = None
         for r, b in enumerate(self.peer_base):
             if r != self.rank:
                 self.sampler.peer_close(b)

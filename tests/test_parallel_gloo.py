@@ -28,6 +28,41 @@ def _worker(rank, world, port, q):
     for r in range(world):
         ok = ok and bool((allrec[r, :, 1:] == r + 1).all()) and bool((allrec[r, :, 0] == torch.arange(rows, dtype=torch.uint8)).all())
     slow = max_over_ranks(1.0 + rank, torch.device("cpu"))
+
+    # the peer-store exchange's bookkeeping, with a stand-in for the sampler library: every rank ends up with
+    # every rank's buffer address, and the addresses of a step follow its parity
+    from pagoda_b200.parallel import PeerExchange
+
+    class FakeSampler:
+        opened, closed, freed = [], [], []
+
+        def peer_alloc(self, nbytes):
+            self.nbytes = nbytes
+            return 0x10000000 * (rank + 1), (rank + 1).to_bytes(8, "little") + bytes(56)
+
+        def peer_open(self, handle):
+            r = int.from_bytes(handle[:8], "little")
+            self.opened.append(r)
+            return 0x10000000 * r + 0x1000000          # a peer's buffer appears at some other local address
+
+        def peer_close(self, addr):
+            self.closed.append(addr)
+
+        def peer_free(self, addr):
+            self.freed.append(addr)
+
+    fs = FakeSampler()
+    px = PeerExchange(fs, rows, rec, torch.device("cpu"))
+    steps = [px.next_step() for _ in range(3)]
+    want_base = [0x10000000 * (r + 1) + (0 if r == rank else 0x1000000) for r in range(world)]
+    one = world * rows * rec
+    ok = ok and fs.nbytes >= 2 * one + 2 * world * 4 and fs.opened == [r + 1 for r in range(world) if r != rank]
+    for epoch, par, recs, flags in steps:
+        ok = ok and par == (epoch & 1) and recs == [b + par * one for b in want_base]
+        ok = ok and flags == [b + px.flag_off + par * world * 4 for b in want_base]
+    ok = ok and [s_[0] for s_ in steps] == [1, 2, 3]
+    px.close()
+    ok = ok and len(fs.closed) == world - 1 and fs.freed == [want_base[rank]]
     q.put((rank, lo, hi, clo, chi, ok, slow))
     dist.barrier()
     dist.destroy_process_group()
