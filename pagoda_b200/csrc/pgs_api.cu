@@ -23,6 +23,7 @@ size_t general_smem_bytes();
 
 size_t fused_smem_bytes(uint32_t slice_len, uint32_t cluster);
 uint32_t fused_threads();
+uint32_t fused_piece_bytes();
 cudaError_t fused_ctas_per_sm(size_t smem, int* out);
 cudaError_t configure_fused(size_t max_smem);
 cudaError_t fused_max_clusters(uint32_t cluster, size_t smem, int* out);
@@ -319,7 +320,7 @@ bool fused_shape(pgs_handle* h, uint32_t vocab, uint32_t rows) {
     for (uint32_t c = 1; c <= (uint32_t)pgs::F_MAXC; c++) {
         const uint32_t slice = (((vocab + c - 1) / c) + 31u) & ~31u;
         const size_t smem = pgs::fused_smem_bytes(slice, c);
-        if (smem > h->smem_optin || (slice * 4u + 32767u) / 32768u > 8u) continue;
+        if (smem > h->smem_optin || (slice * 4u + pgs::fused_piece_bytes() - 1u) / pgs::fused_piece_bytes() > 8u) continue;
         int n = 0;
         if (pgs::fused_max_clusters(c, smem, &n) != cudaSuccess || n <= 0) { cudaGetLastError(); continue; }
         const uint32_t waves = (rows + (uint32_t)n - 1) / (uint32_t)n;
