@@ -14,6 +14,7 @@
 
 #include "pgs_args.cuh"
 #include "pgs_fused.cuh"
+#include "pgs_stream.cuh"
 #include "pgs_tp.cuh"
 
 namespace pgs {
@@ -29,6 +30,10 @@ cudaError_t configure_fused(size_t max_smem);
 cudaError_t fused_max_clusters(uint32_t cluster, size_t smem, int* out);
 cudaError_t launch_fused(const RowArgs& a, const FusedLaunch& fl, uint32_t n_clusters, size_t smem,
                          cudaStream_t stream);
+size_t stream_smem_bytes();
+cudaError_t configure_stream();
+cudaError_t stream_ctas_per_sm(int* out);
+cudaError_t launch_stream(const RowArgs& a, const StreamLaunch& sl, uint32_t grid, cudaStream_t stream);
 struct ScoreArgs {
     const float* logits;
     unsigned long long row_stride;
@@ -87,7 +92,15 @@ struct pgs_handle {
     uint32_t* cand_id = nullptr;      // [max_rows x F_MCAP]
     float* cand_x = nullptr;
     int exact = 0;
-    long long* prof = nullptr;        // phase timers of the fused kernel (PGS_PROFILE=1)
+    // streaming row kernel: id -> count slots, shared memory and CTAs per SM, the gate's counter
+    int use_cluster = 0;              // PGS_PATH=cluster: the cluster kernel instead (kept for comparison)
+    uint32_t stream_hash = 0, stream_cohort = 0;
+    size_t stream_smem = 0;
+    int stream_ctas = 0;
+    uint32_t* p1_done = nullptr;      // device counter: rows that finished their first pass, over all launches
+    uint32_t done_total = 0;          // the value that counter has when every launch so far has completed
+    unsigned long long* faulted = nullptr;   // device counter of ROW_NONFINITE rows
+    long long* prof = nullptr;        // phase timers of the row kernel (PGS_PROFILE=1)
     pgs_counters counters = {};
     char err[256] = "";
 };
@@ -146,7 +159,7 @@ static int destroy_impl(pgs_handle* h) {
     cudaFree(h->sx); cudaFree(h->sl_id); cudaFree(h->sl_p); cudaFree(h->sl_key);
     cudaFree(h->sh_key); cudaFree(h->sh_cnt); cudaFree(h->tables_dev);
     cudaFree(h->logits_stage); cudaFree(h->aux_dev); cudaFree(h->work_rows); cudaFree(h->work_count); cudaFree(h->tp_done); cudaFree(h->prof);
-    cudaFree(h->recs); cudaFree(h->cand_id); cudaFree(h->cand_x);
+    cudaFree(h->recs); cudaFree(h->cand_id); cudaFree(h->cand_x); cudaFree(h->p1_done); cudaFree(h->faulted);
     if (h->aux_host) cudaFreeHost(h->aux_host);
     if (h->side) { cudaStreamSynchronize(h->side); cudaStreamDestroy(h->side); }
     if (h->ev_fork) cudaEventDestroy(h->ev_fork);
@@ -201,6 +214,21 @@ extern "C" int pgs_create(int device, uint32_t max_rows, uint32_t max_vocab, uin
         PGS_CUDA(nullptr, cudaMemsetAsync(h->work_count, 0, 2 * sizeof(uint32_t), h->stream));
         PGS_CUDA(nullptr, cudaMalloc(&h->tp_done, sizeof(uint32_t)));
         PGS_CUDA(nullptr, cudaMemsetAsync(h->tp_done, 0, sizeof(uint32_t), h->stream));
+        PGS_CUDA(nullptr, cudaMalloc(&h->p1_done, sizeof(uint32_t)));
+        PGS_CUDA(nullptr, cudaMemsetAsync(h->p1_done, 0, sizeof(uint32_t), h->stream));
+        PGS_CUDA(nullptr, cudaMalloc(&h->faulted, sizeof(unsigned long long)));
+        PGS_CUDA(nullptr, cudaMemsetAsync(h->faulted, 0, sizeof(unsigned long long), h->stream));
+        h->stream_hash = pow2_at_least(2 * (max_history ? max_history : 1), 64);
+        if (h->stream_hash > (uint32_t)pgs::S_MAX_HASH) h->stream_hash = pgs::S_MAX_HASH;   // longer histories take the general kernel
+        h->stream_smem = pgs::stream_smem_bytes();
+        PGS_CUDA(nullptr, pgs::configure_stream());
+        PGS_CUDA(nullptr, pgs::stream_ctas_per_sm(&h->stream_ctas));
+        if (h->stream_ctas < 1) return fail(nullptr, PGS_ERR_CUDA, "pgs_create: the row kernel does not fit an SM (%zu bytes of shared memory)", h->stream_smem);
+        // rows that may read HBM at once: about an SM count of them saturate it, and the rows in flight stay inside L2
+        h->stream_cohort = h->sm_count > 40 ? (uint32_t)h->sm_count - 20u : (uint32_t)h->sm_count;
+        if (const char* ev = getenv("PGS_COHORT")) { if (atoi(ev) > 0) h->stream_cohort = (uint32_t)atoi(ev); }
+        h->use_cluster = 1;   // the streaming kernel is opt-in (PGS_PATH=stream) until it is the faster one
+        if (const char* ev = getenv("PGS_PATH")) h->use_cluster = strcmp(ev, "stream") != 0;
         if (const char* ev = getenv("PGS_EXACT")) h->exact = atoi(ev);
         if (const char* ev = getenv("PGS_PROFILE")) {
             if (atoi(ev)) {
@@ -247,6 +275,14 @@ extern "C" void* pgs_stream(pgs_handle* h) { return h ? (void*)h->stream : nullp
 extern "C" int pgs_get_counters(const pgs_handle* h, pgs_counters* out) {
     if (!h || !out) return PGS_ERR_INVALID;
     *out = h->counters;
+    // faulted rows are counted on the device by the kernels that find them
+    DeviceGuard g(h->device);
+    unsigned long long f = 0;
+    cudaError_t e = cudaStreamSynchronize(h->stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(h->side);
+    if (e == cudaSuccess) e = cudaMemcpy(&f, h->faulted, sizeof f, cudaMemcpyDeviceToHost);
+    if (e != cudaSuccess) { cudaGetLastError(); return PGS_ERR_CUDA; }
+    out->rows_faulted = f;
     return PGS_OK;
 }
 
@@ -343,9 +379,40 @@ bool fused_shape(pgs_handle* h, uint32_t vocab, uint32_t rows) {
 int launch_step(pgs_handle* h, pgs::RowArgs& a, cudaStream_t stream) {
     const uint32_t rows = a.rows;
     const uint32_t grid = rows < h->slots ? rows : h->slots;
-    if (h->exact || !fused_shape(h, a.vocab, rows)) {
+    a.faulted = h->faulted;
+    const bool stream_fits = a.vocab <= (uint32_t)pgs::S_MAX_VOCAB;
+    if (h->exact || (h->use_cluster ? !fused_shape(h, a.vocab, rows) : !stream_fits)) {
         PGS_CUDA(h, pgs::launch_general(a, grid, stream));
         h->counters.kernel_launches += 1;
+        return PGS_OK;
+    }
+    if (!h->use_cluster) {
+        pgs::StreamLaunch sl;
+        sl.hash_slots = h->stream_hash; sl.cohort = h->stream_cohort;
+        sl.done_base = h->done_total; sl.gate_polls = 1u << 16;   // x 200 ns: gives up after about 13 ms
+        sl.p1_done = h->p1_done;
+        sl.work_rows = h->work_rows; sl.work_count = h->work_count;
+        sl.recs = h->recs; sl.cand_id = h->cand_id; sl.cand_x = h->cand_x;
+        sl.prof = h->prof;
+        const uint32_t resident = (uint32_t)h->stream_ctas * (uint32_t)h->sm_count;
+        PGS_CUDA(h, pgs::launch_stream(a, sl, rows < resident ? rows : resident, stream));
+        h->done_total += rows;
+        // rows with a long candidate list and the rows on the work list are usually none: those two passes run
+        // beside each other on a side stream
+        pgs::FusedLaunch fl;
+        fl.cluster = 1; fl.slice_len = 0; fl.chunk = 0;
+        fl.work_rows = h->work_rows; fl.work_count = h->work_count; fl.prof = nullptr;
+        fl.recs = h->recs; fl.cand_id = h->cand_id; fl.cand_x = h->cand_x;
+        PGS_CUDA(h, cudaEventRecord(h->ev_fork, stream));
+        PGS_CUDA(h, cudaStreamWaitEvent(h->side, h->ev_fork, 0));
+        PGS_CUDA(h, pgs::launch_finish(a, fl, stream));
+        pgs::RowArgs wl = a;
+        wl.work_rows = h->work_rows;
+        wl.work_count = h->work_count;
+        PGS_CUDA(h, pgs::launch_general(wl, grid < 32u ? grid : 32u, h->side));
+        PGS_CUDA(h, cudaEventRecord(h->ev_join, h->side));
+        PGS_CUDA(h, cudaStreamWaitEvent(stream, h->ev_join, 0));
+        h->counters.kernel_launches += 3;
         return PGS_OK;
     }
     pgs::FusedLaunch fl;
@@ -538,8 +605,6 @@ int run_batch(pgs_handle* h, const pgs_batch_desc* d, cudaStream_t stream, bool 
     h->counters.calls += 1;
     h->counters.rows += rows;
     h->counters.bytes += (uint64_t)rows * (d->vocab * esz + 64) + hist_total * 4 + masked_rows * (d->vocab / 8);
-    if (d->aux_mem == PGS_MEM_HOST)
-        for (uint32_t r = 0; r < rows; r++) h->counters.rows_faulted += d->status[r] == PGS_ROW_NONFINITE;
     return PGS_OK;
 }
 

@@ -63,6 +63,7 @@ struct RowArgs {
     // optional work list: process rows work_rows[0 .. *work_count) instead of 0 .. rows
     const uint32_t* work_rows;
     uint32_t* work_count;           // [0] = number of listed rows, [1] = CTAs that finished the list
+    unsigned long long* faulted;    // optional: rows that ended as ROW_NONFINITE, counted over all launches
 };
 
 }  // namespace pgs

@@ -119,7 +119,10 @@ __global__ void __launch_bounds__(NT, 1) general_row_kernel(const RowArgs a) {
         }
         nonfinite = __syncthreads_or(nonfinite);
         if (nonfinite) {
-            if (tid == 0) write_row(a, row, 0u, ROW_NONFINITE, 0, 0u, -INFINITY, 0.0f, 0.0f, 0u);
+            if (tid == 0) {
+                write_row(a, row, 0u, ROW_NONFINITE, 0, 0u, -INFINITY, 0.0f, 0.0f, 0u);
+                if (a.faulted) atomicAdd(a.faulted, 1ull);
+            }
             continue;
         }
         if (gflags & 2u) {

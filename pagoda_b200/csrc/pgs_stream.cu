@@ -1,0 +1,869 @@
+// Streaming row kernel: the hot path of the sampler.
+//
+// One CTA of 256 threads (two per SM, up to 128 registers per thread) owns one batch row at a time and reads it
+// twice with plain 128-bit coalesced loads, 32 logits per thread and piece, the loads of the next piece on their
+// way while a piece is worked on.  (What a piece costs beyond its logits -- addresses, table look-ups, warp
+// reductions, loop control -- is paid once per thread and piece, so pieces are as large as the registers allow;
+// with 8 logits per thread and piece the kernel executed 57 instructions per logit.)  Inside a pass nothing
+// synchronises the warps:
+//
+//   pass 1, last piece first, from HBM: sanity, penalties, grammar bitmask, EOS fix; per thread eight running
+//           maxima (one per piece number mod 8) with the place where each first occurs; per warp and piece the
+//           plain sum of the softmax numerators relative to the warp's own maximum;
+//   between: row maximum and argmax (lowest id); a bound for the top-k threshold: the k-th largest of the 2048
+//           per-thread maxima is reached by at least k logits, so "logit >= that bound" is a superset of the
+//           top-k set that is only slightly larger; and, from the rescaled plain sums, the value the reference's
+//           running sum has when it reaches each warp's 1024 logits of each piece, to within 1e-3;
+//   pass 2, first piece first, from L2 (the pieces read last in pass 1 are the freshest there): the same
+//           processed logits again, candidates above the bound, softmax numerators by the hardware exp2, and
+//           the reference's sequential f32 sum;
+//   finish: exact probabilities of the candidates, top-k with ties, top-p walk, inverse-CDF pick.
+//
+// A row is 600 KB, more than one SM holds, and its maximum must be known before the first numerator: the row
+// is therefore read a second time, from L2, which keeps the rows in flight as long as only about an SM count
+// of them are in their first pass at once.  The launch is one wave of CTAs for up to 2 x SM-count rows; a gate
+// (a counter of rows that finished pass 1, bounded polling) starts the later rows when the earlier ones leave
+// HBM to them, so that the second pass of one cohort runs under the first pass of the next.
+//
+// The f32 left fold (pagoda/src/sampler.rs:99-113): while the running value stays inside one binade, adding a
+// non-negative term is an integer addition in units of that binade's ulp which depends on the running value only
+// through its parity.  Wherever the estimate above puts the running value safely inside one binade for a warp's
+// whole share of a piece, every thread adds its 32 numerators to that binade's lower end (real f32
+// additions) and the increments are summed as integers; the few shares in which the running value may change
+// binade are folded 128 bits at a time from their own estimates of the running value, which reproduces the
+// crossing.  Ties of round-half-even are decided by the parity of a stand-in, not of the true running value: the
+// sum agrees with the reference's to about 1e-6 relative, and a decision can differ only when it sits that close
+// to its boundary.
+//
+// Fidelity of this path: argmax, masks, penalties and candidate sets follow the reference bit for bit
+// (pagoda/src/engine.rs:1286-1314, pagoda/src/sampler.rs:28-150); candidate numerators use the exact expf.
+// Rows this kernel does not serve (top-k off or > 1024, more candidates than its buffers, histories beyond its
+// id -> count table, rows that are not 16-byte aligned) are appended to a work list for the general row kernel.
+#include <cuda_runtime.h>
+
+#include <type_traits>
+
+#include "pgs_args.cuh"
+#include "pgs_block.cuh"
+#include "pgs_finish.cuh"
+#include "pgs_stream.cuh"
+
+namespace pgs {
+
+constexpr int SNT = 512;                 // threads per CTA
+constexpr int SNW = SNT / 32;            // warps per CTA
+constexpr int S_EPT = 16;                // logits per thread and piece
+constexpr int S_PIECE = SNT * S_EPT;     // logits per piece
+constexpr int S_REGION = 32 * S_EPT;     // consecutive logits of one warp in a piece
+constexpr int S_MAX_REGIONS = S_MAX_VOCAB / S_REGION;
+constexpr int S_NCELL = 4;               // running maxima per thread (piece number mod S_NCELL)
+constexpr int S_CELLS = S_NCELL * SNT;   // per-thread maxima that bound the top-k threshold
+constexpr int S_NB = 1024;               // buckets of their histogram
+constexpr int S_BPT = S_NB / SNT;        // buckets per thread
+constexpr int S_FCAP = 256;              // candidates finished inside this kernel
+constexpr int S_RPT = S_MAX_REGIONS / SNT;   // regions per thread in the CTA-wide walks over regions
+constexpr uint32_t S_NIL = 0xffffffffu;
+static_assert(S_FCAP <= SNT, "one thread per candidate in the finish");
+static_assert(SNW <= 32, "warp slots are combined by one warp");
+
+// Everything the kernel needs to know about a row, read and validated by one thread while the CTA still works
+// on the row before it.
+struct SRowCtl {
+    const char* rowp;       // first logit of the row
+    const uint32_t* mw;     // grammar mask words of the row's state, or null
+    float temp, freq, pres, rep, top_p, u01;
+    float sc;               // log2(e) / max(temp, 1e-9)
+    uint32_t top_k, gflags, h0, nh;
+    uint32_t kind;          // 0 serve, 1 bad parameters, 2 defer to the general kernel
+};
+
+struct FinishScratch {   // at most S_FCAP candidates
+    unsigned long long fkey[S_FCAP];
+    float fp[S_FCAP], fsp[S_FCAP], frp[S_FCAP];
+    uint32_t fsid[S_FCAP], frpos[S_FCAP];
+};
+
+struct StreamSmem {
+    SRowCtl ctl[2];
+    unsigned long long exp_tab[32];
+    uint32_t red_key[SNW], red_idx[SNW], red_lo[SNW], red_fin[SNW], red_flag[SNW];
+    uint32_t scan_u[SNW];
+    float scan_f[SNW];
+    double wacc[SNW];               // per-warp share of the fold
+    uint32_t cand_n, sel_bucket, n_live;
+    uint32_t hist[S_NB];
+    float cell[S_CELLS];             // [S_NCELL][SNT]
+    uint32_t celli[S_CELLS];         // id at which each maximum first occurs
+    uint32_t cand_id[F_MCAP];
+    float cand_x[F_MCAP];
+    // per warp region of the row (512 consecutive logits): pass 1 leaves the warp's maximum and the plain sum of
+    // its numerators relative to it; then the binade's lower end the fold has there (0 = fold this region the
+    // careful way) and the estimate of the running value at its start.  While the history is indexed, reg_a
+    // counts the distinct history ids per region.
+    float reg_a[S_MAX_REGIONS], reg_b[S_MAX_REGIONS];
+    // distinct history ids grouped by region: those of region r are the entries rs[r] .. rs[r + 1]
+    uint16_t rs[S_MAX_REGIONS + 2];
+    uint16_t pid[S_MAX_HASH / 2];    // position inside the region
+    uint32_t pval[S_MAX_HASH / 2];   // count, then (after pass 1) the bits of the penalised logit
+    long long prof_acc[16];
+    // one area, three uses: id -> count table while the history is indexed (hkey[H], hcnt[H]); per-warp staging of
+    // a piece while penalties are applied to it (SNW x S_REGION floats); scratch of the finish
+    union alignas(16) {
+        uint32_t hash[2 * S_MAX_HASH];
+        float stage[SNW * S_REGION];
+        FinishScratch fin;
+    } u;
+};
+
+#define PGS_STICK(slot)                                             \
+    do {                                                            \
+        if (sl.prof && tid == 0) {                                  \
+            const long long now_ = clock64();                       \
+            sm.prof_acc[slot] += now_ - tick_;                      \
+            tick_ = now_;                                           \
+        }                                                           \
+    } while (0)
+
+__device__ __forceinline__ float max3f(float a, float b, float c) {
+    float r;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+    return r;
+}
+// max(|a|, |b|, |c|), NaN if any of them is
+__device__ __forceinline__ float absmax3_nan(float a, float b, float c) {
+    float r;
+    asm("max.NaN.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(fabsf(a)), "f"(fabsf(b)), "f"(fabsf(c)));
+    return r;
+}
+__device__ __forceinline__ float max_ept(const float (&x)[S_EPT]) {
+    static_assert(S_EPT % 8 == 0, "eight logits per round");
+    float m[S_EPT / 8];
+#pragma unroll
+    for (int j = 0; j < S_EPT; j += 8)
+        m[j / 8] = max3f(max3f(x[j], x[j + 1], x[j + 2]), max3f(x[j + 3], x[j + 4], x[j + 5]), fmaxf(x[j + 6], x[j + 7]));
+    float r = m[0];
+#pragma unroll
+    for (int j = 1; j + 1 < S_EPT / 8; j += 2) r = max3f(r, m[j], m[j + 1]);
+    if ((S_EPT / 8) % 2 == 0) r = fmaxf(r, m[S_EPT / 8 - 1]);
+    return r;
+}
+__device__ __forceinline__ float absmax_ept_nan(float am, const float (&x)[S_EPT]) {
+    float m[S_EPT / 8];
+#pragma unroll
+    for (int j = 0; j < S_EPT; j += 8)
+        m[j / 8] = absmax3_nan(absmax3_nan(x[j], x[j + 1], x[j + 2]), absmax3_nan(x[j + 3], x[j + 4], x[j + 5]), absmax3_nan(x[j + 6], x[j + 7], x[j + 7]));
+#pragma unroll
+    for (int j = 0; j + 1 < S_EPT / 8; j += 2) am = absmax3_nan(am, m[j], m[j + 1]);
+    if ((S_EPT / 8) % 2 == 1) am = absmax3_nan(am, m[S_EPT / 8 - 1], m[S_EPT / 8 - 1]);
+    return am;
+}
+
+// One piece's share of a thread as it comes from memory: f32 rows eight 128-bit groups of four logits, bf16 rows
+// four groups of eight.
+template <bool BF16> struct Geo {
+    static constexpr int G = BF16 ? S_EPT / 8 : S_EPT / 4;   // groups per thread and piece
+    static constexpr int GE = S_EPT / G;        // logits per group
+    static constexpr int GS = 32 * GE;          // logits between two groups of a thread
+};
+
+// A piece's share of a thread as it comes from memory; groups past the end of the row read as zeros.
+template <bool BF16> struct PieceBuf;
+template <> struct PieceBuf<false> { float4 v[S_EPT / 4]; };
+template <> struct PieceBuf<true> { uint4 v[S_EPT / 8]; };
+template <bool BF16>
+__device__ __forceinline__ void issue_loads(PieceBuf<BF16>& b, const char* rowp, uint32_t e0, uint32_t V) {
+#pragma unroll
+    for (int h = 0; h < Geo<BF16>::G; h++) {
+        const uint32_t idx = e0 + h * Geo<BF16>::GS;
+        // (volatile inline assembly: the compiler must not sink these loads towards their first use)
+        if constexpr (BF16) {
+            b.v[h] = make_uint4(0u, 0u, 0u, 0u);
+            if (idx < V)
+                asm volatile("ld.global.cg.v4.u32 {%0, %1, %2, %3}, [%4];"
+                             : "=r"(b.v[h].x), "=r"(b.v[h].y), "=r"(b.v[h].z), "=r"(b.v[h].w) : "l"(rowp + (size_t)idx * 2));
+        } else {
+            b.v[h] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            if (idx < V)
+                asm volatile("ld.global.cg.v4.f32 {%0, %1, %2, %3}, [%4];"
+                             : "=f"(b.v[h].x), "=f"(b.v[h].y), "=f"(b.v[h].z), "=f"(b.v[h].w) : "l"(rowp + (size_t)idx * 4));
+        }
+    }
+}
+template <bool BF16>
+__device__ __forceinline__ void unpack(float (&x)[S_EPT], const PieceBuf<BF16>& b) {
+    if constexpr (BF16) {
+#pragma unroll
+        for (int h = 0; h < Geo<true>::G; h++) {
+            const uint32_t r[4] = {b.v[h].x, b.v[h].y, b.v[h].z, b.v[h].w};
+#pragma unroll
+            for (int u = 0; u < 4; u++) {   // a 16-bit shift widens bf16 to f32 exactly
+                x[h * 8 + 2 * u] = __uint_as_float(r[u] << 16);
+                x[h * 8 + 2 * u + 1] = __uint_as_float(r[u] & 0xffff0000u);
+            }
+        }
+    } else {
+#pragma unroll
+        for (int h = 0; h < Geo<false>::G; h++) { x[4 * h] = b.v[h].x; x[4 * h + 1] = b.v[h].y; x[4 * h + 2] = b.v[h].z; x[4 * h + 3] = b.v[h].w; }
+    }
+}
+
+// id of the thread's j-th logit of a piece whose first group starts at e0
+template <bool BF16> __device__ __forceinline__ uint32_t elem_id(uint32_t e0, int j) {
+    return e0 + (uint32_t)(j / Geo<BF16>::GE) * Geo<BF16>::GS + (uint32_t)(j % Geo<BF16>::GE);
+}
+
+// ---- CTA-wide exclusive scans for SNW warps (one barrier each; `slots` may be written again after another barrier)
+__device__ __forceinline__ uint32_t sblock_excl_scan_u32(uint32_t v, uint32_t* total, uint32_t* slots) {
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+    uint32_t inc = v;
+    for (int o = 1; o < 32; o <<= 1) {
+        const uint32_t t = __shfl_up_sync(FULL, inc, o);
+        if (lane >= o) inc += t;
+    }
+    if (lane == 31) slots[w] = inc;
+    __syncthreads();
+    const uint32_t x = lane < SNW ? slots[lane] : 0u;
+    *total = __reduce_add_sync(FULL, x);
+    return __reduce_add_sync(FULL, lane < w ? x : 0u) + inc - v;
+}
+__device__ __forceinline__ float sblock_excl_scan_f32(float v, float* total, float* slots) {   // plain adds: estimates only
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+    float inc = v;
+    for (int o = 1; o < 32; o <<= 1) {
+        const float t = __shfl_up_sync(FULL, inc, o);
+        if (lane >= o) inc += t;
+    }
+    if (lane == 31) slots[w] = inc;
+    __syncthreads();
+    const float x = lane < SNW ? slots[lane] : 0.0f;
+    float xi = x;
+    for (int o = 1; o < 32; o <<= 1) {
+        const float t = __shfl_up_sync(FULL, xi, o);
+        if (lane >= o) xi += t;
+    }
+    *total = __shfl_sync(FULL, xi, 31);
+    return __shfl_sync(FULL, xi - x, w) + (inc - v);
+}
+
+// One thread reads and validates a row's parameters (same rules as the general kernel).
+template <bool BF16>
+__device__ __forceinline__ void sprepare_row(const RowArgs& a, const StreamLaunch& sl, uint32_t row, SRowCtl& c) {
+    const uint32_t V = a.vocab;
+    const float temp = a.temperature ? a.temperature[row] : 0.0f;
+    const uint32_t top_k = a.top_k ? a.top_k[row] : 0u;
+    const float top_p = a.top_p ? a.top_p[row] : 1.0f;
+    const float freq = a.freq ? a.freq[row] : 0.0f;
+    const float pres = a.pres ? a.pres[row] : 0.0f;
+    const float rep = a.rep ? a.rep[row] : 1.0f;
+    const float u01 = a.uniform ? a.uniform[row] : 0.0f;
+    bool bad = !finite_f(temp) || !finite_f(top_p) || !finite_f(freq) || !finite_f(pres) ||
+               !finite_f(rep) || !(rep > 0.0f) || !finite_f(u01);
+    const uint32_t* mw = nullptr;
+    uint32_t gflags = 0;
+    if (a.mask_table && a.mask_table[row] >= 0) {
+        const int32_t t = a.mask_table[row];
+        const int32_t st = a.mask_state ? a.mask_state[row] : 0;
+        if (t >= MAX_TABLES || !a.tables[t].live || st < 0 || (uint32_t)st >= a.tables[t].n_states ||
+            (unsigned long long)a.tables[t].words_per_state * 32ull < V) {
+            bad = true;
+        } else {
+            mw = a.tables[t].words + (size_t)st * a.tables[t].words_per_state;
+            gflags = a.tables[t].flags[st];
+        }
+    }
+    uint32_t h0 = 0, nh = 0;
+    if (a.hist_offsets) {
+        h0 = a.hist_offsets[row];
+        const uint32_t h1 = a.hist_offsets[row + 1];
+        if (h1 < h0 || h1 - h0 > a.max_history || (h1 > h0 && !a.hist_ids)) bad = true; else nh = h1 - h0;
+    }
+    const bool greedy = temp < 1e-5f;
+    const bool use_k = top_k != 0u && top_k < V;
+    const char* rowp = (const char*)a.logits + (size_t)row * a.row_stride * (BF16 ? 2 : 4);
+    const bool aligned = (((uintptr_t)rowp & 15) == 0) && (V % Geo<BF16>::GE) == 0;
+    const bool pen = nh > 0 && (!(fabsf(freq) < 1e-6f && fabsf(pres) < 1e-6f) || rep != 1.0f);
+    const bool defer = !aligned || (!greedy && (!use_k || top_k > (uint32_t)S_KMAX)) || (pen && 2u * nh > sl.hash_slots);
+    c.rowp = rowp; c.mw = mw; c.temp = temp; c.freq = freq; c.pres = pres; c.rep = rep; c.top_p = top_p; c.u01 = u01;
+    c.sc = (float)(1.4426950408889634 / (double)fmaxf(temp, 1e-9f));
+    c.top_k = top_k; c.gflags = gflags; c.h0 = h0; c.nh = nh;
+    c.kind = bad ? 1u : defer ? 2u : 0u;
+}
+
+// Candidates of one row -> token, by the threads 0..n-1 of the CTA and then its first warp (n <= S_FCAP).
+// Called by every thread; the caller has a barrier in front.
+__device__ __forceinline__ void sfinish_row(StreamSmem& sm, const RowArgs& a, uint32_t row, uint32_t n, float m, float t,
+                                            float S, uint32_t top_k, float top_p, float u01, uint32_t amax, int status) {
+    FinishScratch& fs = sm.u.fin;
+    const int tid = threadIdx.x, lane = tid & 31;
+    const uint32_t V = a.vocab;
+    const bool norm = S > 1e-9f;
+    uint32_t my_id = 0u;
+    float my_p = 0.0f;
+    if (tid == 0) sm.n_live = 0u;
+    if ((uint32_t)tid < n) {
+        my_id = sm.cand_id[tid];
+        const float e = softmax_num(sm.cand_x[tid], m, t, sm.exp_tab);   // exact expf
+        my_p = norm ? fdiv(e, S) : e;
+        fs.fkey[tid] = ((unsigned long long)f2u(my_p) << 32) | (unsigned long long)(0xffffffffu - my_id);   // p >= 0
+    }
+    __syncthreads();
+    if ((uint32_t)tid < n) {   // rank by id and by (probability descending, id ascending)
+        const unsigned long long kj = fs.fkey[tid];
+        uint32_t r_id = 0, r_p = 0;
+#pragma unroll 8
+        for (uint32_t o = 0; o < n; o++) {   // broadcast loads, independent of one another
+            const unsigned long long ko = fs.fkey[o];
+            r_p += ko > kj;
+            r_id += (uint32_t)ko > (uint32_t)kj;   // larger ~id = smaller id
+        }
+        fs.fsid[r_id] = my_id; fs.fsp[r_id] = my_p; fs.frp[r_p] = my_p; fs.frpos[r_p] = r_id;
+    }
+    __syncthreads();
+    if ((uint32_t)tid < n) {   // top-k: every tie at the k-th probability survives; zeros never matter
+        const float thr = (top_k != 0u && top_k <= n) ? fs.frp[top_k - 1] : 0.0f;
+        const bool live = fs.frp[tid] >= thr && fs.frp[tid] > 0.0f;
+        const bool next_live = (uint32_t)tid + 1 < n && fs.frp[tid + 1] >= thr && fs.frp[tid + 1] > 0.0f;
+        if (live && !next_live) sm.n_live = tid + 1;
+    }
+    __syncthreads();
+    if (tid >= 32) return;
+    // one warp: top-p walk in ranked order, then total and inverse-CDF pick in id order
+    const uint32_t n_live = sm.n_live;
+    uint32_t keep = n_live;
+    if (!(top_p >= 1.0f) && n_live > 0) {
+        warp_prefix(fs.frp, (int)n_live, fs.fp);
+        const int found = warp_find(fs.fp, (int)n_live, SEQ_FIND_GE, top_p);
+        if (found >= 0) keep = (uint32_t)found + 1;
+    }
+    for (uint32_t j = keep + lane; j < n; j += 32) fs.fsp[fs.frpos[j]] = 0.0f;
+    __syncwarp();
+    const float total = warp_prefix(fs.fsp, (int)n, fs.fp);
+    int pick = -1;
+    if (total > 1e-9f) pick = warp_find(fs.fp, (int)n, SEQ_FIND_GT, fmul(u01, total));
+    if (lane == 0) {
+        uint32_t token = amax;
+        int drew = 0;
+        if (total > 1e-9f) { token = pick >= 0 ? fs.fsid[pick] : V - 1; drew = 1; }
+        a.token[row] = token; a.status[row] = status;
+        if (a.drew) a.drew[row] = (uint8_t)drew;
+        if (a.argmax) a.argmax[row] = amax;
+        if (a.row_max) a.row_max[row] = m;
+        if (a.sumexp) a.sumexp[row] = S;
+        if (a.total) a.total[row] = total;
+    }
+    if (a.n_kept || a.dump_ids || a.dump_probs) {   // diagnostics: the kept set in id order
+        uint32_t done = 0;
+        for (uint32_t base = 0; base < n; base += 32) {
+            const uint32_t j = base + lane;
+            const bool kept = j < n && fs.fsp[j] > 0.0f;
+            const unsigned mask = __ballot_sync(FULL, kept);
+            const uint32_t at = done + __popc(mask & ((1u << lane) - 1u));
+            if (kept && at < a.dump_cap) {
+                if (a.dump_ids) a.dump_ids[(size_t)row * a.dump_cap + at] = fs.fsid[j];
+                if (a.dump_probs) a.dump_probs[(size_t)row * a.dump_cap + at] = fs.fsp[j];
+            }
+            done += __popc(mask);
+        }
+        if (lane == 0 && a.n_kept) a.n_kept[row] = done;
+    }
+}
+
+template <bool BF16>
+__global__ void __launch_bounds__(SNT, 2) stream_row_kernel(const RowArgs a, const StreamLaunch sl) {
+    constexpr int G = Geo<BF16>::G, GE = Geo<BF16>::GE, GS = Geo<BF16>::GS;
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    StreamSmem& sm = *reinterpret_cast<StreamSmem*>(smem_raw);
+    const uint32_t H = sl.hash_slots;
+    uint32_t* hkey = sm.u.hash;
+    uint32_t* hcnt = sm.u.hash + H;
+    const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
+    const uint32_t V = a.vocab;
+    const uint32_t n_pieces = (V + S_PIECE - 1) / S_PIECE;
+    const uint32_t n_regions = (V + S_REGION - 1) / S_REGION;
+    const bool ragged = (V % S_PIECE) != 0;
+    const uint32_t lane_e0 = (uint32_t)w * S_REGION + (uint32_t)lane * GE;   // first element of the thread inside a piece
+    const uint32_t mshift = ((uint32_t)lane * GE) & 31u;                     // its position inside a mask word
+    float* stg = sm.u.stage + w * S_REGION;
+    if (tid < 32) sm.exp_tab[tid] = kExp2TableDev[tid];
+    if (tid == 0)
+#pragma unroll 1
+        for (int i = 0; i < 16; i++) sm.prof_acc[i] = 0;
+    constexpr int PREP_TID = SNT - 32;   // lane 0 of the last warp
+    if (tid == PREP_TID && blockIdx.x < a.rows) sprepare_row<BF16>(a, sl, blockIdx.x, sm.ctl[0]);
+    long long tick_ = clock64();
+    uint32_t it = 0;
+    for (uint32_t row = blockIdx.x; row < a.rows; row += gridDim.x, it++) {
+        // ---- gate: at most `cohort` rows ahead of the rows that have left their first pass
+        if (tid == 0 && row >= sl.cohort) {
+            const uint32_t need = row - sl.cohort + 1u;
+            const volatile uint32_t* done = sl.p1_done;
+#pragma unroll 1
+            for (uint32_t poll = 0; poll < sl.gate_polls; poll++) {
+                if (*done - sl.done_base >= need) break;
+                __nanosleep(200);
+            }
+        }
+        // this row's parameters are complete, and every warp is done with the row before
+        __syncthreads();
+        PGS_STICK(0);   // gate + row barrier
+        const SRowCtl& ctl = sm.ctl[it & 1];
+        if (tid == PREP_TID && row + gridDim.x < a.rows) sprepare_row<BF16>(a, sl, row + gridDim.x, sm.ctl[(it + 1) & 1]);
+        const bool writer = tid == 0;
+        if (ctl.kind != 0u) {
+            if (writer) {
+                if (ctl.kind == 1u) { a.token[row] = 0; a.status[row] = ROW_BAD_PARAM; if (a.drew) a.drew[row] = 0; }
+                else sl.work_rows[atomicAdd(sl.work_count, 1u)] = row;
+                sl.recs[row].kind = 0;
+                atomicAdd(sl.p1_done, 1u);
+            }
+            continue;
+        }
+        const float temp = ctl.temp;
+        const uint32_t top_k = ctl.top_k, gflags = ctl.gflags, h0 = ctl.h0, nh = ctl.nh;
+        const uint32_t* mw = ctl.mw;
+        const char* rowp = ctl.rowp;
+        const float sc = ctl.sc;
+        const bool greedy = temp < 1e-5f;
+        const bool has_mask = mw != nullptr;
+        const bool do_fp = !(fabsf(ctl.freq) < 1e-6f && fabsf(ctl.pres) < 1e-6f);
+        const bool do_rep = ctl.rep != 1.0f;
+        const bool pen = nh > 0 && (do_fp || do_rep);
+        // the EOS fix (engine.rs:1307-1312) touches one logit: where it sits in the piece / thread / register layout
+        const bool eos_on = has_mask && (gflags & 1u) && a.eos >= 0 && (uint32_t)a.eos < V;
+        uint32_t eos_piece = 0xffffffffu, eos_sub = 0u;
+        if (eos_on) {
+            const uint32_t r = (uint32_t)a.eos % S_PIECE, p = r % S_REGION;
+            const uint32_t e_tid = (r / S_REGION) * 32u + (p % GS) / GE;
+            if (e_tid == (uint32_t)tid) { eos_piece = (uint32_t)a.eos / S_PIECE; eos_sub = (p / GS) * GE + p % GE; }
+        }
+
+        // Two pieces per thread: the loads of piece s + 1 are out while piece s is worked on.  The first piece of a
+        // pass is requested by the caller, ahead of whatever it has to do first.
+        PieceBuf<BF16> buf0, buf1;
+        auto run_pass = [&](auto& body, bool rev) {
+            auto piece_of = [&](uint32_t st) { return rev ? n_pieces - 1u - st : st; };
+#pragma unroll 1
+            for (uint32_t st = 0;; st += 2) {
+                if (st + 1 < n_pieces) issue_loads<BF16>(buf1, rowp, piece_of(st + 1) * S_PIECE + lane_e0, V);
+                body(buf0, piece_of(st));
+                if (st + 1 >= n_pieces) break;
+                if (st + 2 < n_pieces) issue_loads<BF16>(buf0, rowp, piece_of(st + 2) * S_PIECE + lane_e0, V);
+                body(buf1, piece_of(st + 1));
+                if (st + 2 >= n_pieces) break;
+            }
+        };
+        // first loads of pass 1 (the last piece of the row), requested before the history is indexed
+        issue_loads<BF16>(buf0, rowp, (n_pieces - 1) * S_PIECE + lane_e0, V);
+
+        // ---- history: distinct ids with their counts, grouped by the warp region they fall into
+        if (pen) {
+            uint32_t* rcnt = reinterpret_cast<uint32_t*>(sm.reg_a);   // distinct ids per region, then the scatter cursor
+#pragma unroll 1
+            for (uint32_t s = tid; s < H; s += SNT) { hkey[s] = S_NIL; hcnt[s] = 0u; }
+#pragma unroll 1
+            for (uint32_t r = tid; r < n_regions; r += SNT) rcnt[r] = 0u;
+            __syncthreads();
+            int spilled = 0;
+#pragma unroll 1
+            for (uint32_t j = tid; j < nh; j += SNT) {
+                const uint32_t id = __ldg(a.hist_ids + h0 + j);
+                if (id >= V) continue;   // engine.rs:1562
+                uint32_t s = (id * 2654435761u) & (H - 1u);
+                bool placed = false;
+#pragma unroll 1
+                for (int probe = 0; probe < 128; probe++) {
+                    const uint32_t prev = atomicCAS(&hkey[s], S_NIL, id);
+                    if (prev == S_NIL) atomicAdd(&rcnt[id / S_REGION], 1u);
+                    if (prev == S_NIL || prev == id) { atomicAdd(&hcnt[s], 1u); placed = true; break; }
+                    s = (s + 1u) & (H - 1u);
+                }
+                if (!placed) spilled = 1;
+            }
+            spilled = __syncthreads_or(spilled);
+            if (spilled) {   // CTA-uniform
+                if (writer) { sl.work_rows[atomicAdd(sl.work_count, 1u)] = row; sl.recs[row].kind = 0; atomicAdd(sl.p1_done, 1u); }
+                continue;
+            }
+            // exclusive scan of the counts in region order; thread t owns the regions t * rpt ..
+            const uint32_t rpt = (n_regions + SNT - 1) / SNT;   // <= S_RPT
+            uint32_t cnt[S_RPT], own = 0u;
+#pragma unroll
+            for (int j = 0; j < S_RPT; j++) {
+                const uint32_t r = (uint32_t)tid * rpt + j;
+                cnt[j] = ((uint32_t)j < rpt && r < n_regions) ? rcnt[r] : 0u;
+                own += cnt[j];
+            }
+            uint32_t total;
+            uint32_t before = sblock_excl_scan_u32(own, &total, sm.scan_u);
+#pragma unroll
+            for (int j = 0; j < S_RPT; j++) {
+                const uint32_t r = (uint32_t)tid * rpt + j;
+                if ((uint32_t)j < rpt && r < n_regions) { sm.rs[r] = (uint16_t)before; rcnt[r] = before; }
+                before += cnt[j];
+            }
+            if (tid == 0) sm.rs[n_regions] = (uint16_t)total;
+            __syncthreads();
+#pragma unroll 1
+            for (uint32_t s = tid; s < H; s += SNT) {
+                const uint32_t id = hkey[s];
+                if (id == S_NIL) continue;
+                const uint32_t at = atomicAdd(&rcnt[id / S_REGION], 1u);
+                sm.pid[at] = (uint16_t)(id % S_REGION);
+                sm.pval[at] = hcnt[s];
+            }
+            __syncthreads();   // the table is dead from here on: its space is the staging area
+        }
+        PGS_STICK(1);   // history indexed
+
+        // The processed logits of one piece in registers: penalties (through the warp's staging area: the owner
+        // of a history id is whichever lane holds it), grammar mask / end of row, EOS fix.  PASS 1 computes the
+        // penalised values and leaves them where the counts were; PASS 2 takes them from there.
+        auto make_x = [&](float (&x)[S_EPT], uint32_t q, auto pass_tag) {
+            constexpr int PASS = decltype(pass_tag)::value;
+            const uint32_t region = q * SNW + (uint32_t)w;
+            if (pen && region < n_regions) {
+                const uint32_t c0 = sm.rs[region], c1 = sm.rs[region + 1];
+                if (c1 > c0) {   // warp-uniform
+#pragma unroll
+                    for (int j = 0; j < S_EPT; j += 4)
+                        *reinterpret_cast<float4*>(stg + (j / GE) * GS + lane * GE + (j % GE)) = make_float4(x[j], x[j + 1], x[j + 2], x[j + 3]);
+                    __syncwarp();
+#pragma unroll 1
+                    for (uint32_t i = c0 + lane; i < c1; i += 32) {
+                        const uint32_t off = sm.pid[i];
+                        if (PASS == 1) {
+                            float v = stg[off];
+                            if (do_rep) v = v > 0.0f ? fdiv(v, ctl.rep) : fmul(v, ctl.rep);
+                            if (do_fp) {
+                                v = fsub(v, fmul(ctl.freq, (float)sm.pval[i]));
+                                if (fabsf(ctl.pres) > 1e-6f) v = fsub(v, ctl.pres);
+                            }
+                            v = finite_f(v) ? v : -INFINITY;   // an overflowed penalty counts as masked
+                            stg[off] = v;
+                            sm.pval[i] = f2u(v);
+                        } else {
+                            stg[off] = u2f(sm.pval[i]);
+                        }
+                    }
+                    __syncwarp();
+#pragma unroll
+                    for (int j = 0; j < S_EPT; j += 4) {
+                        const float4 v = *reinterpret_cast<const float4*>(stg + (j / GE) * GS + lane * GE + (j % GE));
+                        x[j] = v.x; x[j + 1] = v.y; x[j + 2] = v.z; x[j + 3] = v.w;
+                    }
+                    __syncwarp();   // the next piece's staging must not overtake these reads
+                }
+            }
+            if (has_mask || (ragged && q == n_pieces - 1)) {   // warp-uniform
+#pragma unroll
+                for (int h = 0; h < G; h++) {
+                    const uint32_t idx = q * S_PIECE + lane_e0 + h * GS;
+                    const uint32_t bits = idx < V ? (has_mask ? __ldg(mw + (idx >> 5)) >> mshift : 0xffffffffu) : 0u;
+#pragma unroll
+                    for (int c = 0; c < GE; c++)
+                        if (!((bits >> c) & 1u)) x[h * GE + c] = -INFINITY;
+                }
+                if (q == eos_piece) {
+#pragma unroll
+                    for (int j = 0; j < S_EPT; j++)
+                        if ((uint32_t)j == eos_sub && !finite_f(x[j])) x[j] = 0.0f;
+                }
+            }
+        };
+
+        // ================================================================ pass 1 (HBM, last piece first)
+#pragma unroll
+        for (int c = 0; c < S_NCELL; c++) sm.cell[c * SNT + tid] = -INFINITY;
+        float am = 0.0f;   // max |raw logit|, NaN-propagating: the sanity check
+        auto p1_body = [&](const PieceBuf<BF16>& b, uint32_t q) {
+            float x[S_EPT];
+            unpack<BF16>(x, b);
+            am = absmax_ept_nan(am, x);
+            make_x(x, q, std::integral_constant<int, 1>());
+            const float pm = max_ept(x);
+            const uint32_t ci = (q % S_NCELL) * SNT + tid;
+            const float cur = sm.cell[ci];
+            // pieces arrive in descending order, so an equal maximum here has the lower id
+            if (pm > cur || (pm == cur && pm > -INFINITY)) {
+                int j0 = 0;
+#pragma unroll
+                for (int j = S_EPT - 1; j >= 0; j--) if (x[j] == pm) j0 = j;
+                sm.cell[ci] = pm;
+                sm.celli[ci] = elem_id<BF16>(q * S_PIECE + lane_e0, j0);
+            }
+            if (!greedy) {
+                // plain sum of the numerators of the warp's 1024 logits, relative to their own maximum
+                const uint32_t wkey = __reduce_max_sync(FULL, order_key(pm));
+                float wm = -INFINITY, ps = 0.0f;
+                if (wkey) {
+                    wm = key_to_float(wkey);
+                    const float cc = -wm * sc;
+                    float p0 = 0.0f, p1 = 0.0f, p2 = 0.0f, p3 = 0.0f;
+#pragma unroll
+                    for (int j = 0; j < S_EPT; j += 4) {
+                        p0 += ex2_approx_ftz(__fmaf_rn(x[j], sc, cc));
+                        p1 += ex2_approx_ftz(__fmaf_rn(x[j + 1], sc, cc));
+                        p2 += ex2_approx_ftz(__fmaf_rn(x[j + 2], sc, cc));
+                        p3 += ex2_approx_ftz(__fmaf_rn(x[j + 3], sc, cc));
+                    }
+                    ps = (p0 + p1) + (p2 + p3);
+#pragma unroll
+                    for (int o = 16; o; o >>= 1) ps += __shfl_xor_sync(FULL, ps, o);
+                }
+                const uint32_t region = q * SNW + (uint32_t)w;
+                if (lane == 0 && region < n_regions) { sm.reg_a[region] = wm; sm.reg_b[region] = ps; }
+            }
+        };
+        run_pass(p1_body, true);
+        // the first loads of pass 2 go out before the reductions
+        if (!greedy) issue_loads<BF16>(buf0, rowp, lane_e0, V);
+        PGS_STICK(2);   // pass 1
+
+        // ---- row maximum / argmax (lowest id), sanity, and the material for the top-k bound
+        {
+            uint32_t bkey = 0u, bidx = 0xffffffffu, lo = 0xffffffffu, fin = 0u;
+#pragma unroll
+            for (int c = 0; c < S_NCELL; c++) {
+                const uint32_t k = order_key(sm.cell[c * SNT + tid]);
+                if (!k) continue;
+                const uint32_t i = sm.celli[c * SNT + tid];
+                if (k > bkey || (k == bkey && i < bidx)) { bkey = k; bidx = i; }
+                lo = umin(lo, k);
+                fin++;
+            }
+            const uint32_t wk = __reduce_max_sync(FULL, bkey);
+            const uint32_t wi = __reduce_min_sync(FULL, bkey == wk ? bidx : 0xffffffffu);
+            const uint32_t wlo = __reduce_min_sync(FULL, lo);
+            const uint32_t wfin = __reduce_add_sync(FULL, fin);
+            const uint32_t wbad = __any_sync(FULL, !(am < INFINITY)) ? 1u : 0u;
+            if (lane == 0) { sm.red_key[w] = wk; sm.red_idx[w] = wi; sm.red_lo[w] = wlo; sm.red_fin[w] = wfin; sm.red_flag[w] = wbad; }
+#pragma unroll
+            for (int u = 0; u < S_BPT; u++) sm.hist[u * SNT + tid] = 0u;
+            if (tid == 0) { sm.cand_n = 0u; sm.sel_bucket = 0u; }
+        }
+        __syncthreads();
+        const uint32_t gkey = __reduce_max_sync(FULL, lane < SNW ? sm.red_key[lane] : 0u);
+        const uint32_t amax_raw = __reduce_min_sync(FULL, (lane < SNW && sm.red_key[lane] == gkey) ? sm.red_idx[lane] : 0xffffffffu);
+        const uint32_t lo_key = __reduce_min_sync(FULL, lane < SNW ? sm.red_lo[lane] : 0xffffffffu);
+        const uint32_t n_fin = __reduce_add_sync(FULL, lane < SNW ? sm.red_fin[lane] : 0u);
+        const bool nonfinite = __any_sync(FULL, lane < SNW && sm.red_flag[lane] != 0u);
+        const bool any = gkey != 0u;
+        const float m = any ? key_to_float(gkey) : -INFINITY;
+        const uint32_t amax = any ? amax_raw : 0u;
+        const int status = any ? ROW_OK : ROW_EMPTY;
+        if (writer) atomicAdd(sl.p1_done, 1u);
+        if (nonfinite || (gflags & 2u) || greedy || !any) {
+            if (writer) {
+                if (nonfinite) {
+                    a.token[row] = 0; a.status[row] = ROW_NONFINITE; if (a.drew) a.drew[row] = 0;
+                    if (a.faulted) atomicAdd(a.faulted, 1ull);
+                } else if (gflags & 2u) {
+                    a.token[row] = 0; a.status[row] = ROW_DEAD; if (a.drew) a.drew[row] = 0;
+                } else {
+                    a.token[row] = amax; a.status[row] = status;
+                    if (a.drew) a.drew[row] = 0;
+                    if (a.argmax) a.argmax[row] = amax;
+                    if (a.row_max) a.row_max[row] = m;
+                    if (a.sumexp) a.sumexp[row] = 0.0f;
+                    if (a.total) a.total[row] = 0.0f;
+                    if (a.n_kept) a.n_kept[row] = 0u;
+                }
+                sl.recs[row].kind = 0;
+            }
+            PGS_STICK(3);
+            continue;
+        }
+
+        // ---- top-k bound.  The per-thread maxima are spread over S_NB equal-width buckets between their
+        // smallest finite value and the row maximum (a monotone map); with b the highest bucket such that the
+        // buckets b.. hold at least top_k maxima, every logit of bucket b - 1 or higher is a candidate.
+        const float t = fmaxf(temp, 1e-9f);
+        float cut = -INFINITY;
+        if (n_fin >= top_k) {   // CTA-uniform
+            const float lo_v = key_to_float(lo_key);
+            const float scb = m > lo_v ? (float)(S_NB - 1) / (m - lo_v) : 0.0f;
+#pragma unroll
+            for (int c = 0; c < S_NCELL; c++) {
+                const float cv = sm.cell[c * SNT + tid];
+                if (finite_f(cv)) atomicAdd(&sm.hist[min((uint32_t)(S_NB - 1), (uint32_t)((cv - lo_v) * scb))], 1u);
+            }
+            __syncthreads();
+            // thread j owns the S_BPT buckets S_NB-1 - j*S_BPT - u; `above` = maxima in higher buckets
+            uint32_t hv[S_BPT], own = 0u;
+#pragma unroll
+            for (int u = 0; u < S_BPT; u++) { hv[u] = sm.hist[(S_NB - 1) - tid * S_BPT - u]; own += hv[u]; }
+            uint32_t total;
+            uint32_t above = sblock_excl_scan_u32(own, &total, sm.scan_u);
+#pragma unroll
+            for (int u = 0; u < S_BPT; u++) {
+                if (above < top_k && top_k <= above + hv[u]) sm.sel_bucket = (uint32_t)((S_NB - 1) - tid * S_BPT - u);
+                above += hv[u];
+            }
+            __syncthreads();
+            const uint32_t bsel = sm.sel_bucket;
+            const float bound = (bsel >= 1u && scb > 0.0f) ? lo_v + ((float)bsel - 1.0f) / scb : lo_v;
+            // every logit whose probability could still tie with the k-th one stays above the cut
+            const float delta = 4.8e-7f * (fabsf(m - bound) + 4.0f * t) + 4.8e-7f * (fabsf(bound) + fabsf(m));
+            cut = bound - delta;
+        }
+        const float cut_f = fmaxf(cut, -3.4e38f);   // masked entries (-inf) are never candidates
+
+        // ---- where the fold stands at every warp region.  The plain sums overestimate the fold's running value
+        // by up to a few 1e-4 (the small terms it drops), so a region takes the quick path only if the whole
+        // interval [start * (1 - 2^-9), end * (1 + 2^-9)] lies inside one binade.
+        {
+            float carry = 0.0f;
+#pragma unroll 1
+            for (uint32_t r0 = 0; r0 < n_regions; r0 += SNT) {   // CTA-uniform trip count
+                const uint32_t r = r0 + (uint32_t)tid;
+                float P = 0.0f;
+                if (r < n_regions && sm.reg_b[r] > 0.0f) P = sm.reg_b[r] * ex2_approx_ftz((sm.reg_a[r] - m) * sc);
+                float tot;
+                const float pre = carry + sblock_excl_scan_f32(P, &tot, sm.scan_f);
+                if (r < n_regions) {
+                    const float lo_e = pre * 0.998046875f, hi_e = (pre + P) * 1.001953125f;
+                    const uint32_t kb = f2u(lo_e) & 0x7f800000u;
+                    const bool quick = kb != 0u && kb == (f2u(hi_e) & 0x7f800000u);
+                    sm.reg_a[r] = quick ? u2f(kb) : 0.0f;
+                    sm.reg_b[r] = pre;
+                }
+                carry += tot;
+                __syncthreads();   // scan_f is reused by the next round
+            }
+        }
+        PGS_STICK(3);   // reductions, bound, fold table
+
+        // ================================================================ pass 2 (L2, first piece first)
+        // numerator = 2^(x * sc + c): c = -m * sc split into c_hi + c_lo; c_lo scales the final sum
+        const double c_d = -(double)m * (double)sc;
+        const float c_hi = (float)c_d;
+        const double c_lo = c_d - (double)c_hi;
+        double accd = 0.0;   // this warp's share of the fold (the same value in all its lanes)
+        auto p2_body = [&](const PieceBuf<BF16>& b, uint32_t q) {
+            float x[S_EPT];
+            unpack<BF16>(x, b);
+            make_x(x, q, std::integral_constant<int, 2>());
+            if (max_ept(x) >= cut_f) {
+#pragma unroll
+                for (int j = 0; j < S_EPT; j++)
+                    if (x[j] >= cut_f) {
+                        const uint32_t at = atomicAdd(&sm.cand_n, 1u);
+                        if (at < (uint32_t)F_MCAP) { sm.cand_id[at] = elem_id<BF16>(q * S_PIECE + lane_e0, j); sm.cand_x[at] = x[j]; }
+                    }
+            }
+            const uint32_t region = q * SNW + (uint32_t)w;
+            if (region >= n_regions) return;   // warp-uniform: past the end of the row
+#pragma unroll
+            for (int j = 0; j < S_EPT; j++) x[j] = ex2_approx_ftz(__fmaf_rn(x[j], sc, c_hi));   // -inf -> 0
+            const float base = sm.reg_a[region];
+            bool quick = base != 0.0f;
+            if (quick) {
+                // every thread from the lower end of the binade the fold is in
+                float ac[4] = {base, base, base, base};   // four chains: the increments do not depend on the order
+#pragma unroll
+                for (int j = 0; j < S_EPT / 4; j++) {
+#pragma unroll
+                    for (int c = 0; c < 4; c++) ac[c] = fadd(ac[c], x[c * (S_EPT / 4) + j]);
+                }
+                const uint32_t bb = f2u(base);
+                quick = __all_sync(FULL, ((((f2u(ac[0]) ^ bb) | (f2u(ac[1]) ^ bb)) | ((f2u(ac[2]) ^ bb) | (f2u(ac[3]) ^ bb))) & 0xff800000u) == 0u);
+                if (quick) {
+                    const uint32_t ws = __reduce_add_sync(FULL, ((f2u(ac[0]) - bb) + (f2u(ac[1]) - bb)) + ((f2u(ac[2]) - bb) + (f2u(ac[3]) - bb)));   // < 32 * 2^25
+                    accd += (double)ws * ((double)base * 1.1920928955078125e-07);        // units of the binade's ulp
+                }
+            }
+            if (!quick) {
+                // the running value may leave its binade here (or the fold starts here): every 128-bit group from
+                // its own estimate of the running value, real additions, so that a crossing is reproduced
+                float stv[G], run = 0.0f;
+#pragma unroll
+                for (int h = 0; h < G; h++) {
+                    float gs = 0.0f;
+#pragma unroll
+                    for (int c = 0; c < GE; c++) gs += x[h * GE + c];
+                    float inc = gs;
+#pragma unroll
+                    for (int o = 1; o < 32; o <<= 1) {
+                        const float up = __shfl_up_sync(FULL, inc, o);
+                        if (lane >= o) inc += up;
+                    }
+                    stv[h] = run + (inc - gs);
+                    run += __shfl_sync(FULL, inc, 31);
+                }
+                const float R0 = sm.reg_b[region];
+                float tinc = 0.0f;
+#pragma unroll
+                for (int h = 0; h < G; h++) {
+                    const float R = fadd(R0, stv[h]);
+                    float a2 = R;
+#pragma unroll
+                    for (int c = 0; c < GE; c++) a2 = fadd(a2, x[h * GE + c]);
+                    tinc = fadd(tinc, fsub(a2, R));
+                }
+                double td = (double)tinc;
+#pragma unroll
+                for (int o = 16; o; o >>= 1) td += __shfl_xor_sync(FULL, td, o);
+                accd += td;
+            }
+        };
+        run_pass(p2_body, false);
+        if (lane == 0) sm.wacc[w] = accd;
+        __syncthreads();   // the candidate list and the warps' shares are complete
+        PGS_STICK(4);   // pass 2
+        double s_d = lane < SNW ? sm.wacc[lane] : 0.0;
+#pragma unroll
+        for (int o = 16; o; o >>= 1) s_d += __shfl_xor_sync(FULL, s_d, o);
+        const float S = (float)(s_d * (1.0 + c_lo * 0.6931471805599453));
+        const uint32_t n_cand = sm.cand_n;
+        if (n_cand > (uint32_t)F_MCAP) {   // CTA-uniform
+            if (writer) { sl.work_rows[atomicAdd(sl.work_count, 1u)] = row; sl.recs[row].kind = 0; }
+            continue;
+        }
+        if (n_cand <= (uint32_t)S_FCAP) {
+            if (writer) sl.recs[row].kind = 0;
+            sfinish_row(sm, a, row, n_cand, m, t, S, top_k, ctl.top_p, ctl.u01, amax, status);
+        } else {
+            // long lists: the finish kernel takes the row from here
+#pragma unroll 1
+            for (uint32_t j = tid; j < n_cand; j += SNT) {
+                sl.cand_id[(size_t)row * F_MCAP + j] = sm.cand_id[j];
+                sl.cand_x[(size_t)row * F_MCAP + j] = sm.cand_x[j];
+            }
+            if (writer) {
+                RowRec& rec = sl.recs[row];
+                rec.kind = 1; rec.n_cand = n_cand; rec.amax = amax; rec.status = status;
+                rec.m = m; rec.t = t; rec.n_parts = 1; rec.part[0] = (double)S;
+            }
+        }
+        PGS_STICK(5);   // finish
+    }
+    if (sl.prof && tid == 0)
+#pragma unroll 1
+        for (int i = 0; i < 16; i++) sl.prof[blockIdx.x * 16 + i] += sm.prof_acc[i];
+}
+
+size_t stream_smem_bytes() { return sizeof(StreamSmem); }
+uint32_t stream_threads() { return SNT; }
+
+cudaError_t configure_stream() {
+    cudaError_t e = cudaFuncSetAttribute(stream_row_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(StreamSmem));
+    if (e != cudaSuccess) return e;
+    e = cudaFuncSetAttribute(stream_row_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(StreamSmem));
+    if (e != cudaSuccess) return e;
+    e = cudaFuncSetAttribute(stream_row_kernel<false>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+    if (e != cudaSuccess) return e;
+    return cudaFuncSetAttribute(stream_row_kernel<true>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+}
+
+// CTAs of this kernel that one SM holds
+cudaError_t stream_ctas_per_sm(int* out) {
+    return cudaOccupancyMaxActiveBlocksPerMultiprocessor(out, stream_row_kernel<false>, SNT, sizeof(StreamSmem));
+}
+
+cudaError_t launch_stream(const RowArgs& a, const StreamLaunch& sl, uint32_t grid, cudaStream_t stream) {
+    if (a.dtype == 0) stream_row_kernel<false><<<grid, SNT, sizeof(StreamSmem), stream>>>(a, sl);
+    else stream_row_kernel<true><<<grid, SNT, sizeof(StreamSmem), stream>>>(a, sl);
+    return cudaGetLastError();
+}
+
+}  // namespace pgs
