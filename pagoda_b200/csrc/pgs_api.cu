@@ -224,11 +224,11 @@ extern "C" int pgs_create(int device, uint32_t max_rows, uint32_t max_vocab, uin
         PGS_CUDA(nullptr, pgs::configure_stream());
         PGS_CUDA(nullptr, pgs::stream_ctas_per_sm(&h->stream_ctas));
         if (h->stream_ctas < 1) return fail(nullptr, PGS_ERR_CUDA, "pgs_create: the row kernel does not fit an SM (%zu bytes of shared memory)", h->stream_smem);
-        // rows that may read HBM at once: about an SM count of them saturate it, and the rows in flight stay inside L2
-        h->stream_cohort = h->sm_count > 40 ? (uint32_t)h->sm_count - 20u : (uint32_t)h->sm_count;
+        // rows that may be in their first pass at once: no limit by default (measured on 256 x 151936: a limit of
+        // about an SM count keeps pass 2 in L2 but leaves half the threads of every SM waiting at the gate)
+        h->stream_cohort = 0xffffffffu;
         if (const char* ev = getenv("PGS_COHORT")) { if (atoi(ev) > 0) h->stream_cohort = (uint32_t)atoi(ev); }
-        h->use_cluster = 1;   // the streaming kernel is opt-in (PGS_PATH=stream) until it is the faster one
-        if (const char* ev = getenv("PGS_PATH")) h->use_cluster = strcmp(ev, "stream") != 0;
+        if (const char* ev = getenv("PGS_PATH")) h->use_cluster = strcmp(ev, "cluster") == 0;
         if (const char* ev = getenv("PGS_EXACT")) h->exact = atoi(ev);
         if (const char* ev = getenv("PGS_PROFILE")) {
             if (atoi(ev)) {
@@ -403,15 +403,11 @@ int launch_step(pgs_handle* h, pgs::RowArgs& a, cudaStream_t stream) {
         fl.cluster = 1; fl.slice_len = 0; fl.chunk = 0;
         fl.work_rows = h->work_rows; fl.work_count = h->work_count; fl.prof = nullptr;
         fl.recs = h->recs; fl.cand_id = h->cand_id; fl.cand_x = h->cand_x;
-        PGS_CUDA(h, cudaEventRecord(h->ev_fork, stream));
-        PGS_CUDA(h, cudaStreamWaitEvent(h->side, h->ev_fork, 0));
         PGS_CUDA(h, pgs::launch_finish(a, fl, stream));
         pgs::RowArgs wl = a;
         wl.work_rows = h->work_rows;
         wl.work_count = h->work_count;
-        PGS_CUDA(h, pgs::launch_general(wl, grid < 32u ? grid : 32u, h->side));
-        PGS_CUDA(h, cudaEventRecord(h->ev_join, h->side));
-        PGS_CUDA(h, cudaStreamWaitEvent(stream, h->ev_join, 0));
+        PGS_CUDA(h, pgs::launch_general(wl, grid < 32u ? grid : 32u, stream));
         h->counters.kernel_launches += 3;
         return PGS_OK;
     }

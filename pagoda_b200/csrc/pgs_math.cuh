@@ -149,6 +149,7 @@ __device__ __forceinline__ float ex2_approx_ftz(float x) {
 PGS_HD uint32_t order_key(float x) {
     uint32_t b = f2u(x);
     if ((b & 0x7f800000u) == 0x7f800000u) return 0u;
+    if ((b << 1) == 0u) b = 0u;   // -0.0 and +0.0 compare equal in the reference's argmax (sampler.rs:64)
     return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
 }
 PGS_HD float key_to_float(uint32_t k) {

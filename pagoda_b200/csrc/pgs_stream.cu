@@ -1,19 +1,17 @@
 // Streaming row kernel: the hot path of the sampler.
 //
-// One CTA of 256 threads (two per SM, up to 128 registers per thread) owns one batch row at a time and reads it
-// twice with plain 128-bit coalesced loads, 32 logits per thread and piece, the loads of the next piece on their
-// way while a piece is worked on.  (What a piece costs beyond its logits -- addresses, table look-ups, warp
-// reductions, loop control -- is paid once per thread and piece, so pieces are as large as the registers allow;
-// with 8 logits per thread and piece the kernel executed 57 instructions per logit.)  Inside a pass nothing
-// synchronises the warps:
+// One CTA of 512 threads (two per SM) owns one batch row at a time and reads it twice with plain 128-bit
+// coalesced loads, sixteen logits per thread and piece.  Inside a pass nothing synchronises the warps, so the
+// loads of some overlap the arithmetic of the others, and what a piece costs beyond its logits (addresses, table
+// look-ups, warp reductions, loop control) is paid once per sixteen logits:
 //
-//   pass 1, last piece first, from HBM: sanity, penalties, grammar bitmask, EOS fix; per thread eight running
-//           maxima (one per piece number mod 8) with the place where each first occurs; per warp and piece the
+//   pass 1, last piece first, from HBM: sanity, penalties, grammar bitmask, EOS fix; per thread its running
+//           maximum and four more (one per piece number mod 4) that bound the top-k threshold; per warp and piece the
 //           plain sum of the softmax numerators relative to the warp's own maximum;
-//   between: row maximum and argmax (lowest id); a bound for the top-k threshold: the k-th largest of the 2048
+//   between: row maximum and argmax (lowest id: the threads that hold the maximum look at that piece again); a bound for the top-k threshold: the k-th largest of the 2048
 //           per-thread maxima is reached by at least k logits, so "logit >= that bound" is a superset of the
 //           top-k set that is only slightly larger; and, from the rescaled plain sums, the value the reference's
-//           running sum has when it reaches each warp's 1024 logits of each piece, to within 1e-3;
+//           running sum has when it reaches each warp's 512 logits of each piece, to within 1e-3;
 //   pass 2, first piece first, from L2 (the pieces read last in pass 1 are the freshest there): the same
 //           processed logits again, candidates above the bound, softmax numerators by the hardware exp2, and
 //           the reference's sequential f32 sum;
@@ -28,7 +26,7 @@
 // The f32 left fold (pagoda/src/sampler.rs:99-113): while the running value stays inside one binade, adding a
 // non-negative term is an integer addition in units of that binade's ulp which depends on the running value only
 // through its parity.  Wherever the estimate above puts the running value safely inside one binade for a warp's
-// whole share of a piece, every thread adds its 32 numerators to that binade's lower end (real f32
+// whole share of a piece, every thread adds its sixteen numerators to that binade's lower end (real f32
 // additions) and the increments are summed as integers; the few shares in which the running value may change
 // binade are folded 128 bits at a time from their own estimates of the running value, which reproduces the
 // crossing.  Ties of round-half-even are decided by the parity of a stand-in, not of the true running value: the
@@ -72,9 +70,19 @@ struct SRowCtl {
     const char* rowp;       // first logit of the row
     const uint32_t* mw;     // grammar mask words of the row's state, or null
     float temp, freq, pres, rep, top_p, u01;
-    float sc;               // log2(e) / max(temp, 1e-9)
+    float sc, sc_lo;        // log2(e) / max(temp, 1e-9) as a two-float sum
     uint32_t top_k, gflags, h0, nh;
     uint32_t kind;          // 0 serve, 1 bad parameters, 2 defer to the general kernel
+};
+
+// What the pass loops need to know about the row they work on.
+enum : uint32_t { PF_PEN = 1u, PF_REP = 2u, PF_FP = 4u, PF_PRES = 8u };
+struct PassArgs {
+    const char* rowp;
+    const uint32_t* mw;
+    float sc, sc_lo, c_hi, c_lo, cut_f, freq, pres, rep;
+    uint32_t V, n_full, n_regions, flags;
+    uint32_t eos_piece, eos_tid, eos_sub;
 };
 
 struct FinishScratch {   // at most S_FCAP candidates
@@ -85,15 +93,17 @@ struct FinishScratch {   // at most S_FCAP candidates
 
 struct StreamSmem {
     SRowCtl ctl[2];
+    PassArgs pa;
     unsigned long long exp_tab[32];
-    uint32_t red_key[SNW], red_idx[SNW], red_lo[SNW], red_fin[SNW], red_flag[SNW];
+    uint32_t red_key[SNW], red_lo[SNW], red_fin[SNW], red_flag[SNW];
     uint32_t scan_u[SNW];
     float scan_f[SNW];
     double wacc[SNW];               // per-warp share of the fold
-    uint32_t cand_n, sel_bucket, n_live;
+    uint32_t cand_n, sel_bucket, n_live, amax;
     uint32_t hist[S_NB];
     float cell[S_CELLS];             // [S_NCELL][SNT]
-    uint32_t celli[S_CELLS];         // id at which each maximum first occurs
+    float t_am[SNT], t_max[SNT];     // per-thread results of pass 1 over the whole pieces
+    uint32_t t_q[SNT];
     uint32_t cand_id[F_MCAP];
     float cand_x[F_MCAP];
     // per warp region of the row (512 consecutive logits): pass 1 leaves the warp's maximum and the plain sum of
@@ -103,6 +113,7 @@ struct StreamSmem {
     float reg_a[S_MAX_REGIONS], reg_b[S_MAX_REGIONS];
     // distinct history ids grouped by region: those of region r are the entries rs[r] .. rs[r + 1]
     uint16_t rs[S_MAX_REGIONS + 2];
+    uint32_t pmask[S_MAX_REGIONS / 32];   // bit r: region r holds history ids
     uint16_t pid[S_MAX_HASH / 2];    // position inside the region
     uint32_t pval[S_MAX_HASH / 2];   // count, then (after pass 1) the bits of the penalised logit
     long long prof_acc[16];
@@ -165,47 +176,6 @@ template <bool BF16> struct Geo {
     static constexpr int GE = S_EPT / G;        // logits per group
     static constexpr int GS = 32 * GE;          // logits between two groups of a thread
 };
-
-// A piece's share of a thread as it comes from memory; groups past the end of the row read as zeros.
-template <bool BF16> struct PieceBuf;
-template <> struct PieceBuf<false> { float4 v[S_EPT / 4]; };
-template <> struct PieceBuf<true> { uint4 v[S_EPT / 8]; };
-template <bool BF16>
-__device__ __forceinline__ void issue_loads(PieceBuf<BF16>& b, const char* rowp, uint32_t e0, uint32_t V) {
-#pragma unroll
-    for (int h = 0; h < Geo<BF16>::G; h++) {
-        const uint32_t idx = e0 + h * Geo<BF16>::GS;
-        // (volatile inline assembly: the compiler must not sink these loads towards their first use)
-        if constexpr (BF16) {
-            b.v[h] = make_uint4(0u, 0u, 0u, 0u);
-            if (idx < V)
-                asm volatile("ld.global.cg.v4.u32 {%0, %1, %2, %3}, [%4];"
-                             : "=r"(b.v[h].x), "=r"(b.v[h].y), "=r"(b.v[h].z), "=r"(b.v[h].w) : "l"(rowp + (size_t)idx * 2));
-        } else {
-            b.v[h] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-            if (idx < V)
-                asm volatile("ld.global.cg.v4.f32 {%0, %1, %2, %3}, [%4];"
-                             : "=f"(b.v[h].x), "=f"(b.v[h].y), "=f"(b.v[h].z), "=f"(b.v[h].w) : "l"(rowp + (size_t)idx * 4));
-        }
-    }
-}
-template <bool BF16>
-__device__ __forceinline__ void unpack(float (&x)[S_EPT], const PieceBuf<BF16>& b) {
-    if constexpr (BF16) {
-#pragma unroll
-        for (int h = 0; h < Geo<true>::G; h++) {
-            const uint32_t r[4] = {b.v[h].x, b.v[h].y, b.v[h].z, b.v[h].w};
-#pragma unroll
-            for (int u = 0; u < 4; u++) {   // a 16-bit shift widens bf16 to f32 exactly
-                x[h * 8 + 2 * u] = __uint_as_float(r[u] << 16);
-                x[h * 8 + 2 * u + 1] = __uint_as_float(r[u] & 0xffff0000u);
-            }
-        }
-    } else {
-#pragma unroll
-        for (int h = 0; h < Geo<false>::G; h++) { x[4 * h] = b.v[h].x; x[4 * h + 1] = b.v[h].y; x[4 * h + 2] = b.v[h].z; x[4 * h + 3] = b.v[h].w; }
-    }
-}
 
 // id of the thread's j-th logit of a piece whose first group starts at e0
 template <bool BF16> __device__ __forceinline__ uint32_t elem_id(uint32_t e0, int j) {
@@ -284,7 +254,12 @@ __device__ __forceinline__ void sprepare_row(const RowArgs& a, const StreamLaunc
     const bool pen = nh > 0 && (!(fabsf(freq) < 1e-6f && fabsf(pres) < 1e-6f) || rep != 1.0f);
     const bool defer = !aligned || (!greedy && (!use_k || top_k > (uint32_t)S_KMAX)) || (pen && 2u * nh > sl.hash_slots);
     c.rowp = rowp; c.mw = mw; c.temp = temp; c.freq = freq; c.pres = pres; c.rep = rep; c.top_p = top_p; c.u01 = u01;
-    c.sc = (float)(1.4426950408889634 / (double)fmaxf(temp, 1e-9f));
+    const double scale_d = 1.4426950408889634 / (double)fmaxf(temp, 1e-9f);
+    // rounded down, so that the second float is positive and a masked entry (-inf) stays -inf through both products
+    float sc_hi = (float)scale_d;
+    if ((double)sc_hi >= scale_d) sc_hi = u2f(f2u(sc_hi) - 1u);
+    c.sc = sc_hi;
+    c.sc_lo = (float)(scale_d - (double)sc_hi);
     c.top_k = top_k; c.gflags = gflags; c.h0 = h0; c.nh = nh;
     c.kind = bad ? 1u : defer ? 2u : 0u;
 }
@@ -368,9 +343,298 @@ __device__ __forceinline__ void sfinish_row(StreamSmem& sm, const RowArgs& a, ui
     }
 }
 
+// ------------------------------------------------------------------------------------------------------------
+// The two passes.  Their loops over the whole pieces of a row are functions of their own (not inlined), so that
+// the registers of each loop are allocated for that loop alone (sixteen logits and a dozen values of state: no
+// spills in the loops).  What they need to know about the row is in shared
+// memory (PassArgs); the ragged last piece of a row, if any, is handled by the caller with the same piece code.
+
+template <bool BF16> struct Raw;
+template <> struct Raw<false> { float4 v[4]; };
+template <> struct Raw<true> { uint4 v[2]; };
+
+// a whole piece: no bounds checks
+template <bool BF16>
+__device__ __forceinline__ void raw_load(Raw<BF16>& r, const char* p) {
+    constexpr int G = Geo<BF16>::G, STEP = Geo<BF16>::GS * (BF16 ? 2 : 4);
+#pragma unroll
+    for (int h = 0; h < G; h++) {
+        if constexpr (BF16) r.v[h] = __ldcg(reinterpret_cast<const uint4*>(p + h * STEP));
+        else r.v[h] = __ldcg(reinterpret_cast<const float4*>(p + h * STEP));
+    }
+}
+// the ragged last piece: groups past the end of the row read as zeros
+template <bool BF16>
+__device__ __forceinline__ void raw_load_tail(Raw<BF16>& r, const char* p, uint32_t e0, uint32_t V) {
+    constexpr int G = Geo<BF16>::G, GS = Geo<BF16>::GS, STEP = GS * (BF16 ? 2 : 4);
+#pragma unroll
+    for (int h = 0; h < G; h++) {
+        if constexpr (BF16) r.v[h] = e0 + h * GS < V ? __ldcg(reinterpret_cast<const uint4*>(p + h * STEP)) : make_uint4(0u, 0u, 0u, 0u);
+        else r.v[h] = e0 + h * GS < V ? __ldcg(reinterpret_cast<const float4*>(p + h * STEP)) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    }
+}
+template <bool BF16>
+__device__ __forceinline__ void raw_unpack(float (&x)[S_EPT], const Raw<BF16>& r) {
+    if constexpr (BF16) {
+#pragma unroll
+        for (int h = 0; h < Geo<true>::G; h++) {
+            const uint32_t u4[4] = {r.v[h].x, r.v[h].y, r.v[h].z, r.v[h].w};
+#pragma unroll
+            for (int u = 0; u < 4; u++) {   // a 16-bit shift widens bf16 to f32 exactly
+                x[h * 8 + 2 * u] = __uint_as_float(u4[u] << 16);
+                x[h * 8 + 2 * u + 1] = __uint_as_float(u4[u] & 0xffff0000u);
+            }
+        }
+    } else {
+#pragma unroll
+        for (int h = 0; h < Geo<false>::G; h++) { x[4 * h] = r.v[h].x; x[4 * h + 1] = r.v[h].y; x[4 * h + 2] = r.v[h].z; x[4 * h + 3] = r.v[h].w; }
+    }
+}
+
+// Raw logits of piece q -> the logits the chain sees: penalties (through the warp's staging area: the owner of a
+// history id is whichever lane holds it), grammar mask / end of row, EOS fix.  PASS 1 computes the penalised
+// values and leaves them where the counts were; PASS 2 takes them from there.
+template <bool BF16, bool MASK, bool TAIL, int PASS>
+__device__ __forceinline__ void fix_x(StreamSmem& sm, float (&x)[S_EPT], uint32_t q) {
+    constexpr int G = Geo<BF16>::G, GE = Geo<BF16>::GE, GS = Geo<BF16>::GS;
+    const PassArgs& pa = sm.pa;
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+    const uint32_t region = q * SNW + (uint32_t)w;
+    if ((pa.flags & PF_PEN) && ((sm.pmask[region >> 5] >> (region & 31u)) & 1u)) {   // warp-uniform
+        float* stg = sm.u.stage + w * S_REGION;
+        const uint32_t c0 = sm.rs[region], c1 = sm.rs[region + 1];
+#pragma unroll
+        for (int j = 0; j < S_EPT; j += 4)
+            *reinterpret_cast<float4*>(stg + (j / GE) * GS + lane * GE + (j % GE)) = make_float4(x[j], x[j + 1], x[j + 2], x[j + 3]);
+        __syncwarp();
+#pragma unroll 1
+        for (uint32_t i = c0 + lane; i < c1; i += 32) {
+            const uint32_t off = sm.pid[i];
+            if (PASS == 1) {
+                float v = stg[off];
+                if (pa.flags & PF_REP) v = v > 0.0f ? fdiv(v, pa.rep) : fmul(v, pa.rep);
+                if (pa.flags & PF_FP) {
+                    v = fsub(v, fmul(pa.freq, (float)sm.pval[i]));
+                    if (pa.flags & PF_PRES) v = fsub(v, pa.pres);
+                }
+                v = finite_f(v) ? v : -INFINITY;   // an overflowed penalty counts as masked
+                stg[off] = v;
+                sm.pval[i] = f2u(v);
+            } else {
+                stg[off] = u2f(sm.pval[i]);
+            }
+        }
+        __syncwarp();
+#pragma unroll
+        for (int j = 0; j < S_EPT; j += 4) {
+            const float4 v = *reinterpret_cast<const float4*>(stg + (j / GE) * GS + lane * GE + (j % GE));
+            x[j] = v.x; x[j + 1] = v.y; x[j + 2] = v.z; x[j + 3] = v.w;
+        }
+        __syncwarp();   // the next piece's staging must not overtake these reads
+    }
+    if (MASK || TAIL) {
+        const uint32_t e0 = q * S_PIECE + (uint32_t)w * S_REGION + (uint32_t)lane * GE;
+        const uint32_t mshift = ((uint32_t)lane * GE) & 31u;
+#pragma unroll
+        for (int h = 0; h < G; h++) {
+            const uint32_t idx = e0 + h * GS;
+            uint32_t bits = 0xffffffffu;
+            if (MASK) bits = (!TAIL || idx < pa.V) ? __ldg(pa.mw + (idx >> 5)) >> mshift : 0u;
+            else if (idx >= pa.V) bits = 0u;
+#pragma unroll
+            for (int c = 0; c < GE; c++)
+                if (!((bits >> c) & 1u)) x[h * GE + c] = -INFINITY;
+        }
+        if (MASK && q == pa.eos_piece && threadIdx.x == pa.eos_tid) {   // the EOS fix (engine.rs:1307-1312)
+#pragma unroll
+            for (int j = 0; j < S_EPT; j++)
+                if ((uint32_t)j == pa.eos_sub && !finite_f(x[j])) x[j] = 0.0f;
+        }
+    }
+}
+
+// pass 1 on one piece
+template <bool BF16, bool MASK, bool TAIL, bool STOCH>
+__device__ __forceinline__ void p1_piece(StreamSmem& sm, const Raw<BF16>& raw, uint32_t q, float& am, float& tmx, uint32_t& tqx) {
+    float x[S_EPT];
+    raw_unpack<BF16>(x, raw);
+    am = absmax_ept_nan(am, x);   // max |raw logit|, NaN-propagating: the sanity check
+    fix_x<BF16, MASK, TAIL, 1>(sm, x, q);
+    const float pm = max_ept(x);
+    if (pm >= tmx) { tmx = pm; tqx = q; }   // pieces arrive in descending order: an equal maximum here has the lower id
+    if (STOCH) {
+        const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+        const float sc = sm.pa.sc;
+        // one of the per-thread maxima that bound the top-k threshold
+        const uint32_t ci = (q % S_NCELL) * SNT + threadIdx.x;
+        if (pm > sm.cell[ci]) sm.cell[ci] = pm;
+        // plain sum of the numerators of the warp's 512 logits, relative to their own maximum
+        const uint32_t pb = f2u(pm);
+        const uint32_t wkey = __reduce_max_sync(FULL, pb ^ (((uint32_t)((int32_t)pb >> 31)) | 0x80000000u));   // monotone; -inf lowest
+        const float wm = u2f((wkey & 0x80000000u) ? (wkey & 0x7fffffffu) : ~wkey);
+        const float cc = -wm * sc;
+        float p0 = 0.0f, p1 = 0.0f, p2 = 0.0f, p3 = 0.0f;
+#pragma unroll
+        for (int j = 0; j < S_EPT; j += 4) {
+            p0 += ex2_approx_ftz(__fmaf_rn(x[j], sc, cc));
+            p1 += ex2_approx_ftz(__fmaf_rn(x[j + 1], sc, cc));
+            p2 += ex2_approx_ftz(__fmaf_rn(x[j + 2], sc, cc));
+            p3 += ex2_approx_ftz(__fmaf_rn(x[j + 3], sc, cc));
+        }
+        // summed over the warp in fixed point (a lane's sum is at most 16, and an estimate is all that is needed); an
+        // all-masked region has NaN here, which converts to 0
+        const uint32_t ws = __reduce_add_sync(FULL, __float2uint_rn(((p0 + p1) + (p2 + p3)) * 1048576.0f));
+        if (lane == 0) {
+            const uint32_t region = q * SNW + (uint32_t)w;
+            sm.reg_a[region] = wm; sm.reg_b[region] = (float)ws * (1.0f / 1048576.0f);
+        }
+    }
+}
+
+// This warp's share of the fold (the same value in all its lanes): a count of ulps of the binade cur_bb, folded into
+// accd whenever the binade changes.
+struct FoldAcc {
+    double accd;
+    unsigned long long cur_n;
+    uint32_t cur_bb;
+    __device__ __forceinline__ void flush() {
+        accd += (double)cur_n * ((double)u2f(cur_bb) * 1.1920928955078125e-07);   // units of that binade's ulp
+        cur_n = 0ull;
+    }
+};
+
+// pass 2 on one piece
+template <bool BF16, bool MASK, bool TAIL>
+__device__ __forceinline__ void p2_piece(StreamSmem& sm, const Raw<BF16>& raw, uint32_t q, FoldAcc& fa) {
+    constexpr int G = Geo<BF16>::G, GE = Geo<BF16>::GE;
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+    const float sc = sm.pa.sc, c_hi = sm.pa.c_hi, c_lo = sm.pa.c_lo, cut_f = sm.pa.cut_f;
+    float x[S_EPT];
+    raw_unpack<BF16>(x, raw);
+    fix_x<BF16, MASK, TAIL, 2>(sm, x, q);
+    if (max_ept(x) >= cut_f) {
+        const uint32_t e0 = q * S_PIECE + (uint32_t)w * S_REGION + (uint32_t)lane * GE;
+#pragma unroll
+        for (int j = 0; j < S_EPT; j++)
+            if (x[j] >= cut_f) {
+                const uint32_t at = atomicAdd(&sm.cand_n, 1u);
+                if (at < (uint32_t)F_MCAP) { sm.cand_id[at] = elem_id<BF16>(e0, j); sm.cand_x[at] = x[j]; }
+            }
+    }
+    const uint32_t region = q * SNW + (uint32_t)w;
+    if (TAIL && region >= sm.pa.n_regions) return;   // warp-uniform: past the end of the row
+#pragma unroll
+    if (BF16) {
+        // bf16 rows hold every value thousands of times, and a numerator that is off by 1e-6 in the same direction for
+        // all of them moves whole groups of additions across a rounding boundary: scale and constant as two floats
+        const float sc_lo = sm.pa.sc_lo;
+#pragma unroll
+        for (int j = 0; j < S_EPT; j++) x[j] = __fmaf_rn(x[j], sc, c_hi) + __fmaf_rn(x[j], sc_lo, c_lo);   // -inf stays -inf
+    } else {
+#pragma unroll
+        for (int j = 0; j < S_EPT; j++) x[j] = __fmaf_rn(x[j], sc, c_hi);   // -inf stays -inf
+        if (c_lo != 0.0f) {   // CTA-uniform: the constant needs its second float (cold rows, large maxima)
+#pragma unroll
+            for (int j = 0; j < S_EPT; j++) x[j] += c_lo;
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < S_EPT; j++) x[j] = ex2_approx_ftz(x[j]);   // -inf -> 0
+    const float base = sm.reg_a[region];
+    const uint32_t bb = f2u(base);
+    bool quick = bb != 0u;
+    if (quick) {
+        // every thread from the lower end of the binade the fold is in; four chains: the increments do not depend on
+        // the order
+        float ac[4] = {base, base, base, base};
+#pragma unroll
+        for (int j = 0; j < S_EPT / 4; j++) {
+#pragma unroll
+            for (int c = 0; c < 4; c++) ac[c] = fadd(ac[c], x[c * (S_EPT / 4) + j]);
+        }
+        quick = __all_sync(FULL, ((((f2u(ac[0]) ^ bb) | (f2u(ac[1]) ^ bb)) | ((f2u(ac[2]) ^ bb) | (f2u(ac[3]) ^ bb))) & 0xff800000u) == 0u);
+        if (quick) {
+            const uint32_t ws = __reduce_add_sync(FULL, ((f2u(ac[0]) - bb) + (f2u(ac[1]) - bb)) + ((f2u(ac[2]) - bb) + (f2u(ac[3]) - bb)));   // < 32 * 2^25
+            if (bb != fa.cur_bb) { fa.flush(); fa.cur_bb = bb; }
+            fa.cur_n += ws;
+        }
+    }
+    if (!quick) {
+        // the running value may leave its binade here (or the fold starts here): every 128-bit group from its own
+        // estimate of the running value, real additions, so that a crossing is reproduced
+        float stv[G], run = 0.0f;
+#pragma unroll
+        for (int h = 0; h < G; h++) {
+            float gs = 0.0f;
+#pragma unroll
+            for (int c = 0; c < GE; c++) gs += x[h * GE + c];
+            float inc = gs;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const float up = __shfl_up_sync(FULL, inc, o);
+                if (lane >= o) inc += up;
+            }
+            stv[h] = run + (inc - gs);
+            run += __shfl_sync(FULL, inc, 31);
+        }
+        const float R0 = sm.reg_b[region];
+        float tinc = 0.0f;
+#pragma unroll
+        for (int h = 0; h < G; h++) {
+            const float R = fadd(R0, stv[h]);
+            float a2 = R;
+#pragma unroll
+            for (int c = 0; c < GE; c++) a2 = fadd(a2, x[h * GE + c]);
+            tinc = fadd(tinc, fsub(a2, R));
+        }
+        double td = (double)tinc;
+#pragma unroll
+        for (int o = 16; o; o >>= 1) td += __shfl_xor_sync(FULL, td, o);
+        fa.accd += td;
+    }
+}
+
+// pass 1 over the whole pieces n_full-1 .. 0; the thread's results go to sm.t_*[tid]
+template <bool BF16, bool MASK, bool STOCH>
+__device__ __noinline__ void pass1_whole(StreamSmem& sm) {
+    constexpr int PB = S_PIECE * (BF16 ? 2 : 4);
+    const uint32_t lane_e0 = (threadIdx.x >> 5) * S_REGION + (threadIdx.x & 31) * Geo<BF16>::GE;
+    const uint32_t n = sm.pa.n_full;   // >= 1
+    const char* p = sm.pa.rowp + (size_t)lane_e0 * (BF16 ? 2 : 4) + (size_t)(n - 1u) * PB;
+    float am = 0.0f, tmx = -INFINITY;
+    uint32_t tqx = 0u;
+#pragma unroll 1
+    for (uint32_t q = n; q-- > 0u; p -= PB) {
+        Raw<BF16> b;
+        raw_load<BF16>(b, p);
+        p1_piece<BF16, MASK, false, STOCH>(sm, b, q, am, tmx, tqx);
+    }
+    sm.t_am[threadIdx.x] = am; sm.t_max[threadIdx.x] = tmx; sm.t_q[threadIdx.x] = tqx;
+}
+
+// pass 2 over the whole pieces 0 .. n_full-1; the warp's share of the fold is added to sm.wacc[w]
+template <bool BF16, bool MASK>
+__device__ __noinline__ void pass2_whole(StreamSmem& sm) {
+    constexpr int PB = S_PIECE * (BF16 ? 2 : 4);
+    const uint32_t lane_e0 = (threadIdx.x >> 5) * S_REGION + (threadIdx.x & 31) * Geo<BF16>::GE;
+    const uint32_t n = sm.pa.n_full;   // >= 1
+    const char* p = sm.pa.rowp + (size_t)lane_e0 * (BF16 ? 2 : 4);
+    FoldAcc fa;
+    fa.accd = 0.0; fa.cur_n = 0ull; fa.cur_bb = 0u;
+#pragma unroll 1
+    for (uint32_t q = 0u; q < n; q++, p += PB) {
+        Raw<BF16> b;
+        raw_load<BF16>(b, p);
+        p2_piece<BF16, MASK, false>(sm, b, q, fa);
+    }
+    fa.flush();
+    if ((threadIdx.x & 31) == 0) sm.wacc[threadIdx.x >> 5] += fa.accd;
+}
+
 template <bool BF16>
 __global__ void __launch_bounds__(SNT, 2) stream_row_kernel(const RowArgs a, const StreamLaunch sl) {
-    constexpr int G = Geo<BF16>::G, GE = Geo<BF16>::GE, GS = Geo<BF16>::GS;
+    constexpr int GE = Geo<BF16>::GE, GS = Geo<BF16>::GS;
+    constexpr int ESZ = BF16 ? 2 : 4;
     extern __shared__ __align__(16) unsigned char smem_raw[];
     StreamSmem& sm = *reinterpret_cast<StreamSmem*>(smem_raw);
     const uint32_t H = sl.hash_slots;
@@ -378,12 +642,10 @@ __global__ void __launch_bounds__(SNT, 2) stream_row_kernel(const RowArgs a, con
     uint32_t* hcnt = sm.u.hash + H;
     const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
     const uint32_t V = a.vocab;
-    const uint32_t n_pieces = (V + S_PIECE - 1) / S_PIECE;
+    const uint32_t n_full = V / S_PIECE;                        // whole pieces
+    const bool has_tail = (V % S_PIECE) != 0u;                  // plus a ragged one at the end of the row
     const uint32_t n_regions = (V + S_REGION - 1) / S_REGION;
-    const bool ragged = (V % S_PIECE) != 0;
     const uint32_t lane_e0 = (uint32_t)w * S_REGION + (uint32_t)lane * GE;   // first element of the thread inside a piece
-    const uint32_t mshift = ((uint32_t)lane * GE) & 31u;                     // its position inside a mask word
-    float* stg = sm.u.stage + w * S_REGION;
     if (tid < 32) sm.exp_tab[tid] = kExp2TableDev[tid];
     if (tid == 0)
 #pragma unroll 1
@@ -420,60 +682,55 @@ __global__ void __launch_bounds__(SNT, 2) stream_row_kernel(const RowArgs a, con
         }
         const float temp = ctl.temp;
         const uint32_t top_k = ctl.top_k, gflags = ctl.gflags, h0 = ctl.h0, nh = ctl.nh;
-        const uint32_t* mw = ctl.mw;
         const char* rowp = ctl.rowp;
         const float sc = ctl.sc;
         const bool greedy = temp < 1e-5f;
-        const bool has_mask = mw != nullptr;
+        const bool has_mask = ctl.mw != nullptr;
         const bool do_fp = !(fabsf(ctl.freq) < 1e-6f && fabsf(ctl.pres) < 1e-6f);
         const bool do_rep = ctl.rep != 1.0f;
         const bool pen = nh > 0 && (do_fp || do_rep);
-        // the EOS fix (engine.rs:1307-1312) touches one logit: where it sits in the piece / thread / register layout
-        const bool eos_on = has_mask && (gflags & 1u) && a.eos >= 0 && (uint32_t)a.eos < V;
-        uint32_t eos_piece = 0xffffffffu, eos_sub = 0u;
-        if (eos_on) {
-            const uint32_t r = (uint32_t)a.eos % S_PIECE, p = r % S_REGION;
-            const uint32_t e_tid = (r / S_REGION) * 32u + (p % GS) / GE;
-            if (e_tid == (uint32_t)tid) { eos_piece = (uint32_t)a.eos / S_PIECE; eos_sub = (p / GS) * GE + p % GE; }
-        }
-
-        // Two pieces per thread: the loads of piece s + 1 are out while piece s is worked on.  The first piece of a
-        // pass is requested by the caller, ahead of whatever it has to do first.
-        PieceBuf<BF16> buf0, buf1;
-        auto run_pass = [&](auto& body, bool rev) {
-            auto piece_of = [&](uint32_t st) { return rev ? n_pieces - 1u - st : st; };
-#pragma unroll 1
-            for (uint32_t st = 0;; st += 2) {
-                if (st + 1 < n_pieces) issue_loads<BF16>(buf1, rowp, piece_of(st + 1) * S_PIECE + lane_e0, V);
-                body(buf0, piece_of(st));
-                if (st + 1 >= n_pieces) break;
-                if (st + 2 < n_pieces) issue_loads<BF16>(buf0, rowp, piece_of(st + 2) * S_PIECE + lane_e0, V);
-                body(buf1, piece_of(st + 1));
-                if (st + 2 >= n_pieces) break;
+        if (tid == 0) {   // what the pass loops read
+            PassArgs& pa = sm.pa;
+            pa.rowp = rowp; pa.mw = ctl.mw; pa.sc = sc; pa.sc_lo = ctl.sc_lo; pa.c_hi = 0.0f; pa.c_lo = 0.0f; pa.cut_f = 0.0f;
+            pa.freq = ctl.freq; pa.pres = ctl.pres; pa.rep = ctl.rep;
+            pa.V = V; pa.n_full = n_full; pa.n_regions = n_regions;
+            pa.flags = (pen ? PF_PEN : 0u) | (do_rep ? PF_REP : 0u) | (do_fp ? PF_FP : 0u) | (fabsf(ctl.pres) > 1e-6f ? PF_PRES : 0u);
+            // the EOS fix touches one logit: where it sits in the piece / thread / register layout
+            pa.eos_piece = 0xffffffffu; pa.eos_tid = 0u; pa.eos_sub = 0u;
+            if (has_mask && (gflags & 1u) && a.eos >= 0 && (uint32_t)a.eos < V) {
+                const uint32_t r = (uint32_t)a.eos % S_PIECE, p = r % S_REGION;
+                pa.eos_piece = (uint32_t)a.eos / S_PIECE;
+                pa.eos_tid = (r / S_REGION) * 32u + (p % GS) / GE;
+                pa.eos_sub = (p / GS) * GE + p % GE;
             }
-        };
-        // first loads of pass 1 (the last piece of the row), requested before the history is indexed
-        issue_loads<BF16>(buf0, rowp, (n_pieces - 1) * S_PIECE + lane_e0, V);
+        }
 
         // ---- history: distinct ids with their counts, grouped by the warp region they fall into
         if (pen) {
             uint32_t* rcnt = reinterpret_cast<uint32_t*>(sm.reg_a);   // distinct ids per region, then the scatter cursor
+            // the first id of every thread is requested before the tables are cleared
+            const uint32_t hid0 = (uint32_t)tid < nh ? __ldg(a.hist_ids + h0 + tid) : S_NIL;
 #pragma unroll 1
             for (uint32_t s = tid; s < H; s += SNT) { hkey[s] = S_NIL; hcnt[s] = 0u; }
 #pragma unroll 1
             for (uint32_t r = tid; r < n_regions; r += SNT) rcnt[r] = 0u;
+#pragma unroll 1
+            for (uint32_t r = tid; r < (uint32_t)(S_MAX_REGIONS / 32); r += SNT) sm.pmask[r] = 0u;
             __syncthreads();
             int spilled = 0;
 #pragma unroll 1
             for (uint32_t j = tid; j < nh; j += SNT) {
-                const uint32_t id = __ldg(a.hist_ids + h0 + j);
+                const uint32_t id = j == (uint32_t)tid ? hid0 : __ldg(a.hist_ids + h0 + j);
                 if (id >= V) continue;   // engine.rs:1562
                 uint32_t s = (id * 2654435761u) & (H - 1u);
                 bool placed = false;
 #pragma unroll 1
                 for (int probe = 0; probe < 128; probe++) {
                     const uint32_t prev = atomicCAS(&hkey[s], S_NIL, id);
-                    if (prev == S_NIL) atomicAdd(&rcnt[id / S_REGION], 1u);
+                    if (prev == S_NIL) {
+                        atomicAdd(&rcnt[id / S_REGION], 1u);
+                        atomicOr(&sm.pmask[id / (S_REGION * 32)], 1u << ((id / S_REGION) & 31u));
+                    }
                     if (prev == S_NIL || prev == id) { atomicAdd(&hcnt[s], 1u); placed = true; break; }
                     s = (s + 1u) & (H - 1u);
                 }
@@ -511,147 +768,86 @@ __global__ void __launch_bounds__(SNT, 2) stream_row_kernel(const RowArgs a, con
                 sm.pid[at] = (uint16_t)(id % S_REGION);
                 sm.pval[at] = hcnt[s];
             }
-            __syncthreads();   // the table is dead from here on: its space is the staging area
         }
-        PGS_STICK(1);   // history indexed
-
-        // The processed logits of one piece in registers: penalties (through the warp's staging area: the owner
-        // of a history id is whichever lane holds it), grammar mask / end of row, EOS fix.  PASS 1 computes the
-        // penalised values and leaves them where the counts were; PASS 2 takes them from there.
-        auto make_x = [&](float (&x)[S_EPT], uint32_t q, auto pass_tag) {
-            constexpr int PASS = decltype(pass_tag)::value;
-            const uint32_t region = q * SNW + (uint32_t)w;
-            if (pen && region < n_regions) {
-                const uint32_t c0 = sm.rs[region], c1 = sm.rs[region + 1];
-                if (c1 > c0) {   // warp-uniform
-#pragma unroll
-                    for (int j = 0; j < S_EPT; j += 4)
-                        *reinterpret_cast<float4*>(stg + (j / GE) * GS + lane * GE + (j % GE)) = make_float4(x[j], x[j + 1], x[j + 2], x[j + 3]);
-                    __syncwarp();
-#pragma unroll 1
-                    for (uint32_t i = c0 + lane; i < c1; i += 32) {
-                        const uint32_t off = sm.pid[i];
-                        if (PASS == 1) {
-                            float v = stg[off];
-                            if (do_rep) v = v > 0.0f ? fdiv(v, ctl.rep) : fmul(v, ctl.rep);
-                            if (do_fp) {
-                                v = fsub(v, fmul(ctl.freq, (float)sm.pval[i]));
-                                if (fabsf(ctl.pres) > 1e-6f) v = fsub(v, ctl.pres);
-                            }
-                            v = finite_f(v) ? v : -INFINITY;   // an overflowed penalty counts as masked
-                            stg[off] = v;
-                            sm.pval[i] = f2u(v);
-                        } else {
-                            stg[off] = u2f(sm.pval[i]);
-                        }
-                    }
-                    __syncwarp();
-#pragma unroll
-                    for (int j = 0; j < S_EPT; j += 4) {
-                        const float4 v = *reinterpret_cast<const float4*>(stg + (j / GE) * GS + lane * GE + (j % GE));
-                        x[j] = v.x; x[j + 1] = v.y; x[j + 2] = v.z; x[j + 3] = v.w;
-                    }
-                    __syncwarp();   // the next piece's staging must not overtake these reads
-                }
-            }
-            if (has_mask || (ragged && q == n_pieces - 1)) {   // warp-uniform
-#pragma unroll
-                for (int h = 0; h < G; h++) {
-                    const uint32_t idx = q * S_PIECE + lane_e0 + h * GS;
-                    const uint32_t bits = idx < V ? (has_mask ? __ldg(mw + (idx >> 5)) >> mshift : 0xffffffffu) : 0u;
-#pragma unroll
-                    for (int c = 0; c < GE; c++)
-                        if (!((bits >> c) & 1u)) x[h * GE + c] = -INFINITY;
-                }
-                if (q == eos_piece) {
-#pragma unroll
-                    for (int j = 0; j < S_EPT; j++)
-                        if ((uint32_t)j == eos_sub && !finite_f(x[j])) x[j] = 0.0f;
-                }
-            }
-        };
-
-        // ================================================================ pass 1 (HBM, last piece first)
 #pragma unroll
         for (int c = 0; c < S_NCELL; c++) sm.cell[c * SNT + tid] = -INFINITY;
-        float am = 0.0f;   // max |raw logit|, NaN-propagating: the sanity check
-        auto p1_body = [&](const PieceBuf<BF16>& b, uint32_t q) {
-            float x[S_EPT];
-            unpack<BF16>(x, b);
-            am = absmax_ept_nan(am, x);
-            make_x(x, q, std::integral_constant<int, 1>());
-            const float pm = max_ept(x);
-            const uint32_t ci = (q % S_NCELL) * SNT + tid;
-            const float cur = sm.cell[ci];
-            // pieces arrive in descending order, so an equal maximum here has the lower id
-            if (pm > cur || (pm == cur && pm > -INFINITY)) {
-                int j0 = 0;
-#pragma unroll
-                for (int j = S_EPT - 1; j >= 0; j--) if (x[j] == pm) j0 = j;
-                sm.cell[ci] = pm;
-                sm.celli[ci] = elem_id<BF16>(q * S_PIECE + lane_e0, j0);
-            }
-            if (!greedy) {
-                // plain sum of the numerators of the warp's 1024 logits, relative to their own maximum
-                const uint32_t wkey = __reduce_max_sync(FULL, order_key(pm));
-                float wm = -INFINITY, ps = 0.0f;
-                if (wkey) {
-                    wm = key_to_float(wkey);
-                    const float cc = -wm * sc;
-                    float p0 = 0.0f, p1 = 0.0f, p2 = 0.0f, p3 = 0.0f;
-#pragma unroll
-                    for (int j = 0; j < S_EPT; j += 4) {
-                        p0 += ex2_approx_ftz(__fmaf_rn(x[j], sc, cc));
-                        p1 += ex2_approx_ftz(__fmaf_rn(x[j + 1], sc, cc));
-                        p2 += ex2_approx_ftz(__fmaf_rn(x[j + 2], sc, cc));
-                        p3 += ex2_approx_ftz(__fmaf_rn(x[j + 3], sc, cc));
-                    }
-                    ps = (p0 + p1) + (p2 + p3);
-#pragma unroll
-                    for (int o = 16; o; o >>= 1) ps += __shfl_xor_sync(FULL, ps, o);
-                }
-                const uint32_t region = q * SNW + (uint32_t)w;
-                if (lane == 0 && region < n_regions) { sm.reg_a[region] = wm; sm.reg_b[region] = ps; }
-            }
-        };
-        run_pass(p1_body, true);
-        // the first loads of pass 2 go out before the reductions
-        if (!greedy) issue_loads<BF16>(buf0, rowp, lane_e0, V);
+        __syncthreads();   // the id -> count table is dead from here on (its space is the staging area); PassArgs are set
+        PGS_STICK(1);   // history indexed
+
+        // ================================================================ pass 1 (HBM, last piece first)
+        float am = 0.0f;            // max |raw logit|
+        float tmx = -INFINITY;      // the thread's running maximum, and the lowest piece that holds it
+        uint32_t tqx = 0u;
+        if (has_tail) {
+            Raw<BF16> raw;
+            raw_load_tail<BF16>(raw, rowp + ((size_t)n_full * S_PIECE + lane_e0) * ESZ, n_full * S_PIECE + lane_e0, V);
+            if (has_mask) { if (greedy) p1_piece<BF16, true, true, false>(sm, raw, n_full, am, tmx, tqx); else p1_piece<BF16, true, true, true>(sm, raw, n_full, am, tmx, tqx); }
+            else { if (greedy) p1_piece<BF16, false, true, false>(sm, raw, n_full, am, tmx, tqx); else p1_piece<BF16, false, true, true>(sm, raw, n_full, am, tmx, tqx); }
+        }
+        if (n_full > 0u) {
+            if (has_mask) { if (greedy) pass1_whole<BF16, true, false>(sm); else pass1_whole<BF16, true, true>(sm); }
+            else { if (greedy) pass1_whole<BF16, false, false>(sm); else pass1_whole<BF16, false, true>(sm); }
+            am = absmax3_nan(am, sm.t_am[tid], 0.0f);
+            if (sm.t_max[tid] >= tmx) { tmx = sm.t_max[tid]; tqx = sm.t_q[tid]; }   // the whole pieces come before the ragged one
+        }
         PGS_STICK(2);   // pass 1
 
-        // ---- row maximum / argmax (lowest id), sanity, and the material for the top-k bound
+        // ---- row maximum, sanity, and the material for the top-k bound
         {
-            uint32_t bkey = 0u, bidx = 0xffffffffu, lo = 0xffffffffu, fin = 0u;
+            uint32_t lo = 0xffffffffu, fin = 0u;
+            if (!greedy) {
 #pragma unroll
-            for (int c = 0; c < S_NCELL; c++) {
-                const uint32_t k = order_key(sm.cell[c * SNT + tid]);
-                if (!k) continue;
-                const uint32_t i = sm.celli[c * SNT + tid];
-                if (k > bkey || (k == bkey && i < bidx)) { bkey = k; bidx = i; }
-                lo = umin(lo, k);
-                fin++;
+                for (int c = 0; c < S_NCELL; c++) {
+                    const uint32_t k = order_key(sm.cell[c * SNT + tid]);
+                    if (!k) continue;
+                    lo = umin(lo, k);
+                    fin++;
+                }
             }
-            const uint32_t wk = __reduce_max_sync(FULL, bkey);
-            const uint32_t wi = __reduce_min_sync(FULL, bkey == wk ? bidx : 0xffffffffu);
+            const uint32_t wk = __reduce_max_sync(FULL, order_key(tmx));
             const uint32_t wlo = __reduce_min_sync(FULL, lo);
             const uint32_t wfin = __reduce_add_sync(FULL, fin);
             const uint32_t wbad = __any_sync(FULL, !(am < INFINITY)) ? 1u : 0u;
-            if (lane == 0) { sm.red_key[w] = wk; sm.red_idx[w] = wi; sm.red_lo[w] = wlo; sm.red_fin[w] = wfin; sm.red_flag[w] = wbad; }
+            if (lane == 0) { sm.red_key[w] = wk; sm.red_lo[w] = wlo; sm.red_fin[w] = wfin; sm.red_flag[w] = wbad; sm.wacc[w] = 0.0; }
 #pragma unroll
             for (int u = 0; u < S_BPT; u++) sm.hist[u * SNT + tid] = 0u;
-            if (tid == 0) { sm.cand_n = 0u; sm.sel_bucket = 0u; }
+            if (tid == 0) { sm.cand_n = 0u; sm.sel_bucket = 0u; sm.amax = 0xffffffffu; }
         }
         __syncthreads();
         const uint32_t gkey = __reduce_max_sync(FULL, lane < SNW ? sm.red_key[lane] : 0u);
-        const uint32_t amax_raw = __reduce_min_sync(FULL, (lane < SNW && sm.red_key[lane] == gkey) ? sm.red_idx[lane] : 0xffffffffu);
         const uint32_t lo_key = __reduce_min_sync(FULL, lane < SNW ? sm.red_lo[lane] : 0xffffffffu);
         const uint32_t n_fin = __reduce_add_sync(FULL, lane < SNW ? sm.red_fin[lane] : 0u);
         const bool nonfinite = __any_sync(FULL, lane < SNW && sm.red_flag[lane] != 0u);
         const bool any = gkey != 0u;
         const float m = any ? key_to_float(gkey) : -INFINITY;
-        const uint32_t amax = any ? amax_raw : 0u;
         const int status = any ? ROW_OK : ROW_EMPTY;
         if (writer) atomicAdd(sl.p1_done, 1u);
+        // ---- argmax: the lowest id that holds the maximum.  Every thread whose own maximum is the row's looks at
+        // the lowest of its pieces that holds it once more (the penalised values are in place by now).
+        if (any && !nonfinite && !(gflags & 2u)) {
+            // (the piece code is a warp-wide operation, so a warp goes through the pieces its lanes ask for one by
+            // one; nearly always that is a single piece of a single warp)
+            unsigned pending = __ballot_sync(FULL, order_key(tmx) == gkey);
+#pragma unroll 1
+            while (pending) {   // warp-uniform
+                const uint32_t q = __shfl_sync(FULL, tqx, __ffs(pending) - 1);
+                Raw<BF16> raw;
+                raw_load_tail<BF16>(raw, rowp + ((size_t)q * S_PIECE + lane_e0) * ESZ, q * S_PIECE + lane_e0, V);
+                float x[S_EPT];
+                raw_unpack<BF16>(x, raw);
+                if (has_mask) fix_x<BF16, true, true, 2>(sm, x, q); else fix_x<BF16, false, true, 2>(sm, x, q);
+                const bool mine = ((pending >> lane) & 1u) && tqx == q;
+                if (mine) {
+                    int j0 = 0;
+#pragma unroll
+                    for (int j = S_EPT - 1; j >= 0; j--) if (x[j] == m) j0 = j;
+                    atomicMin(&sm.amax, elem_id<BF16>(q * S_PIECE + lane_e0, j0));
+                }
+                pending &= ~__ballot_sync(FULL, mine);
+            }
+            __syncthreads();
+        }
+        const uint32_t amax = any ? sm.amax : 0u;
         if (nonfinite || (gflags & 2u) || greedy || !any) {
             if (writer) {
                 if (nonfinite) {
@@ -706,11 +902,19 @@ __global__ void __launch_bounds__(SNT, 2) stream_row_kernel(const RowArgs a, con
             const float delta = 4.8e-7f * (fabsf(m - bound) + 4.0f * t) + 4.8e-7f * (fabsf(bound) + fabsf(m));
             cut = bound - delta;
         }
-        const float cut_f = fmaxf(cut, -3.4e38f);   // masked entries (-inf) are never candidates
+        // numerator = 2^(x * sc + c): c = -m * sc as c_hi + c_lo (c_lo only when it matters: the numerators then keep
+        // the reference's scale to 1e-7, which the fold needs where many logits are equal); what is left of c scales
+        // the final sum
+        const double c_d = -(double)m * (BF16 ? (double)sc + (double)ctl.sc_lo : (double)sc);
+        const float c_hi = (float)c_d;
+        float c_lo = (float)(c_d - (double)c_hi);
+        if (!BF16 && fabsf(c_lo) < 1e-7f) c_lo = 0.0f;
+        const double c_rest = c_d - (double)c_hi - (double)c_lo;
+        if (tid == 0) { sm.pa.c_hi = c_hi; sm.pa.c_lo = c_lo; sm.pa.cut_f = fmaxf(cut, -3.4e38f); }   // masked entries (-inf) are never candidates
 
         // ---- where the fold stands at every warp region.  The plain sums overestimate the fold's running value
         // by up to a few 1e-4 (the small terms it drops), so a region takes the quick path only if the whole
-        // interval [start * (1 - 2^-9), end * (1 + 2^-9)] lies inside one binade.
+        // interval [start * (1 - slack), end * (1 + slack)], slack >= 2^-9, lies inside one binade.
         {
             float carry = 0.0f;
 #pragma unroll 1
@@ -721,99 +925,39 @@ __global__ void __launch_bounds__(SNT, 2) stream_row_kernel(const RowArgs a, con
                 float tot;
                 const float pre = carry + sblock_excl_scan_f32(P, &tot, sm.scan_f);
                 if (r < n_regions) {
-                    const float lo_e = pre * 0.998046875f, hi_e = (pre + P) * 1.001953125f;
+                    // (the plain sums carry the rounding of their exponents' constant: 2^-24 of |max * sc|)
+                    const float slack = 0.001953125f + 1e-7f * fabsf(m * sc);
+                    const float lo_e = pre * (1.0f - slack), hi_e = (pre + P) * (1.0f + slack);
                     const uint32_t kb = f2u(lo_e) & 0x7f800000u;
                     const bool quick = kb != 0u && kb == (f2u(hi_e) & 0x7f800000u);
                     sm.reg_a[r] = quick ? u2f(kb) : 0.0f;
                     sm.reg_b[r] = pre;
                 }
                 carry += tot;
-                __syncthreads();   // scan_f is reused by the next round
+                __syncthreads();   // scan_f is reused by the next round; after the last one the table and PassArgs are complete
             }
         }
         PGS_STICK(3);   // reductions, bound, fold table
 
         // ================================================================ pass 2 (L2, first piece first)
-        // numerator = 2^(x * sc + c): c = -m * sc split into c_hi + c_lo; c_lo scales the final sum
-        const double c_d = -(double)m * (double)sc;
-        const float c_hi = (float)c_d;
-        const double c_lo = c_d - (double)c_hi;
-        double accd = 0.0;   // this warp's share of the fold (the same value in all its lanes)
-        auto p2_body = [&](const PieceBuf<BF16>& b, uint32_t q) {
-            float x[S_EPT];
-            unpack<BF16>(x, b);
-            make_x(x, q, std::integral_constant<int, 2>());
-            if (max_ept(x) >= cut_f) {
-#pragma unroll
-                for (int j = 0; j < S_EPT; j++)
-                    if (x[j] >= cut_f) {
-                        const uint32_t at = atomicAdd(&sm.cand_n, 1u);
-                        if (at < (uint32_t)F_MCAP) { sm.cand_id[at] = elem_id<BF16>(q * S_PIECE + lane_e0, j); sm.cand_x[at] = x[j]; }
-                    }
-            }
-            const uint32_t region = q * SNW + (uint32_t)w;
-            if (region >= n_regions) return;   // warp-uniform: past the end of the row
-#pragma unroll
-            for (int j = 0; j < S_EPT; j++) x[j] = ex2_approx_ftz(__fmaf_rn(x[j], sc, c_hi));   // -inf -> 0
-            const float base = sm.reg_a[region];
-            bool quick = base != 0.0f;
-            if (quick) {
-                // every thread from the lower end of the binade the fold is in
-                float ac[4] = {base, base, base, base};   // four chains: the increments do not depend on the order
-#pragma unroll
-                for (int j = 0; j < S_EPT / 4; j++) {
-#pragma unroll
-                    for (int c = 0; c < 4; c++) ac[c] = fadd(ac[c], x[c * (S_EPT / 4) + j]);
-                }
-                const uint32_t bb = f2u(base);
-                quick = __all_sync(FULL, ((((f2u(ac[0]) ^ bb) | (f2u(ac[1]) ^ bb)) | ((f2u(ac[2]) ^ bb) | (f2u(ac[3]) ^ bb))) & 0xff800000u) == 0u);
-                if (quick) {
-                    const uint32_t ws = __reduce_add_sync(FULL, ((f2u(ac[0]) - bb) + (f2u(ac[1]) - bb)) + ((f2u(ac[2]) - bb) + (f2u(ac[3]) - bb)));   // < 32 * 2^25
-                    accd += (double)ws * ((double)base * 1.1920928955078125e-07);        // units of the binade's ulp
-                }
-            }
-            if (!quick) {
-                // the running value may leave its binade here (or the fold starts here): every 128-bit group from
-                // its own estimate of the running value, real additions, so that a crossing is reproduced
-                float stv[G], run = 0.0f;
-#pragma unroll
-                for (int h = 0; h < G; h++) {
-                    float gs = 0.0f;
-#pragma unroll
-                    for (int c = 0; c < GE; c++) gs += x[h * GE + c];
-                    float inc = gs;
-#pragma unroll
-                    for (int o = 1; o < 32; o <<= 1) {
-                        const float up = __shfl_up_sync(FULL, inc, o);
-                        if (lane >= o) inc += up;
-                    }
-                    stv[h] = run + (inc - gs);
-                    run += __shfl_sync(FULL, inc, 31);
-                }
-                const float R0 = sm.reg_b[region];
-                float tinc = 0.0f;
-#pragma unroll
-                for (int h = 0; h < G; h++) {
-                    const float R = fadd(R0, stv[h]);
-                    float a2 = R;
-#pragma unroll
-                    for (int c = 0; c < GE; c++) a2 = fadd(a2, x[h * GE + c]);
-                    tinc = fadd(tinc, fsub(a2, R));
-                }
-                double td = (double)tinc;
-#pragma unroll
-                for (int o = 16; o; o >>= 1) td += __shfl_xor_sync(FULL, td, o);
-                accd += td;
-            }
-        };
-        run_pass(p2_body, false);
-        if (lane == 0) sm.wacc[w] = accd;
+        if (has_tail) {
+            Raw<BF16> raw;
+            raw_load_tail<BF16>(raw, rowp + ((size_t)n_full * S_PIECE + lane_e0) * ESZ, n_full * S_PIECE + lane_e0, V);
+            FoldAcc fa;
+            fa.accd = 0.0; fa.cur_n = 0ull; fa.cur_bb = 0u;
+            if (has_mask) p2_piece<BF16, true, true>(sm, raw, n_full, fa); else p2_piece<BF16, false, true>(sm, raw, n_full, fa);
+            fa.flush();
+            if (lane == 0) sm.wacc[w] += fa.accd;
+        }
+        if (n_full > 0u) {
+            if (has_mask) pass2_whole<BF16, true>(sm); else pass2_whole<BF16, false>(sm);
+        }
         __syncthreads();   // the candidate list and the warps' shares are complete
         PGS_STICK(4);   // pass 2
         double s_d = lane < SNW ? sm.wacc[lane] : 0.0;
 #pragma unroll
         for (int o = 16; o; o >>= 1) s_d += __shfl_xor_sync(FULL, s_d, o);
-        const float S = (float)(s_d * (1.0 + c_lo * 0.6931471805599453));
+        const float S = (float)(s_d * exp2(c_rest));
         const uint32_t n_cand = sm.cand_n;
         if (n_cand > (uint32_t)F_MCAP) {   // CTA-uniform
             if (writer) { sl.work_rows[atomicAdd(sl.work_count, 1u)] = row; sl.recs[row].kind = 0; }
