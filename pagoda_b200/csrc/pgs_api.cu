@@ -22,14 +22,6 @@ cudaError_t configure_general();
 cudaError_t launch_general(const RowArgs& a, uint32_t grid, cudaStream_t stream);
 size_t general_smem_bytes();
 
-size_t fused_smem_bytes(uint32_t slice_len, uint32_t cluster);
-uint32_t fused_threads();
-uint32_t fused_piece_bytes();
-cudaError_t fused_ctas_per_sm(size_t smem, int* out);
-cudaError_t configure_fused(size_t max_smem);
-cudaError_t fused_max_clusters(uint32_t cluster, size_t smem, int* out);
-cudaError_t launch_fused(const RowArgs& a, const FusedLaunch& fl, uint32_t n_clusters, size_t smem,
-                         cudaStream_t stream);
 size_t stream_smem_bytes();
 cudaError_t configure_stream();
 cudaError_t stream_ctas_per_sm(int* out);
@@ -51,8 +43,7 @@ cudaError_t launch_tp_merge(const TpArgs& a, const TpOut& o, cudaStream_t stream
 cudaError_t launch_draft_accept(const uint32_t* row_argmax, const uint32_t* draft, uint32_t sequences,
                                 uint32_t positions, uint32_t* accepted, uint32_t* next, cudaStream_t stream);
 cudaError_t configure_finish();
-cudaError_t launch_finish(const RowArgs& a, const FusedLaunch& fl, cudaStream_t stream);
-cudaError_t launch_finish_small(const RowArgs& a, const FusedLaunch& fl, cudaStream_t stream);
+cudaError_t launch_finish(const RowArgs& a, const Handoff& ho, cudaStream_t stream);
 }  // namespace pgs
 
 static thread_local char g_create_error[256] = "";
@@ -61,8 +52,8 @@ struct pgs_handle {
     int device = 0;
     int sm_count = 0;
     cudaStream_t stream = nullptr;
-    cudaStream_t side = nullptr;      // runs the rarely needed passes beside the main one
-    cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
+    cudaStream_t last_stream = nullptr;   // stream of the step before: steps of one handle share its scratch and must not overlap
+    cudaEvent_t ev_step = nullptr;
     uint32_t max_rows = 0, max_vocab = 0, max_history = 0;
     uint32_t slots = 0, vocab_pad = 0, sort_pad = 0, hash_cap = 0;
     // scratch slots
@@ -81,19 +72,17 @@ struct pgs_handle {
     unsigned char* aux_host = nullptr;   // pinned
     unsigned char* aux_dev = nullptr;
     size_t aux_bytes = 0;
-    // fused cluster kernel: launch shape for the last vocabulary size seen, and its work list
-    size_t smem_optin = 0;
-    uint32_t fused_rows = 0, fused_vocab = 0, fused_cluster = 0, fused_slice = 0, fused_chunk = 0, fused_clusters = 0;
-    size_t fused_smem = 0;
+    // rows the row kernel hands on: to the general kernel (work list), to the finish kernel (long candidate lists)
     uint32_t* work_rows = nullptr;
     uint32_t* work_count = nullptr;   // [2]
     uint32_t* tp_done = nullptr;      // CTAs finished in the current peer-store push
+    uint32_t* long_rows = nullptr;
+    uint32_t* long_count = nullptr;   // [2]
     pgs::RowRec* recs = nullptr;      // [max_rows]
     uint32_t* cand_id = nullptr;      // [max_rows x F_MCAP]
     float* cand_x = nullptr;
     int exact = 0;
     // streaming row kernel: id -> count slots, shared memory and CTAs per SM, the gate's counter
-    int use_cluster = 0;              // PGS_PATH=cluster: the cluster kernel instead (kept for comparison)
     uint32_t stream_hash = 0, stream_cohort = 0;
     size_t stream_smem = 0;
     int stream_ctas = 0;
@@ -159,11 +148,9 @@ static int destroy_impl(pgs_handle* h) {
     cudaFree(h->sx); cudaFree(h->sl_id); cudaFree(h->sl_p); cudaFree(h->sl_key);
     cudaFree(h->sh_key); cudaFree(h->sh_cnt); cudaFree(h->tables_dev);
     cudaFree(h->logits_stage); cudaFree(h->aux_dev); cudaFree(h->work_rows); cudaFree(h->work_count); cudaFree(h->tp_done); cudaFree(h->prof);
-    cudaFree(h->recs); cudaFree(h->cand_id); cudaFree(h->cand_x); cudaFree(h->p1_done); cudaFree(h->faulted);
+    cudaFree(h->recs); cudaFree(h->cand_id); cudaFree(h->cand_x); cudaFree(h->p1_done); cudaFree(h->faulted); cudaFree(h->long_rows); cudaFree(h->long_count);
     if (h->aux_host) cudaFreeHost(h->aux_host);
-    if (h->side) { cudaStreamSynchronize(h->side); cudaStreamDestroy(h->side); }
-    if (h->ev_fork) cudaEventDestroy(h->ev_fork);
-    if (h->ev_join) cudaEventDestroy(h->ev_join);
+    if (h->ev_step) cudaEventDestroy(h->ev_step);
     if (h->stream) cudaStreamDestroy(h->stream);
     delete h;
     return PGS_OK;
@@ -196,12 +183,9 @@ extern "C" int pgs_create(int device, uint32_t max_rows, uint32_t max_vocab, uin
                         device, prop.major, prop.minor);
         h->sm_count = prop.multiProcessorCount;
         PGS_CUDA(nullptr, cudaStreamCreateWithFlags(&h->stream, cudaStreamNonBlocking));
-        PGS_CUDA(nullptr, cudaStreamCreateWithFlags(&h->side, cudaStreamNonBlocking));
-        PGS_CUDA(nullptr, cudaEventCreateWithFlags(&h->ev_fork, cudaEventDisableTiming));
-        PGS_CUDA(nullptr, cudaEventCreateWithFlags(&h->ev_join, cudaEventDisableTiming));
+        PGS_CUDA(nullptr, cudaEventCreateWithFlags(&h->ev_step, cudaEventDisableTiming));
+        h->last_stream = h->stream;
         PGS_CUDA(nullptr, pgs::configure_general());
-        h->smem_optin = prop.sharedMemPerBlockOptin;
-        PGS_CUDA(nullptr, pgs::configure_fused(h->smem_optin));
         PGS_CUDA(nullptr, pgs::configure_finish());
         PGS_CUDA(nullptr, pgs::configure_tp());
         PGS_CUDA(nullptr, pgs::configure_score());
@@ -210,6 +194,9 @@ extern "C" int pgs_create(int device, uint32_t max_rows, uint32_t max_vocab, uin
         PGS_CUDA(nullptr, cudaMalloc(&h->cand_id, (size_t)max_rows * pgs::F_MCAP * sizeof(uint32_t)));
         PGS_CUDA(nullptr, cudaMalloc(&h->cand_x, (size_t)max_rows * pgs::F_MCAP * sizeof(float)));
         PGS_CUDA(nullptr, cudaMalloc(&h->work_rows, (size_t)max_rows * sizeof(uint32_t)));
+        PGS_CUDA(nullptr, cudaMalloc(&h->long_rows, (size_t)max_rows * sizeof(uint32_t)));
+        PGS_CUDA(nullptr, cudaMalloc(&h->long_count, 2 * sizeof(uint32_t)));
+        PGS_CUDA(nullptr, cudaMemsetAsync(h->long_count, 0, 2 * sizeof(uint32_t), h->stream));
         PGS_CUDA(nullptr, cudaMalloc(&h->work_count, 2 * sizeof(uint32_t)));
         PGS_CUDA(nullptr, cudaMemsetAsync(h->work_count, 0, 2 * sizeof(uint32_t), h->stream));
         PGS_CUDA(nullptr, cudaMalloc(&h->tp_done, sizeof(uint32_t)));
@@ -228,7 +215,6 @@ extern "C" int pgs_create(int device, uint32_t max_rows, uint32_t max_vocab, uin
         // about an SM count keeps pass 2 in L2 but leaves half the threads of every SM waiting at the gate)
         h->stream_cohort = 0xffffffffu;
         if (const char* ev = getenv("PGS_COHORT")) { if (atoi(ev) > 0) h->stream_cohort = (uint32_t)atoi(ev); }
-        if (const char* ev = getenv("PGS_PATH")) h->use_cluster = strcmp(ev, "cluster") == 0;
         if (const char* ev = getenv("PGS_EXACT")) h->exact = atoi(ev);
         if (const char* ev = getenv("PGS_PROFILE")) {
             if (atoi(ev)) {
@@ -279,7 +265,7 @@ extern "C" int pgs_get_counters(const pgs_handle* h, pgs_counters* out) {
     DeviceGuard g(h->device);
     unsigned long long f = 0;
     cudaError_t e = cudaStreamSynchronize(h->stream);
-    if (e == cudaSuccess) e = cudaStreamSynchronize(h->side);
+    if (e == cudaSuccess && h->last_stream != h->stream) e = cudaStreamSynchronize(h->last_stream);
     if (e == cudaSuccess) e = cudaMemcpy(&f, h->faulted, sizeof f, cudaMemcpyDeviceToHost);
     if (e != cudaSuccess) { cudaGetLastError(); return PGS_ERR_CUDA; }
     out->rows_faulted = f;
@@ -341,100 +327,44 @@ extern "C" int pgs_mask_table_free(pgs_handle* h, int32_t table_id) {
 
 namespace {
 
-// Launch shape of the fused kernel for a vocabulary size and a batch size.  A row lives in the shared memory
-// of one cluster from its copy to its last fold, so the rows in flight are bounded by shared memory: smaller
-// clusters keep more rows in flight but give every thread more logits.  The cluster size is the one with the
-// smallest estimated batch time: waves of resident clusters times a row time made of a fixed part (barriers,
-// exchanges, reductions: measured about 23 k cycles) and a streaming part (about 0.26 cycles per logit of a
-// slice).  Returns false when no cluster of up to 8 CTAs can hold the row.
-bool fused_shape(pgs_handle* h, uint32_t vocab, uint32_t rows) {
-    if (h->fused_vocab == vocab && h->fused_rows == rows) return h->fused_clusters > 0;
-    h->fused_vocab = vocab;
-    h->fused_rows = rows;
-    h->fused_clusters = 0;
-    double best_cost = 0.0;
-    for (uint32_t c = 1; c <= (uint32_t)pgs::F_MAXC; c++) {
-        const uint32_t slice = (((vocab + c - 1) / c) + 31u) & ~31u;
-        const size_t smem = pgs::fused_smem_bytes(slice, c);
-        if (smem > h->smem_optin || (slice * 4u + pgs::fused_piece_bytes() - 1u) / pgs::fused_piece_bytes() > 8u) continue;
-        int n = 0;
-        if (pgs::fused_max_clusters(c, smem, &n) != cudaSuccess || n <= 0) { cudaGetLastError(); continue; }
-        const uint32_t waves = (rows + (uint32_t)n - 1) / (uint32_t)n;
-        const double cost = (double)waves * (23000.0 + 0.26 * (double)slice);
-        if (h->fused_clusters && cost >= best_cost) continue;
-        best_cost = cost;
-        // consecutive logits per thread in the sum passes: 4 * odd, so that the 128-bit shared-memory
-        // accesses of a warp (stride = chunk words) fall into distinct bank groups
-        const uint32_t nt = pgs::fused_threads();
-        uint32_t groups = ((slice + nt - 1u) / nt + 3u) / 4u;
-        if ((groups & 1u) == 0) groups += 1;
-        h->fused_cluster = c; h->fused_slice = slice; h->fused_chunk = groups * 4u; h->fused_smem = smem;
-        h->fused_clusters = (uint32_t)n;
-    }
-    return h->fused_clusters > 0;
-}
-
-// One step: the fused cluster kernel serves every row it can hold and lists the others, which
-// the general kernel then processes.  In exact mode every row takes the general kernel.
+// One step: the streaming row kernel serves every row it can and lists the others, which the general kernel then
+// processes; rows with long candidate lists are finished by the finish kernel.  In exact mode every row takes the
+// general kernel.
 int launch_step(pgs_handle* h, pgs::RowArgs& a, cudaStream_t stream) {
     const uint32_t rows = a.rows;
     const uint32_t grid = rows < h->slots ? rows : h->slots;
     a.faulted = h->faulted;
-    const bool stream_fits = a.vocab <= (uint32_t)pgs::S_MAX_VOCAB;
-    if (h->exact || (h->use_cluster ? !fused_shape(h, a.vocab, rows) : !stream_fits)) {
+    // Every step of a handle uses the same scratch, lists and counters: a step on another stream than the one before
+    // waits for that one to finish on the device.
+    if (stream != h->last_stream) {
+        PGS_CUDA(h, cudaEventRecord(h->ev_step, h->last_stream));
+        PGS_CUDA(h, cudaStreamWaitEvent(stream, h->ev_step, 0));
+        h->last_stream = stream;
+    }
+    if (h->exact || a.vocab > (uint32_t)pgs::S_MAX_VOCAB) {
         PGS_CUDA(h, pgs::launch_general(a, grid, stream));
         h->counters.kernel_launches += 1;
         return PGS_OK;
     }
-    if (!h->use_cluster) {
-        pgs::StreamLaunch sl;
-        sl.hash_slots = h->stream_hash; sl.cohort = h->stream_cohort;
-        sl.done_base = h->done_total; sl.gate_polls = 1u << 16;   // x 200 ns: gives up after about 13 ms
-        sl.p1_done = h->p1_done;
-        sl.work_rows = h->work_rows; sl.work_count = h->work_count;
-        sl.recs = h->recs; sl.cand_id = h->cand_id; sl.cand_x = h->cand_x;
-        sl.prof = h->prof;
-        const uint32_t resident = (uint32_t)h->stream_ctas * (uint32_t)h->sm_count;
-        PGS_CUDA(h, pgs::launch_stream(a, sl, rows < resident ? rows : resident, stream));
-        h->done_total += rows;
-        // rows with a long candidate list and the rows on the work list are usually none: those two passes run
-        // beside each other on a side stream
-        pgs::FusedLaunch fl;
-        fl.cluster = 1; fl.slice_len = 0; fl.chunk = 0;
-        fl.work_rows = h->work_rows; fl.work_count = h->work_count; fl.prof = nullptr;
-        fl.recs = h->recs; fl.cand_id = h->cand_id; fl.cand_x = h->cand_x;
-        PGS_CUDA(h, pgs::launch_finish(a, fl, stream));
-        pgs::RowArgs wl = a;
-        wl.work_rows = h->work_rows;
-        wl.work_count = h->work_count;
-        PGS_CUDA(h, pgs::launch_general(wl, grid < 32u ? grid : 32u, stream));
-        h->counters.kernel_launches += 3;
-        return PGS_OK;
-    }
-    pgs::FusedLaunch fl;
-    fl.cluster = h->fused_cluster; fl.slice_len = h->fused_slice; fl.chunk = h->fused_chunk;
-    fl.work_rows = h->work_rows; fl.work_count = h->work_count;
-    fl.prof = h->prof;
-    fl.recs = h->recs; fl.cand_id = h->cand_id; fl.cand_x = h->cand_x;
-    // as many clusters as are resident at once, evened out so that every cluster serves the same number of rows
-    const uint32_t waves = (rows + h->fused_clusters - 1) / h->fused_clusters;
-    const uint32_t nc = (rows + waves - 1) / waves;
-    PGS_CUDA(h, pgs::launch_fused(a, fl, nc, h->fused_smem, stream));
-    // Three independent consumers of the fused kernel's output: rows with a short candidate list
-    // (the common case) finish on the caller's stream; rows with a long list and the rows on the
-    // work list are usually none, so those two passes run beside it on a side stream.
-    PGS_CUDA(h, cudaEventRecord(h->ev_fork, stream));
-    PGS_CUDA(h, cudaStreamWaitEvent(h->side, h->ev_fork, 0));
-    PGS_CUDA(h, pgs::launch_finish_small(a, fl, stream));
-    PGS_CUDA(h, pgs::launch_finish(a, fl, h->side));
+    pgs::StreamLaunch sl;
+    sl.hash_slots = h->stream_hash; sl.cohort = h->stream_cohort;
+    sl.done_base = h->done_total; sl.gate_polls = 1u << 16;   // x 200 ns: gives up after about 13 ms
+    sl.p1_done = h->p1_done;
+    sl.work_rows = h->work_rows; sl.work_count = h->work_count;
+    sl.ho.recs = h->recs; sl.ho.cand_id = h->cand_id; sl.ho.cand_x = h->cand_x;
+    sl.ho.long_rows = h->long_rows; sl.ho.long_count = h->long_count;
+    sl.prof = h->prof;
+    const uint32_t resident = (uint32_t)h->stream_ctas * (uint32_t)h->sm_count;
+    PGS_CUDA(h, pgs::launch_stream(a, sl, rows < resident ? rows : resident, stream));
+    h->done_total += rows;
+    // Both lists are usually empty.  The two passes are set up while the row kernel still runs (programmatic stream
+    // serialization) and return at once when they find nothing listed.
+    PGS_CUDA(h, pgs::launch_finish(a, sl.ho, stream));
     pgs::RowArgs wl = a;
     wl.work_rows = h->work_rows;
     wl.work_count = h->work_count;
-    // the listed rows are few or none: a small grid keeps the empty pass short
-    PGS_CUDA(h, pgs::launch_general(wl, grid < 32u ? grid : 32u, h->side));
-    PGS_CUDA(h, cudaEventRecord(h->ev_join, h->side));
-    PGS_CUDA(h, cudaStreamWaitEvent(stream, h->ev_join, 0));
-    h->counters.kernel_launches += 4;
+    PGS_CUDA(h, pgs::launch_general(wl, grid < 32u ? grid : 32u, stream));
+    h->counters.kernel_launches += 3;
     return PGS_OK;
 }
 
@@ -606,7 +536,7 @@ int run_batch(pgs_handle* h, const pgs_batch_desc* d, cudaStream_t stream, bool 
 
 }  // namespace
 
-// Phase timers of the fused kernel (clock ticks, [ctas x 16]); only with PGS_PROFILE=1.
+// Phase timers of the row kernel (clock ticks, [ctas x 16]); only with PGS_PROFILE=1.
 extern "C" PGS_API int pgs_debug_read_profile(pgs_handle* h, long long* out, uint32_t n_ctas) {
     if (!h || !h->prof || n_ctas > 1024) return PGS_ERR_INVALID;
     DeviceGuard g(h->device);

@@ -48,6 +48,7 @@ __global__ void __launch_bounds__(NT, 1) general_row_kernel(const RowArgs a) {
     const int tid = threadIdx.x;
     const uint32_t V = a.vocab;
     const uint32_t slot = blockIdx.x;
+    if (a.work_rows) cudaGridDependencySynchronize();   // the work-list pass is launched ahead of the end of the kernel that fills the list
     const uint32_t n_work = a.work_rows ? *a.work_count : a.rows;
     if (n_work == 0u) return;   // the usual case of the work-list pass: nothing listed, nothing to reset
     if (tid < 32) sm.exp_tab[tid] = kExp2TableDev[tid];
@@ -304,8 +305,21 @@ cudaError_t configure_general() {
 }
 
 cudaError_t launch_general(const RowArgs& a, uint32_t grid, cudaStream_t stream) {
-    general_row_kernel<<<grid, NT, sizeof(GeneralSmem), stream>>>(a);
-    return cudaGetLastError();
+    if (!a.work_rows) {
+        general_row_kernel<<<grid, NT, sizeof(GeneralSmem), stream>>>(a);
+        return cudaGetLastError();
+    }
+    // the work-list pass: programmatic stream serialization, see cudaGridDependencySynchronize() in the kernel
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid, 1, 1);
+    cfg.blockDim = dim3(NT, 1, 1);
+    cfg.dynamicSmemBytes = sizeof(GeneralSmem);
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr; cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, general_row_kernel, a);
 }
 
 }  // namespace pgs

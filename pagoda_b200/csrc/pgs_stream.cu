@@ -111,6 +111,7 @@ struct StreamSmem {
     // careful way) and the estimate of the running value at its start.  While the history is indexed, reg_a
     // counts the distinct history ids per region.
     float reg_a[S_MAX_REGIONS], reg_b[S_MAX_REGIONS];
+    float reg_t[S_MAX_REGIONS];      // a logit below this adds exactly nothing to the fold in this region
     // distinct history ids grouped by region: those of region r are the entries rs[r] .. rs[r + 1]
     uint16_t rs[S_MAX_REGIONS + 2];
     uint32_t pmask[S_MAX_REGIONS / 32];   // bit r: region r holds history ids
@@ -125,6 +126,8 @@ struct StreamSmem {
         FinishScratch fin;
     } u;
 };
+
+static_assert(sizeof(StreamSmem) <= 113 * 1024, "two CTAs per SM");
 
 #define PGS_STICK(slot)                                             \
     do {                                                            \
@@ -512,7 +515,8 @@ __device__ __forceinline__ void p2_piece(StreamSmem& sm, const Raw<BF16>& raw, u
     float x[S_EPT];
     raw_unpack<BF16>(x, raw);
     fix_x<BF16, MASK, TAIL, 2>(sm, x, q);
-    if (max_ept(x) >= cut_f) {
+    const float pm = max_ept(x);
+    if (pm >= cut_f) {
         const uint32_t e0 = q * S_PIECE + (uint32_t)w * S_REGION + (uint32_t)lane * GE;
 #pragma unroll
         for (int j = 0; j < S_EPT; j++)
@@ -523,7 +527,8 @@ __device__ __forceinline__ void p2_piece(StreamSmem& sm, const Raw<BF16>& raw, u
     }
     const uint32_t region = q * SNW + (uint32_t)w;
     if (TAIL && region >= sm.pa.n_regions) return;   // warp-uniform: past the end of the row
-#pragma unroll
+    // nothing here is large enough to move the running value: the usual case once the sum has grown
+    if (__all_sync(FULL, pm < sm.reg_t[region])) return;
     if (BF16) {
         // bf16 rows hold every value thousands of times, and a numerator that is off by 1e-6 in the same direction for
         // all of them moves whole groups of additions across a rounding boundary: scale and constant as two floats
@@ -542,22 +547,19 @@ __device__ __forceinline__ void p2_piece(StreamSmem& sm, const Raw<BF16>& raw, u
     for (int j = 0; j < S_EPT; j++) x[j] = ex2_approx_ftz(x[j]);   // -inf -> 0
     const float base = sm.reg_a[region];
     const uint32_t bb = f2u(base);
-    bool quick = bb != 0u;
+    const bool quick = bb != 0u;
     if (quick) {
-        // every thread from the lower end of the binade the fold is in; four chains: the increments do not depend on
-        // the order
+        // every thread from the lower end of the binade the fold is in (the table guarantees that nobody leaves it);
+        // four chains: the increments do not depend on the order
         float ac[4] = {base, base, base, base};
 #pragma unroll
         for (int j = 0; j < S_EPT / 4; j++) {
 #pragma unroll
             for (int c = 0; c < 4; c++) ac[c] = fadd(ac[c], x[c * (S_EPT / 4) + j]);
         }
-        quick = __all_sync(FULL, ((((f2u(ac[0]) ^ bb) | (f2u(ac[1]) ^ bb)) | ((f2u(ac[2]) ^ bb) | (f2u(ac[3]) ^ bb))) & 0xff800000u) == 0u);
-        if (quick) {
-            const uint32_t ws = __reduce_add_sync(FULL, ((f2u(ac[0]) - bb) + (f2u(ac[1]) - bb)) + ((f2u(ac[2]) - bb) + (f2u(ac[3]) - bb)));   // < 32 * 2^25
-            if (bb != fa.cur_bb) { fa.flush(); fa.cur_bb = bb; }
-            fa.cur_n += ws;
-        }
+        const uint32_t ws = __reduce_add_sync(FULL, ((f2u(ac[0]) - bb) + (f2u(ac[1]) - bb)) + ((f2u(ac[2]) - bb) + (f2u(ac[3]) - bb)));   // < 32 * 2^25
+        if (bb != fa.cur_bb) { fa.flush(); fa.cur_bb = bb; }
+        fa.cur_n += ws;
     }
     if (!quick) {
         // the running value may leave its binade here (or the fold starts here): every 128-bit group from its own
@@ -675,7 +677,6 @@ __global__ void __launch_bounds__(SNT, 2) stream_row_kernel(const RowArgs a, con
             if (writer) {
                 if (ctl.kind == 1u) { a.token[row] = 0; a.status[row] = ROW_BAD_PARAM; if (a.drew) a.drew[row] = 0; }
                 else sl.work_rows[atomicAdd(sl.work_count, 1u)] = row;
-                sl.recs[row].kind = 0;
                 atomicAdd(sl.p1_done, 1u);
             }
             continue;
@@ -738,7 +739,7 @@ __global__ void __launch_bounds__(SNT, 2) stream_row_kernel(const RowArgs a, con
             }
             spilled = __syncthreads_or(spilled);
             if (spilled) {   // CTA-uniform
-                if (writer) { sl.work_rows[atomicAdd(sl.work_count, 1u)] = row; sl.recs[row].kind = 0; atomicAdd(sl.p1_done, 1u); }
+                if (writer) { sl.work_rows[atomicAdd(sl.work_count, 1u)] = row; atomicAdd(sl.p1_done, 1u); }
                 continue;
             }
             // exclusive scan of the counts in region order; thread t owns the regions t * rpt ..
@@ -864,7 +865,6 @@ __global__ void __launch_bounds__(SNT, 2) stream_row_kernel(const RowArgs a, con
                     if (a.total) a.total[row] = 0.0f;
                     if (a.n_kept) a.n_kept[row] = 0u;
                 }
-                sl.recs[row].kind = 0;
             }
             PGS_STICK(3);
             continue;
@@ -905,7 +905,8 @@ __global__ void __launch_bounds__(SNT, 2) stream_row_kernel(const RowArgs a, con
         // numerator = 2^(x * sc + c): c = -m * sc as c_hi + c_lo (c_lo only when it matters: the numerators then keep
         // the reference's scale to 1e-7, which the fold needs where many logits are equal); what is left of c scales
         // the final sum
-        const double c_d = -(double)m * (BF16 ? (double)sc + (double)ctl.sc_lo : (double)sc);
+        const double scale_d = BF16 ? (double)sc + (double)ctl.sc_lo : (double)sc;
+        const double c_d = -(double)m * scale_d;
         const float c_hi = (float)c_d;
         float c_lo = (float)(c_d - (double)c_hi);
         if (!BF16 && fabsf(c_lo) < 1e-7f) c_lo = 0.0f;
@@ -929,9 +930,21 @@ __global__ void __launch_bounds__(SNT, 2) stream_row_kernel(const RowArgs a, con
                     const float slack = 0.001953125f + 1e-7f * fabsf(m * sc);
                     const float lo_e = pre * (1.0f - slack), hi_e = (pre + P) * (1.0f + slack);
                     const uint32_t kb = f2u(lo_e) & 0x7f800000u;
-                    const bool quick = kb != 0u && kb == (f2u(hi_e) & 0x7f800000u);
+                    // quick: one binade for the whole region, and the region's own sum stays below that binade's
+                    // lower end, so that no thread's additions from there can leave the binade either
+                    const bool quick = kb != 0u && kb == (f2u(hi_e) & 0x7f800000u) && P * (1.0f + slack) < 0.999f * u2f(kb);
                     sm.reg_a[r] = quick ? u2f(kb) : 0.0f;
                     sm.reg_b[r] = pre;
+                    // A numerator below half an ulp of the running value leaves it unchanged, and lo_e never exceeds the
+                    // running value: a logit with x * scale + c < exponent(lo_e) - 24 (less a margin for the hardware
+                    // exp2) adds exactly nothing.  In units of logits:
+                    float thr = -INFINITY;
+                    if (kb != 0u) {
+                        const double lim = (double)((int)(kb >> 23) - 127 - 24) - 0.02;
+                        thr = (float)((lim - c_d) / scale_d);
+                        thr -= 4e-7f * fabsf(thr) + 1e-30f;
+                    }
+                    sm.reg_t[r] = thr;
                 }
                 carry += tot;
                 __syncthreads();   // scan_f is reused by the next round; after the last one the table and PassArgs are complete
@@ -960,23 +973,23 @@ __global__ void __launch_bounds__(SNT, 2) stream_row_kernel(const RowArgs a, con
         const float S = (float)(s_d * exp2(c_rest));
         const uint32_t n_cand = sm.cand_n;
         if (n_cand > (uint32_t)F_MCAP) {   // CTA-uniform
-            if (writer) { sl.work_rows[atomicAdd(sl.work_count, 1u)] = row; sl.recs[row].kind = 0; }
+            if (writer) { sl.work_rows[atomicAdd(sl.work_count, 1u)] = row; }
             continue;
         }
         if (n_cand <= (uint32_t)S_FCAP) {
-            if (writer) sl.recs[row].kind = 0;
             sfinish_row(sm, a, row, n_cand, m, t, S, top_k, ctl.top_p, ctl.u01, amax, status);
         } else {
             // long lists: the finish kernel takes the row from here
 #pragma unroll 1
             for (uint32_t j = tid; j < n_cand; j += SNT) {
-                sl.cand_id[(size_t)row * F_MCAP + j] = sm.cand_id[j];
-                sl.cand_x[(size_t)row * F_MCAP + j] = sm.cand_x[j];
+                sl.ho.cand_id[(size_t)row * F_MCAP + j] = sm.cand_id[j];
+                sl.ho.cand_x[(size_t)row * F_MCAP + j] = sm.cand_x[j];
             }
             if (writer) {
-                RowRec& rec = sl.recs[row];
-                rec.kind = 1; rec.n_cand = n_cand; rec.amax = amax; rec.status = status;
-                rec.m = m; rec.t = t; rec.n_parts = 1; rec.part[0] = (double)S;
+                RowRec& rec = sl.ho.recs[row];
+                rec.n_cand = n_cand; rec.amax = amax; rec.status = status; rec.m = m; rec.t = t; rec.S = S;
+                __threadfence();   // the record and the candidates before the list entry
+                sl.ho.long_rows[atomicAdd(sl.ho.long_count, 1u)] = row;
             }
         }
         PGS_STICK(5);   // finish

@@ -19,9 +19,7 @@ struct StreamLaunch {
     uint32_t* p1_done;          // rows that have finished their first pass, counted over all launches
     uint32_t* work_rows;        // rows handed to the general kernel
     uint32_t* work_count;
-    RowRec* recs;               // [rows] hand-off of rows with long candidate lists to the finish kernel
-    uint32_t* cand_id;          // [rows x F_MCAP]
-    float* cand_x;              // [rows x F_MCAP]
+    Handoff ho;                 // rows with long candidate lists go to the finish kernel
     long long* prof;            // optional phase timers, [gridDim.x x 16]
 };
 
