@@ -41,7 +41,7 @@ enum pgs_error {
     PGS_ERR_CUDA = -2,     /* a CUDA call failed */
     PGS_ERR_NOMEM = -3,
     PGS_ERR_LIMIT = -4,    /* rows / vocab / history beyond what pgs_create was sized for */
-    PGS_ERR_TIMEOUT = -5   /* a bounded device-side wait ran out (peer exchange) */
+    PGS_ERR_TIMEOUT = -5   /* a bounded device-side wait ran out (peer exchange; pgs_tp_exchange_status) */
 };
 
 /* Per-row outcome.  Maps onto the reference's per-request finish reasons so that a
@@ -52,7 +52,7 @@ enum pgs_row_status {
     PGS_ROW_DEAD = 2,      /* grammar state is a dead end (engine.rs:1299-1303) -> Stop, no token */
     PGS_ROW_EMPTY = 3,     /* nothing finite left after masking; token 0, as sampler.rs:59-70 returns */
     PGS_ROW_BAD_PARAM = 4, /* non-finite parameter, bad mask table/state, history too long */
-    PGS_ROW_LOAD_TIMEOUT = 5 /* a bounded wait for an asynchronous copy ran out; nothing sampled */
+    PGS_ROW_LOAD_TIMEOUT = 5 /* a bounded wait for another shard's records ran out; nothing sampled */
 };
 
 enum pgs_mem { PGS_MEM_DEVICE = 0, PGS_MEM_HOST = 1 };
@@ -153,7 +153,12 @@ typedef struct pgs_batch_desc {
  * readable by the host. */
 PGS_API int pgs_sample_batch(pgs_handle *h, const pgs_batch_desc *desc);
 /* Same, enqueued on `cuda_stream` (a cudaStream_t; NULL = the handle's own stream)
- * without waiting.  Every array must be device memory. */
+ * without waiting.  Every array must be device memory.
+ * Steps of one handle share its per-row working storage, so the library orders them on the GPU:
+ * when a step is enqueued on a different stream than the handle's previous step, the new stream
+ * first waits (cudaStreamWaitEvent) for the previous step's last kernel.  The caller only has to
+ * keep to one host thread per handle at a time, and to keep a stream alive until the steps it
+ * carried have finished.  Steps on different handles are independent. */
 PGS_API int pgs_sample_batch_async(pgs_handle *h, const pgs_batch_desc *desc, void *cuda_stream);
 
 /* Allocation-free variant of pgs_sample_batch_async.  It has no counterpart in the reference
@@ -166,8 +171,10 @@ PGS_API int pgs_sample_batch_async(pgs_handle *h, const pgs_batch_desc *desc, vo
  * descriptor in device memory; beyond them the call fails with PGS_ERR_LIMIT / PGS_ERR_INVALID
  * and a message in pgs_static_last_error().  Results are those of the general (bit-exact)
  * kernel.  All calls on one device share the array: calls whose kernels may overlap on the GPU
- * (different streams or host threads) race and must be serialised by the caller.  The first
- * call on each device does a one-time set-up and should be made outside any stream capture.
+ * (different streams or host threads) race and must be serialised by the caller.  hist_offsets
+ * and hist_ids must be given together or not at all.  The first call on each device does a
+ * one-time set-up (guarded by a mutex, so two threads may make it at once) and should be made
+ * outside any stream capture.
  * Only enqueues work on `cuda_stream` (a cudaStream_t; NULL = the default stream). */
 PGS_API int pgs_sample_batch_static(int device_ordinal, const pgs_batch_desc *desc, void *cuda_stream);
 PGS_API const char *pgs_static_last_error(void);
@@ -197,8 +204,22 @@ typedef struct pgs_tp_desc {
     uint64_t row_stride;          /* elements between rows of the shard */
     const float *logits;          /* [rows x row_stride] f32, this rank's columns */
     const float *temperature;     /* per row; NULL = greedy */
-    const float *top_p;           /* per row; NULL = 1.0 */
-    const float *uniform;         /* per row */
+    const float *top_p;           /* per row; NULL = 1.0 (merge) */
+    const float *uniform;         /* per row (merge) */
+    const uint32_t *top_k;        /* per row, 0 = off; NULL = off (merge).  Must not exceed cand: the row gets
+                                   * PGS_ROW_BAD_PARAM otherwise.  Ties at the k-th probability survive as in
+                                   * sampler.rs:116-128, as far as the records hold them. */
+    /* The rest of the chain of engine.rs:1296-1313, applied by the emitting half to its own columns before
+     * anything else, exactly as pgs_sample_batch applies it to whole rows.  Ids are GLOBAL token ids. */
+    const float *frequency_penalty, *presence_penalty, *repetition_penalty;   /* per row; NULL = off */
+    const uint32_t *hist_offsets; /* [rows + 1] CSR; NULL = no history */
+    const uint32_t *hist_ids;     /* generated ids of every row, global */
+    const int32_t *mask_table;    /* per row: table id or -1; NULL = no grammar.  A table used here holds THIS
+                                   * SHARD's bits: bit j of a state's words is column shard_rank * vocab/n_shards + j
+                                   * (words_per_state * 32 >= vocab / n_shards). */
+    const int32_t *mask_state;    /* per row: state inside the table */
+    int32_t eos_token_id;         /* global id; -1 = none.  Only the shard that owns it applies the EOS fix. */
+    int32_t reserved0;
 } pgs_tp_desc;
 PGS_API size_t pgs_tp_record_bytes(uint32_t cand);
 PGS_API int pgs_tp_partial(pgs_handle *h, const pgs_tp_desc *desc, void *records_out, void *cuda_stream);
@@ -212,8 +233,9 @@ PGS_API int pgs_tp_merge(pgs_handle *h, const pgs_tp_desc *desc, const void *rec
  * kernel stores each finished record into slot [shard_rank][row] of EVERY rank's gather buffer -- peer
  * memory over NVLink, mapped by the caller (CUDA IPC or symmetric memory) -- and, when its last row is out,
  * raises flag [shard_rank] in every rank's flag array to `epoch` (system-scope release).  pgs_tp_merge_wait
- * is pgs_tp_merge preceded by a bounded wait (about one second) for all n_shards flags of this rank to
- * reach `epoch`; when a shard never answers, the rows get status PGS_ROW_LOAD_TIMEOUT instead of a hang.
+ * is pgs_tp_merge preceded by a bounded wait (about one second unless pgs_set_wait_limit says otherwise) for all
+ * n_shards flags of this rank to reach `epoch`; when a shard never answers, the rows get status
+ * PGS_ROW_LOAD_TIMEOUT instead of a hang, and the next pgs_tp_exchange_status returns PGS_ERR_TIMEOUT.
  *   peer_records[p]  rank p's gather buffer, [n_shards][rows][pgs_tp_record_bytes(cand)], p = 0..n_shards-1
  *   peer_flags[p]    rank p's flag array, [n_shards] uint32, zero before the first step
  *   epoch            1, 2, 3, ... one per step, the same on every rank
@@ -233,6 +255,13 @@ PGS_API int pgs_tp_partial_push(pgs_handle *h, const pgs_tp_desc *desc, void *co
                                 uint32_t *const *peer_flags, uint32_t epoch, void *cuda_stream);
 PGS_API int pgs_tp_merge_wait(pgs_handle *h, const pgs_tp_desc *desc, const void *records_all,
                               const uint32_t *flags, uint32_t epoch, const pgs_tp_out *out, void *cuda_stream);
+/* Bound of pgs_tp_merge_wait's wait, in polls of about half a microsecond each (default 2^21: about a second).
+ * A serving loop that would rather drop a step than stall sets it to a few thousand. */
+PGS_API int pgs_set_wait_limit(pgs_handle *h, uint32_t polls);
+/* Failure detection for the exchange: waits for the stream of the last pgs_tp_merge_wait and returns
+ * PGS_ERR_TIMEOUT when rows gave up waiting since the previous call of this function (a peer that never
+ * answered), PGS_OK otherwise.  The handle stays usable either way. */
+PGS_API int pgs_tp_exchange_status(pgs_handle *h);
 
 /* Draft verification over per-position argmax ids (pagoda-hf/src/qwen3_5.rs:663-755 produces
  * them; the reference leaves the accept rule open): accepted[s] = length of the longest prefix

@@ -39,7 +39,8 @@ class RowParams(C.Structure):
 class RowOut(C.Structure):
     _fields_ = [("token", C.c_uint32), ("status", C.c_int32), ("drew", C.c_int32),
                 ("argmax", C.c_uint32), ("row_max", C.c_float), ("sumexp", C.c_float),
-                ("total", C.c_float), ("n_kept", C.c_uint32), ("margin", C.c_float)]
+                ("total", C.c_float), ("n_kept", C.c_uint32), ("margin", C.c_float),
+                ("margin_k", C.c_float), ("margin_p", C.c_float), ("margin_cdf", C.c_float)]
 
 
 class Batch(C.Structure):
@@ -61,7 +62,7 @@ class TpOut(C.Structure):
 
 ROW_OUT_DTYPE = np.dtype([("token", "<u4"), ("status", "<i4"), ("drew", "<i4"), ("argmax", "<u4"),
                           ("row_max", "<f4"), ("sumexp", "<f4"), ("total", "<f4"), ("n_kept", "<u4"),
-                          ("margin", "<f4")])
+                          ("margin", "<f4"), ("margin_k", "<f4"), ("margin_p", "<f4"), ("margin_cdf", "<f4")])
 
 _lib = None
 
@@ -93,8 +94,8 @@ def lib():
         L.pgo_sample_row.argtypes = [fp, C.c_size_t, C.POINTER(RowParams), C.POINTER(RowOut), fp, fp]
         L.pgo_sample_batch.argtypes = [C.POINTER(Batch), C.c_void_p, C.c_int]
         L.pgo_bf16_to_f32.argtypes = [C.POINTER(C.c_uint16), fp, C.c_size_t]
-        L.pgo_tp_sample_row.argtypes = [fp, C.c_size_t, C.c_uint32, C.c_uint32, C.c_float, C.c_float,
-                                        C.c_float, C.POINTER(TpOut)]
+        L.pgo_tp_sample_row.argtypes = [fp, C.c_size_t, C.c_uint32, C.c_uint32, C.POINTER(RowParams),
+                                        C.POINTER(TpOut)]
         L.pgo_draft_accept.restype = C.c_uint32
         L.pgo_draft_accept.argtypes = [u32p, u32p, C.c_uint32, u32p]
         L.pgo_regex_new.restype = C.c_void_p
@@ -236,10 +237,8 @@ def bf16_to_f32(bits):
     return out
 
 
-def sample_row(logits, temperature=0.0, top_k=0, top_p=1.0, freq=0.0, pres=0.0, rep=1.0, history=None,
-               mask_words=None, dead=False, complete=False, eos_id=-1, uniform=0.0, want_probs=False):
-    logits = _f32(logits)
-    n = logits.size
+def _row_params(temperature=0.0, top_k=0, top_p=1.0, freq=0.0, pres=0.0, rep=1.0, history=None,
+                mask_words=None, dead=False, complete=False, eos_id=-1, uniform=0.0):
     p = RowParams()
     p.temperature, p.top_p, p.top_k = temperature, top_p, top_k
     p.freq, p.pres, p.rep = freq, pres, rep
@@ -248,6 +247,13 @@ def sample_row(logits, temperature=0.0, top_k=0, top_p=1.0, freq=0.0, pres=0.0, 
     mw = np.ascontiguousarray(mask_words, dtype=np.uint32) if mask_words is not None else None
     p.mask_words = _ptr(mw, C.c_uint32)
     p.grammar_dead, p.grammar_complete, p.eos_id, p.uniform = int(dead), int(complete), eos_id, uniform
+    return p, (hist, mw)
+
+
+def sample_row(logits, want_probs=False, **params):
+    logits = _f32(logits)
+    n = logits.size
+    p, _keep = _row_params(**params)
     out = RowOut()
     work = np.empty(2 * n, dtype=np.float32)
     probs = np.empty(n, dtype=np.float32) if want_probs else None
@@ -301,11 +307,12 @@ def sample_batch(logits, temperature=None, top_k=None, top_p=None, freq=None, pr
     return out
 
 
-def tp_sample_row(logits, n_shards, cand, temperature, top_p, u):
+def tp_sample_row(logits, n_shards, cand, temperature, top_p, u, **chain):
+    """`chain`: top_k, freq, pres, rep, history, mask_words (whole row), dead, complete, eos_id."""
     logits = _f32(logits)
+    p, _keep = _row_params(temperature=temperature, top_p=top_p, uniform=u, **chain)
     out = TpOut()
-    lib().pgo_tp_sample_row(_ptr(logits, C.c_float), logits.size, n_shards, cand, temperature, top_p, u,
-                            C.byref(out))
+    lib().pgo_tp_sample_row(_ptr(logits, C.c_float), logits.size, n_shards, cand, C.byref(p), C.byref(out))
     return out
 
 

@@ -265,7 +265,7 @@ void pgo_sample_row(const float *logits_in, size_t n, const pgo_row_params *p, p
                     float *work, float *probs_out) {
     float *logits = work, *probs = work + n;
     memset(out, 0, sizeof *out);
-    out->margin = 1.0f;
+    out->margin = out->margin_k = out->margin_p = out->margin_cdf = 1.0f;
     out->row_max = -INFINITY;
     /* :1292-1295 sanity before anything else */
     if (!pgo_logits_sane(logits_in, n, n)) {
@@ -319,7 +319,7 @@ void pgo_sample_row(const float *logits_in, size_t n, const pgo_row_params *p, p
         /* margin: gap to the next smaller distinct probability */
         size_t j = p->top_k;
         while (j < n && sorted[j] == threshold) j++;
-        if (j < n && threshold > 0.0f) out->margin = fminf(out->margin, rel_gap(threshold, sorted[j]));
+        if (j < n && threshold > 0.0f) out->margin_k = rel_gap(threshold, sorted[j]);
         free(sorted);
         for (size_t i = 0; i < n; i++)
             if (probs[i] < threshold) probs[i] = 0.0f;
@@ -327,10 +327,7 @@ void pgo_sample_row(const float *logits_in, size_t n, const pgo_row_params *p, p
     if (!(p->top_p >= 1.0f - PGO_EPS)) {
         float before, at;
         top_p_core(probs, n, p->top_p, &before, &at);
-        if (at >= 0.0f) {
-            out->margin = fminf(out->margin, rel_gap(at, p->top_p));
-            out->margin = fminf(out->margin, rel_gap(before, p->top_p));
-        }
+        if (at >= 0.0f) out->margin_p = fminf(rel_gap(at, p->top_p), rel_gap(before, p->top_p));
     }
     for (size_t i = 0; i < n; i++) out->n_kept += probs[i] > 0.0f;
     {   /* sample_categorical with margin bookkeeping */
@@ -350,14 +347,11 @@ void pgo_sample_row(const float *logits_in, size_t n, const pgo_row_params *p, p
                 if (u < acc) { tok = (uint32_t)i; hit = 1; break; }
             }
             out->token = tok;
-            if (hit) {
-                out->margin = fminf(out->margin, fabsf(acc - u) / total);
-                out->margin = fminf(out->margin, fabsf(u - prev) / total + (prev == 0.0f ? 1.0f : 0.0f));
-            } else {
-                out->margin = fminf(out->margin, fabsf(u - acc) / total);
-            }
+            if (hit) out->margin_cdf = fminf(fabsf(acc - u) / total, fabsf(u - prev) / total + (prev == 0.0f ? 1.0f : 0.0f));
+            else out->margin_cdf = fabsf(u - acc) / total;
         }
     }
+    out->margin = fminf(out->margin_k, fminf(out->margin_p, out->margin_cdf));
     if (probs_out) memcpy(probs_out, probs, n * sizeof(float));
 }
 
@@ -419,50 +413,88 @@ static int cmp_cand(const void *a, const void *b) {
     return (x->id > y->id) - (x->id < y->id);
 }
 
-void pgo_tp_sample_row(const float *logits, size_t n, uint32_t n_shards, uint32_t cand,
-                       float temperature, float top_p, float u, pgo_tp_out *out) {
+void pgo_tp_sample_row(const float *logits_in, size_t n, uint32_t n_shards, uint32_t cand,
+                       const pgo_row_params *p, pgo_tp_out *out) {
     memset(out, 0, sizeof *out);
     out->margin = 1.0f;
-    if (!pgo_logits_sane(logits, n, n)) { out->status = PGO_ROW_NONFINITE; return; }
+    out->gmax = -INFINITY;
+    /* the chain in front of the sampler is that of pgo_sample_row: every step touches one logit at a
+     * time, so running it on the whole row equals running it shard by shard */
+    if (p->top_k > cand) { out->status = PGO_ROW_BAD_PARAM; return; }
+    if (!pgo_logits_sane(logits_in, n, n)) { out->status = PGO_ROW_NONFINITE; return; }
+    float *logits = (float *)malloc(n * sizeof(float));
+    memcpy(logits, logits_in, n * sizeof(float));
+    pgo_apply_repetition(logits, n, p->history, p->n_history, p->rep);
+    pgo_apply_penalties(logits, n, p->history, p->n_history, p->freq, p->pres);
+    if (p->mask_words || p->grammar_dead) {
+        if (p->grammar_dead) { out->status = PGO_ROW_DEAD; free(logits); return; }
+        pgo_mask_logits_bits(p->mask_words, logits, n);
+        if (p->grammar_complete && p->eos_id >= 0 && (size_t)p->eos_id < n && !finite_f(logits[p->eos_id]))
+            logits[p->eos_id] = 0.0f;
+    }
     size_t per = n / n_shards;
+    float temperature = p->temperature;
     float t = fmaxf(temperature, PGO_EPS);
+    int greedy = temperature < 1e-5f;
     float *m = (float *)malloc(n_shards * sizeof(float)), *s = (float *)malloc(n_shards * sizeof(float));
-    cand_t *all = (cand_t *)malloc(n * sizeof(cand_t));
+    cand_t *all = (cand_t *)malloc(per * sizeof(cand_t));
     cand_t *keep = (cand_t *)malloc((size_t)n_shards * cand * sizeof(cand_t));
     size_t n_keep = 0;
-    float M = -INFINITY;
+    float M = -INFINITY, best = -INFINITY;
+    int have = 0;
     for (uint32_t r = 0; r < n_shards; r++) {
-        size_t lo = r * per, hi = lo + per;
+        size_t lo = r * per, hi = lo + per, n_fin = 0;
         float mr = -INFINITY;
-        for (size_t i = lo; i < hi; i++) mr = fmaxf(mr, logits[i]);
+        for (size_t i = lo; i < hi; i++)
+            if (finite_f(logits[i])) { mr = fmaxf(mr, logits[i]); all[n_fin].v = logits[i]; all[n_fin].id = (uint32_t)i; n_fin++; }
         float sr = 0.0f;
-        for (size_t i = lo; i < hi; i++) sr += expf((logits[i] - mr) / t);
+        if (!greedy)   /* non-finite entries contribute zero, as in temperature_softmax */
+            for (size_t i = lo; i < hi; i++)
+                if (finite_f(logits[i])) sr += expf((logits[i] - mr) / t);
         m[r] = mr; s[r] = sr;
         M = fmaxf(M, mr);
-        for (size_t i = lo; i < hi; i++) { all[i - lo].v = logits[i]; all[i - lo].id = (uint32_t)i; }
-        qsort(all, per, sizeof(cand_t), cmp_cand);
-        size_t take = cand < per ? cand : per;
-        memcpy(keep + n_keep, all, take * sizeof(cand_t));
-        n_keep += take;
+        if (n_fin) {   /* shard argmax: largest value, lowest id; shards come in id order */
+            float bv = all[0].v; uint32_t bi = all[0].id;
+            for (size_t j = 1; j < n_fin; j++) if (all[j].v > bv) { bv = all[j].v; bi = all[j].id; }
+            if (!have || bv > best) { best = bv; out->argmax = bi; have = 1; }
+        }
+        if (!greedy) {
+            qsort(all, n_fin, sizeof(cand_t), cmp_cand);
+            size_t take = cand < n_fin ? cand : n_fin;
+            memcpy(keep + n_keep, all, take * sizeof(cand_t));
+            n_keep += take;
+        }
     }
+    out->gmax = M;
+    if (!have) out->status = PGO_ROW_EMPTY;
+    if (greedy || !have) { out->token = out->argmax; free(logits); free(m); free(s); free(all); free(keep); return; }
     float S = 0.0f;
-    for (uint32_t r = 0; r < n_shards; r++) S += s[r] * expf((m[r] - M) / t);
-    out->gmax = M; out->gsum = S;
-    /* greedy: best candidate, lowest id on ties == global argmax */
-    qsort(keep, n_keep, sizeof(cand_t), cmp_cand);
-    out->argmax = keep[0].id;
-    if (temperature < 1e-5f) { out->token = out->argmax; free(m); free(s); free(all); free(keep); return; }
+    for (uint32_t r = 0; r < n_shards; r++)
+        if (finite_f(m[r])) S += s[r] * expf((m[r] - M) / t);
+    out->gsum = S;
     float *probs = (float *)calloc(n, sizeof(float));
     for (size_t j = 0; j < n_keep; j++) {
         float e = expf((keep[j].v - M) / t);
         probs[keep[j].id] = S > PGO_EPS ? e / S : e;
     }
-    if (!(top_p >= 1.0f - PGO_EPS)) {
+    if (p->top_k != 0 && (size_t)p->top_k <= n_keep) {   /* apply_top_k over the union (ties survive) */
+        float *sorted = (float *)malloc(n_keep * sizeof(float));
+        for (size_t j = 0; j < n_keep; j++) sorted[j] = probs[keep[j].id];
+        qsort(sorted, n_keep, sizeof(float), cmp_desc_f);
+        float threshold = sorted[p->top_k - 1];
+        size_t j = p->top_k;
+        while (j < n_keep && sorted[j] == threshold) j++;
+        if (j < n_keep && threshold > 0.0f) out->margin = fminf(out->margin, rel_gap(threshold, sorted[j]));
+        free(sorted);
+        for (size_t q = 0; q < n_keep; q++)
+            if (probs[keep[q].id] < threshold) probs[keep[q].id] = 0.0f;
+    }
+    if (!(p->top_p >= 1.0f - PGO_EPS)) {
         float before, at;
-        top_p_core(probs, n, top_p, &before, &at);
+        top_p_core(probs, n, p->top_p, &before, &at);
         if (at >= 0.0f) {
-            out->margin = fminf(out->margin, rel_gap(at, top_p));
-            out->margin = fminf(out->margin, rel_gap(before, top_p));
+            out->margin = fminf(out->margin, rel_gap(at, p->top_p));
+            out->margin = fminf(out->margin, rel_gap(before, p->top_p));
         }
     }
     for (size_t i = 0; i < n; i++) out->n_kept += probs[i] > 0.0f;
@@ -470,10 +502,10 @@ void pgo_tp_sample_row(const float *logits, size_t n, uint32_t n_shards, uint32_
     for (size_t i = 0; i < n; i++) total += probs[i];
     out->total = total;
     if (total <= PGO_EPS) {
-        out->token = pgo_argmax(probs, n);
+        out->token = out->argmax;
     } else {
         out->drew = 1;
-        float uu = u * total, acc = 0.0f, prev = 0.0f;
+        float uu = p->uniform * total, acc = 0.0f, prev = 0.0f;
         uint32_t tok = (uint32_t)(n - 1);
         int hit = 0;
         for (size_t i = 0; i < n; i++) {
@@ -486,7 +518,7 @@ void pgo_tp_sample_row(const float *logits, size_t n, uint32_t n_shards, uint32_
             out->margin = fminf(out->margin, fabsf(uu - prev) / total + (prev == 0.0f ? 1.0f : 0.0f));
         } else out->margin = fminf(out->margin, fabsf(uu - acc) / total);
     }
-    free(probs); free(m); free(s); free(all); free(keep);
+    free(probs); free(logits); free(m); free(s); free(all); free(keep);
 }
 
 uint32_t pgo_draft_accept(const uint32_t *row_argmax, const uint32_t *draft, uint32_t n,

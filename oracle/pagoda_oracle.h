@@ -31,7 +31,8 @@ enum {
     PGO_ROW_OK = 0,
     PGO_ROW_NONFINITE = 1, /* logits_sane failed -> FinishReason::Fault */
     PGO_ROW_DEAD = 2,      /* grammar dead end -> FinishReason::Stop, nothing sampled */
-    PGO_ROW_EMPTY = 3      /* nothing finite left after masking; token 0 as the reference returns */
+    PGO_ROW_EMPTY = 3,     /* nothing finite left after masking; token 0 as the reference returns */
+    PGO_ROW_BAD_PARAM = 4  /* a parameter outside of what the call supports (sharded mode: top_k > cand) */
 };
 
 /* ---- rng.rs:7-31 ---- */
@@ -93,6 +94,10 @@ typedef struct {
     /* relative distance of the closest decision (top-k threshold gap, top-p
      * boundary, CDF boundary) from flipping; 1.0 when no decision was taken */
     float margin;
+    /* the same, one per decision: gap between the top-k threshold and the next smaller distinct
+     * probability; distance of the top-p cumulative sums around the cut from p; distance of
+     * u * total from the CDF steps around the drawn token */
+    float margin_k, margin_p, margin_cdf;
 } pgo_row_out;
 
 /* `logits` is read only; `work` must hold 2*n floats; `probs_out` (may be NULL) receives
@@ -121,14 +126,16 @@ void pgo_bf16_to_f32(const uint16_t *in, float *out, size_t n);
  * The row is split into n_shards equal column ranges.  Each shard contributes its
  * max m_r, its own sequential sum s_r = sum exp((x - m_r)/t) and its top `cand`
  * entries (value desc, id asc).  Merge: M = max m_r; S = sum_r s_r*exp((m_r - M)/t)
- * folded in shard order; candidate probability exp((x - M)/t)/S; then top-p, total
- * and the CDF walk exactly as the single-device chain does over the candidate set. */
+ * folded in shard order; candidate probability exp((x - M)/t)/S; then top-k (p->top_k <= cand,
+ * else PGO_ROW_BAD_PARAM), top-p, total and the CDF walk exactly as the single-device chain does,
+ * over the candidate set.  Sanity, penalties, grammar mask and EOS fix run first, as in
+ * pgo_sample_row; records hold finite logits only, and a shard without any contributes nothing. */
 typedef struct {
     uint32_t token; int32_t status; int32_t drew; uint32_t argmax;
     float gmax, gsum, total; uint32_t n_kept; float margin;
 } pgo_tp_out;
 void pgo_tp_sample_row(const float *logits, size_t n, uint32_t n_shards, uint32_t cand,
-                       float temperature, float top_p, float u, pgo_tp_out *out);
+                       const pgo_row_params *p, pgo_tp_out *out);
 /* draft verification: accept while argmax(row j) == draft[j]; returns accepted count,
  * *next = argmax at the first mismatch, or of the last row when all are accepted */
 uint32_t pgo_draft_accept(const uint32_t *row_argmax, const uint32_t *draft, uint32_t n,

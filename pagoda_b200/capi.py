@@ -25,7 +25,7 @@ EXPORTS = ["pgs_create", "pgs_destroy", "pgs_last_error", "pgs_mask_table_upload
            "pgs_grammar_build_table", "pgs_grammar_state_new", "pgs_grammar_state_reset", "pgs_grammar_state_free",
            "pgs_grammar_advance", "pgs_grammar_mask_state", "pgs_grammar_state_info",
            "pgs_log_softmax", "pgs_tp_record_bytes", "pgs_tp_partial", "pgs_tp_merge", "pgs_tp_partial_push",
-           "pgs_tp_merge_wait", "pgs_debug_read_profile", "pgs_peer_alloc", "pgs_peer_open", "pgs_peer_close", "pgs_peer_free", "pgs_draft_accept"]
+           "pgs_tp_merge_wait", "pgs_set_wait_limit", "pgs_tp_exchange_status", "pgs_debug_read_profile", "pgs_peer_alloc", "pgs_peer_open", "pgs_peer_close", "pgs_peer_free", "pgs_draft_accept"]
 
 
 class SamplerError(RuntimeError):
@@ -53,7 +53,12 @@ class BatchDesc(C.Structure):
 class TpDesc(C.Structure):
     _fields_ = [("struct_size", C.c_uint32), ("rows", C.c_uint32), ("vocab", C.c_uint32), ("n_shards", C.c_uint32),
                 ("shard_rank", C.c_uint32), ("cand", C.c_uint32), ("row_stride", C.c_uint64),
-                ("logits", C.c_void_p), ("temperature", C.c_void_p), ("top_p", C.c_void_p), ("uniform", C.c_void_p)]
+                ("logits", C.c_void_p), ("temperature", C.c_void_p), ("top_p", C.c_void_p), ("uniform", C.c_void_p),
+                ("top_k", C.c_void_p),
+                ("frequency_penalty", C.c_void_p), ("presence_penalty", C.c_void_p), ("repetition_penalty", C.c_void_p),
+                ("hist_offsets", C.c_void_p), ("hist_ids", C.c_void_p),
+                ("mask_table", C.c_void_p), ("mask_state", C.c_void_p),
+                ("eos_token_id", C.c_int32), ("reserved0", C.c_int32)]
 
 
 class TpOut(C.Structure):
@@ -124,6 +129,8 @@ def load_library():
     L.pgs_peer_open.argtypes = [C.c_void_p, C.c_char_p, C.POINTER(C.c_void_p)]
     L.pgs_peer_close.argtypes = [C.c_void_p, C.c_void_p]
     L.pgs_peer_free.argtypes = [C.c_void_p, C.c_void_p]
+    L.pgs_set_wait_limit.argtypes = [C.c_void_p, C.c_uint32]
+    L.pgs_tp_exchange_status.argtypes = [C.c_void_p]
     L.pgs_tp_merge_wait.argtypes = [C.c_void_p, C.POINTER(TpDesc), C.c_void_p, C.c_void_p, C.c_uint32,
                                     C.POINTER(TpOut), C.c_void_p]
     L.pgs_draft_accept.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_uint32, C.c_uint32, C.c_void_p,
@@ -443,8 +450,17 @@ class Sampler:
     def tp_record_bytes(self, cand: int) -> int:
         return self._lib.pgs_tp_record_bytes(cand)
 
-    def _tp_desc(self, rows, vocab, n_shards, rank, cand, logits=None, temperature=None, top_p=None, uniform=None):
+    def _tp_desc(self, rows, vocab, n_shards, rank, cand, logits=None, temperature=None, top_p=None, uniform=None,
+                 top_k=None, frequency_penalty=None, presence_penalty=None, repetition_penalty=None,
+                 hist_offsets=None, hist_ids=None, mask_table=None, mask_state=None, eos_token_id=-1):
+        """Per-row arrays are CUDA tensors (float32 / int32) or None."""
         d = TpDesc()
+        self._tp_keep = (top_k, frequency_penalty, presence_penalty, repetition_penalty, hist_offsets, hist_ids,
+                         mask_table, mask_state)
+        ptr = lambda t: None if t is None else t.data_ptr()
+        d.top_k, d.frequency_penalty, d.presence_penalty = ptr(top_k), ptr(frequency_penalty), ptr(presence_penalty)
+        d.repetition_penalty, d.hist_offsets, d.hist_ids = ptr(repetition_penalty), ptr(hist_offsets), ptr(hist_ids)
+        d.mask_table, d.mask_state, d.eos_token_id = ptr(mask_table), ptr(mask_state), int(eos_token_id)
         d.struct_size = C.sizeof(TpDesc)
         d.rows, d.vocab, d.n_shards, d.shard_rank, d.cand = rows, vocab, n_shards, rank, cand
         if logits is not None:
@@ -457,19 +473,22 @@ class Sampler:
         d.uniform = None if uniform is None else uniform.data_ptr()
         return d
 
-    def tp_partial(self, shard_logits, vocab, n_shards, rank, cand, temperature=None, records=None, stream_ptr=None):
+    def tp_partial(self, shard_logits, vocab, n_shards, rank, cand, temperature=None, records=None, stream_ptr=None,
+                   **chain):
         """Emit this rank's per-row records (uint8 CUDA tensor [rows, record_bytes]) for its column
-        shard `shard_logits` [rows, vocab // n_shards] (float32, CUDA)."""
+        shard `shard_logits` [rows, vocab // n_shards] (float32, CUDA).  `chain`: the penalty / history /
+        grammar arguments of _tp_desc (history ids and eos_token_id are global ids, mask tables hold this
+        shard's bits)."""
         import torch
         rows = shard_logits.shape[0]
         if records is None:
             records = torch.empty((rows, self.tp_record_bytes(cand)), dtype=torch.uint8, device=shard_logits.device)
-        d = self._tp_desc(rows, vocab, n_shards, rank, cand, shard_logits, temperature)
+        d = self._tp_desc(rows, vocab, n_shards, rank, cand, shard_logits, temperature, **chain)
         self._check(self._lib.pgs_tp_partial(self._h, C.byref(d), records.data_ptr(), self._stream(stream_ptr)))
         return records
 
     def tp_merge(self, records_all, vocab, n_shards, rank, cand, temperature=None, top_p=None, uniform=None,
-                 stream_ptr=None):
+                 stream_ptr=None, top_k=None):
         """Merge the all-gathered records [n_shards, rows, record_bytes] into tokens; returns a dict of
         CUDA tensors (token, status, drew, argmax, gmax, gsum, total, n_kept)."""
         import torch
@@ -484,7 +503,7 @@ class Sampler:
                    total=torch.zeros(rows, dtype=torch.float32, device=dev),
                    n_kept=torch.zeros(rows, dtype=torch.int32, device=dev))
         o = TpOut(**{k: v.data_ptr() for k, v in out.items()})
-        d = self._tp_desc(rows, vocab, n_shards, rank, cand, None, temperature, top_p, uniform)
+        d = self._tp_desc(rows, vocab, n_shards, rank, cand, None, temperature, top_p, uniform, top_k=top_k)
         self._check(self._lib.pgs_tp_merge(self._h, C.byref(d), records_all.data_ptr(), C.byref(o),
                                            self._stream(stream_ptr)))
         return out
@@ -509,19 +528,27 @@ class Sampler:
         self._check(self._lib.pgs_peer_free(self._h, C.c_void_p(addr)))
 
     def tp_partial_push(self, shard_logits, vocab, n_shards, rank, cand, peer_record_ptrs, peer_flag_ptrs, epoch,
-                        temperature=None, stream_ptr=None):
+                        temperature=None, stream_ptr=None, **chain):
         """Emit this rank's records straight into every rank's gather buffer (peer stores) and raise this
         shard's flag there.  peer_record_ptrs / peer_flag_ptrs: device addresses (ints), one per rank, of the
         [n_shards, rows, record_bytes] gather buffers and the [n_shards] uint32 flag arrays of this epoch."""
         rows = shard_logits.shape[0]
-        d = self._tp_desc(rows, vocab, n_shards, rank, cand, shard_logits, temperature)
+        d = self._tp_desc(rows, vocab, n_shards, rank, cand, shard_logits, temperature, **chain)
         recs = (C.c_void_p * n_shards)(*[int(p) for p in peer_record_ptrs])
         flags = (C.c_void_p * n_shards)(*[int(p) for p in peer_flag_ptrs])
         self._check(self._lib.pgs_tp_partial_push(self._h, C.byref(d), recs, flags, C.c_uint32(epoch),
                                                   self._stream(stream_ptr)))
 
+    def set_wait_limit(self, polls: int):
+        """Bound of tp_merge_wait's device-side wait, in polls of about half a microsecond."""
+        self._check(self._lib.pgs_set_wait_limit(self._h, C.c_uint32(polls)))
+
+    def tp_exchange_status(self):
+        """Raises SamplerError (code -5) when rows gave up waiting for a shard since the last call."""
+        self._check(self._lib.pgs_tp_exchange_status(self._h))
+
     def tp_merge_wait(self, records_all, flags, epoch, vocab, n_shards, rank, cand, temperature=None, top_p=None,
-                      uniform=None, stream_ptr=None):
+                      uniform=None, stream_ptr=None, top_k=None):
         """tp_merge preceded, on the device, by a bounded wait until all n_shards flags of this rank have
         reached `epoch`.  records_all [n_shards, rows, record_bytes] uint8, flags [n_shards] int32/uint32."""
         import torch
@@ -536,7 +563,7 @@ class Sampler:
                    total=torch.zeros(rows, dtype=torch.float32, device=dev),
                    n_kept=torch.zeros(rows, dtype=torch.int32, device=dev))
         o = TpOut(**{k: v.data_ptr() for k, v in out.items()})
-        d = self._tp_desc(rows, vocab, n_shards, rank, cand, None, temperature, top_p, uniform)
+        d = self._tp_desc(rows, vocab, n_shards, rank, cand, None, temperature, top_p, uniform, top_k=top_k)
         self._check(self._lib.pgs_tp_merge_wait(self._h, C.byref(d), C.c_void_p(records_all.data_ptr()),
                                                 C.c_void_p(flags.data_ptr()), C.c_uint32(epoch), C.byref(o),
                                                 self._stream(stream_ptr)))

@@ -38,7 +38,7 @@ struct ScoreArgs {
 cudaError_t configure_score();
 cudaError_t launch_log_softmax(const ScoreArgs& a, uint32_t grid, cudaStream_t stream);
 cudaError_t configure_tp();
-cudaError_t launch_tp_partial(const TpArgs& a, uint32_t grid, cudaStream_t stream);
+cudaError_t launch_tp_push(const TpArgs& a, cudaStream_t stream);
 cudaError_t launch_tp_merge(const TpArgs& a, const TpOut& o, cudaStream_t stream);
 cudaError_t launch_draft_accept(const uint32_t* row_argmax, const uint32_t* draft, uint32_t sequences,
                                 uint32_t positions, uint32_t* accepted, uint32_t* next, cudaStream_t stream);
@@ -88,7 +88,11 @@ struct pgs_handle {
     int stream_ctas = 0;
     uint32_t* p1_done = nullptr;      // device counter: rows that finished their first pass, over all launches
     uint32_t done_total = 0;          // the value that counter has when every launch so far has completed
-    unsigned long long* faulted = nullptr;   // device counter of ROW_NONFINITE rows
+    unsigned long long* faulted = nullptr;   // device counters: [0] ROW_NONFINITE rows, [1] rows whose exchange wait ran out
+    unsigned long long* tp_timeouts = nullptr;   // = faulted + 1
+    unsigned long long timeouts_seen = 0;    // value of the second counter at the last pgs_tp_exchange_status
+    uint32_t wait_polls = 1u << 21;          // bound of the merge's flag wait (about a second)
+    cudaStream_t tp_stream = nullptr;        // stream of the last pgs_tp_merge_wait
     long long* prof = nullptr;        // phase timers of the row kernel (PGS_PROFILE=1)
     pgs_counters counters = {};
     char err[256] = "";
@@ -203,8 +207,9 @@ extern "C" int pgs_create(int device, uint32_t max_rows, uint32_t max_vocab, uin
         PGS_CUDA(nullptr, cudaMemsetAsync(h->tp_done, 0, sizeof(uint32_t), h->stream));
         PGS_CUDA(nullptr, cudaMalloc(&h->p1_done, sizeof(uint32_t)));
         PGS_CUDA(nullptr, cudaMemsetAsync(h->p1_done, 0, sizeof(uint32_t), h->stream));
-        PGS_CUDA(nullptr, cudaMalloc(&h->faulted, sizeof(unsigned long long)));
-        PGS_CUDA(nullptr, cudaMemsetAsync(h->faulted, 0, sizeof(unsigned long long), h->stream));
+        PGS_CUDA(nullptr, cudaMalloc(&h->faulted, 2 * sizeof(unsigned long long)));
+        PGS_CUDA(nullptr, cudaMemsetAsync(h->faulted, 0, 2 * sizeof(unsigned long long), h->stream));
+        h->tp_timeouts = h->faulted + 1;
         h->stream_hash = pow2_at_least(2 * (max_history ? max_history : 1), 64);
         if (h->stream_hash > (uint32_t)pgs::S_MAX_HASH) h->stream_hash = pgs::S_MAX_HASH;   // longer histories take the general kernel
         h->stream_smem = pgs::stream_smem_bytes();
@@ -359,12 +364,12 @@ int launch_step(pgs_handle* h, pgs::RowArgs& a, cudaStream_t stream) {
     h->done_total += rows;
     // Both lists are usually empty.  The two passes are set up while the row kernel still runs (programmatic stream
     // serialization) and return at once when they find nothing listed.
-    PGS_CUDA(h, pgs::launch_finish(a, sl.ho, stream));
+    if (!a.tp_records) PGS_CUDA(h, pgs::launch_finish(a, sl.ho, stream));   // (records are always written by the row's own CTA)
     pgs::RowArgs wl = a;
     wl.work_rows = h->work_rows;
     wl.work_count = h->work_count;
     PGS_CUDA(h, pgs::launch_general(wl, grid < 32u ? grid : 32u, stream));
-    h->counters.kernel_launches += 3;
+    h->counters.kernel_launches += a.tp_records ? 2 : 3;
     return PGS_OK;
 }
 
@@ -413,8 +418,12 @@ int validate(pgs_handle* h, const pgs_batch_desc* d) {
     if (d->row_stride < d->vocab) return fail(h, PGS_ERR_INVALID, "row_stride < vocab");
     if (d->logits_dtype > PGS_BF16 || d->logits_mem > PGS_MEM_HOST || d->aux_mem > PGS_MEM_HOST)
         return fail(h, PGS_ERR_INVALID, "bad dtype / memory kind");
-    if ((d->hist_offsets == nullptr) != (d->hist_ids == nullptr) && d->hist_offsets == nullptr)
+    if (d->hist_ids && !d->hist_offsets)
         return fail(h, PGS_ERR_INVALID, "hist_ids given without hist_offsets");
+    // Offsets without ids: only host arrays can be checked for "every row is empty"; device offsets
+    // cannot be read here, so there the pair must come together.
+    if (d->hist_offsets && !d->hist_ids && (d->aux_mem != PGS_MEM_HOST || d->hist_offsets[d->rows] != 0))
+        return fail(h, PGS_ERR_INVALID, "hist_offsets given without hist_ids");
     if ((d->dump_ids || d->dump_probs) && d->dump_cap == 0)
         return fail(h, PGS_ERR_INVALID, "dump arrays given with dump_cap == 0");
     return PGS_OK;
@@ -478,7 +487,7 @@ int run_batch(pgs_handle* h, const pgs_batch_desc* d, cudaStream_t stream, bool 
         a.pres = plan.in(d->presence_penalty, rows);
         a.rep = plan.in(d->repetition_penalty, rows);
         a.hist_offsets = plan.in(d->hist_offsets, (size_t)rows + 1);
-        a.hist_ids = d->hist_offsets ? plan.in(d->hist_ids ? d->hist_ids : (const uint32_t*)"", hist_total) : nullptr;
+        a.hist_ids = hist_total ? plan.in(d->hist_ids, hist_total) : nullptr;
         a.mask_table = plan.in(d->mask_table, rows);
         a.mask_state = plan.in(d->mask_state, rows);
         a.uniform = plan.in(d->uniform, rows);
@@ -573,17 +582,42 @@ static int tp_args(pgs_handle* h, const pgs_tp_desc* d, pgs::TpArgs* a) {
     if (d->n_shards == 0 || d->n_shards > 8 || d->shard_rank >= d->n_shards || d->vocab % d->n_shards)
         return fail(h, PGS_ERR_INVALID, "need 1 <= n_shards <= 8, rank < n_shards, vocab divisible by n_shards");
     if (d->cand == 0 || d->cand > 128) return fail(h, PGS_ERR_INVALID, "cand must be in 1..128");
-    if (d->rows == 0 || d->rows > h->max_rows * 16u) return fail(h, PGS_ERR_LIMIT, "too many rows");
+    if (d->rows == 0 || d->rows > h->max_rows) return fail(h, PGS_ERR_LIMIT, "%u rows exceed the handle's %u", d->rows, h->max_rows);
     a->shard_vocab = d->vocab / d->n_shards;
+    if (a->shard_vocab > h->max_vocab) return fail(h, PGS_ERR_LIMIT, "shard width %u exceeds the handle's vocab %u", a->shard_vocab, h->max_vocab);
     if (d->row_stride < a->shard_vocab) return fail(h, PGS_ERR_INVALID, "row_stride < shard width");
     a->logits = d->logits; a->row_stride = d->row_stride; a->rows = d->rows; a->vocab = d->vocab;
     a->shard_lo = d->shard_rank * a->shard_vocab; a->n_shards = d->n_shards; a->cand = d->cand;
-    a->temperature = d->temperature; a->top_p = d->top_p; a->uniform = d->uniform;
+    a->temperature = d->temperature; a->top_p = d->top_p; a->uniform = d->uniform; a->top_k = d->top_k;
+    a->wait_polls = h->wait_polls; a->timeouts = h->tp_timeouts;
     a->rec_bytes = (uint32_t)pgs_tp_record_bytes(d->cand);
     memset(a->peer_records, 0, sizeof a->peer_records);
     memset(a->peer_flags, 0, sizeof a->peer_flags);
     a->flags = nullptr; a->done = nullptr; a->epoch = 0; a->shard_rank = d->shard_rank;
     return PGS_OK;
+}
+
+// The emitting half is the batch step itself over this rank's columns, with records in place of tokens: the same
+// kernels, checks, penalties, mask and EOS fix; history ids and eos_token_id are global ids.
+static int tp_emit(pgs_handle* h, const pgs_tp_desc* d, const pgs::TpArgs& t, unsigned char* records, cudaStream_t stream) {
+    if ((d->hist_offsets == nullptr) != (d->hist_ids == nullptr))
+        return fail(h, PGS_ERR_INVALID, "hist_offsets and hist_ids must be given together");
+    if (((uintptr_t)records & 15u) != 0) return fail(h, PGS_ERR_INVALID, "the record buffer must be 16-byte aligned");
+    pgs::RowArgs a;
+    memset(&a, 0, sizeof a);
+    a.logits = d->logits; a.dtype = 0; a.rows = d->rows; a.vocab = t.shard_vocab; a.row_stride = d->row_stride;
+    a.temperature = d->temperature;
+    a.freq = d->frequency_penalty; a.pres = d->presence_penalty; a.rep = d->repetition_penalty;
+    a.hist_offsets = d->hist_offsets; a.hist_ids = d->hist_ids;
+    a.mask_table = d->mask_table; a.mask_state = d->mask_state; a.tables = h->tables_dev;
+    const int64_t eos_local = (int64_t)d->eos_token_id - (int64_t)t.shard_lo;
+    a.eos = (d->eos_token_id >= 0 && eos_local >= 0 && eos_local < (int64_t)t.shard_vocab) ? (int32_t)eos_local : -1;
+    a.sx = h->sx; a.sl_id = h->sl_id; a.sl_p = h->sl_p; a.sl_key = h->sl_key;
+    a.sh_key = h->sh_key; a.sh_cnt = h->sh_cnt;
+    a.vocab_pad = h->vocab_pad; a.sort_pad = h->sort_pad; a.hash_cap = h->hash_cap;
+    a.max_history = h->max_history;
+    a.tp_records = records; a.tp_rec_bytes = t.rec_bytes; a.tp_cand = t.cand; a.id_base = t.shard_lo;
+    return launch_step(h, a, stream);
 }
 
 extern "C" int pgs_tp_partial(pgs_handle* h, const pgs_tp_desc* d, void* records_out, void* cuda_stream) {
@@ -593,11 +627,7 @@ extern "C" int pgs_tp_partial(pgs_handle* h, const pgs_tp_desc* d, void* records
     if (rc != PGS_OK) return rc;
     if (!d->logits || !records_out) return fail(h, PGS_ERR_INVALID, "logits and records_out are required");
     DeviceGuard g(h->device);
-    a.records = (unsigned char*)records_out;
-    const uint32_t grid = a.rows < (uint32_t)h->sm_count ? a.rows : (uint32_t)h->sm_count;
-    PGS_CUDA(h, pgs::launch_tp_partial(a, grid, cuda_stream ? (cudaStream_t)cuda_stream : h->stream));
-    h->counters.kernel_launches += 1;
-    return PGS_OK;
+    return tp_emit(h, d, a, (unsigned char*)records_out, cuda_stream ? (cudaStream_t)cuda_stream : h->stream);
 }
 
 extern "C" int pgs_tp_merge(pgs_handle* h, const pgs_tp_desc* d, const void* records_all, const pgs_tp_out* out,
@@ -702,8 +732,10 @@ extern "C" int pgs_tp_partial_push(pgs_handle* h, const pgs_tp_desc* d, void* co
     a.records = a.peer_records[d->shard_rank];   // built in this rank's own buffer, then copied out
     a.done = h->tp_done;                         // zero between launches
     a.epoch = epoch;
-    const uint32_t grid = a.rows < (uint32_t)h->sm_count ? a.rows : (uint32_t)h->sm_count;
-    PGS_CUDA(h, pgs::launch_tp_partial(a, grid, cuda_stream ? (cudaStream_t)cuda_stream : h->stream));
+    cudaStream_t stream = cuda_stream ? (cudaStream_t)cuda_stream : h->stream;
+    rc = tp_emit(h, d, a, a.records, stream);
+    if (rc != PGS_OK) return rc;
+    PGS_CUDA(h, pgs::launch_tp_push(a, stream));
     h->counters.kernel_launches += 1;
     return PGS_OK;
 }
@@ -721,9 +753,30 @@ extern "C" int pgs_tp_merge_wait(pgs_handle* h, const pgs_tp_desc* d, const void
     a.flags = (uint32_t*)flags;
     a.epoch = epoch;
     pgs::TpOut o{out->token, out->status, out->drew, out->argmax, out->gmax, out->gsum, out->total, out->n_kept};
-    PGS_CUDA(h, pgs::launch_tp_merge(a, o, cuda_stream ? (cudaStream_t)cuda_stream : h->stream));
+    h->tp_stream = cuda_stream ? (cudaStream_t)cuda_stream : h->stream;
+    PGS_CUDA(h, pgs::launch_tp_merge(a, o, h->tp_stream));
     h->counters.kernel_launches += 1;
     h->counters.rows += a.rows;
+    return PGS_OK;
+}
+
+extern "C" int pgs_set_wait_limit(pgs_handle* h, uint32_t polls) {
+    if (!h) return PGS_ERR_INVALID;
+    if (polls == 0) return fail(h, PGS_ERR_INVALID, "pgs_set_wait_limit: at least one poll");
+    h->wait_polls = polls;
+    return PGS_OK;
+}
+
+extern "C" int pgs_tp_exchange_status(pgs_handle* h) {
+    if (!h) return PGS_ERR_INVALID;
+    DeviceGuard g(h->device);
+    unsigned long long n = 0;
+    cudaError_t e = cudaStreamSynchronize(h->tp_stream ? h->tp_stream : h->stream);
+    if (e == cudaSuccess) e = cudaMemcpy(&n, h->tp_timeouts, sizeof n, cudaMemcpyDeviceToHost);
+    if (e != cudaSuccess) return fail(h, PGS_ERR_CUDA, "pgs_tp_exchange_status: %s", cudaGetErrorString(e));
+    const unsigned long long fresh = n - h->timeouts_seen;
+    h->timeouts_seen = n;
+    if (fresh) return fail(h, PGS_ERR_TIMEOUT, "%llu rows gave up waiting for a shard's records", fresh);
     return PGS_OK;
 }
 

@@ -64,6 +64,24 @@ struct RowArgs {
     const uint32_t* work_rows;
     uint32_t* work_count;           // [0] = number of listed rows, [1] = CTAs that finished the list
     unsigned long long* faulted;    // optional: rows that ended as ROW_NONFINITE, counted over all launches
+    // vocabulary-sharded emit mode (tp_records != nullptr): `logits` holds the columns id_base .. id_base + vocab
+    // of every row, history ids are global ids, and a row ends as a record (TpRecHead + candidates) instead of a
+    // token: the outputs above are not written
+    unsigned char* tp_records;      // [rows x tp_rec_bytes]
+    uint32_t tp_rec_bytes, tp_cand;
+    uint32_t id_base;               // global id of column 0 (0 outside of the sharded mode)
 };
+
+// One shard's share of one row.  n_status: candidates in the record (low 24 bits) and the row status the shard
+// found (high 8 bits: ROW_OK, ROW_NONFINITE, ROW_DEAD or ROW_BAD_PARAM).  m is the shard's maximum (-inf when the
+// shard holds no finite logit), s its f32 left-fold sum of exp((x - m) / t) (0 for greedy rows), argmax a global
+// id.  The head is followed by float x[cand] and uint32 id[cand], sorted by (x descending, id ascending).
+struct TpRecHead { float m; float s; uint32_t n_status; uint32_t argmax; };
+
+__device__ __forceinline__ void tp_write_head(const RowArgs& a, uint32_t row, float m, float s, uint32_t n, int status,
+                                              uint32_t argmax_local) {
+    TpRecHead* h = reinterpret_cast<TpRecHead*>(a.tp_records + (size_t)row * a.tp_rec_bytes);
+    h->m = m; h->s = s; h->n_status = n | ((uint32_t)status << 24); h->argmax = a.id_base + argmax_local;
+}
 
 }  // namespace pgs

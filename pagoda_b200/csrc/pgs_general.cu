@@ -42,6 +42,61 @@ __device__ __forceinline__ void write_row(const RowArgs& a, uint32_t row, uint32
     if (a.n_kept) a.n_kept[row] = n_kept;
 }
 
+// Vocabulary-sharded mode: the shard's record of one row from its processed logits X (penalties, mask and EOS fix
+// applied).  The `tp_cand` largest finite logits by (value descending, id ascending), then the shard's f32
+// left-fold sum (which overwrites X).  Called by the whole CTA.
+__device__ __forceinline__ void tp_emit_row(const RowArgs& a, GeneralSmem& sm, uint32_t row, float* X, uint32_t V, bool any,
+                                            float m, uint32_t amax, float temp, const unsigned long long* tab) {
+    const int tid = threadIdx.x;
+    if (!any || temp < 1e-5f) {   // greedy rows travel as maximum + argmax alone
+        if (tid == 0) tp_write_head(a, row, m, 0.0f, 0u, ROW_OK, amax);
+        return;
+    }
+    float* lx = reinterpret_cast<float*>(sm.sort_tile);
+    uint32_t* lid = reinterpret_cast<uint32_t*>(sm.sort_tile) + 1024;
+    uint32_t* ln = reinterpret_cast<uint32_t*>(sm.sort_tile) + 2048;
+    TpRecHead* head = reinterpret_cast<TpRecHead*>(a.tp_records + (size_t)row * a.tp_rec_bytes);
+    float* rx = reinterpret_cast<float*>(head + 1);
+    uint32_t* rid = reinterpret_cast<uint32_t*>(rx + a.tp_cand);
+    uint32_t fin = 0;
+    for (uint32_t i = tid; i < V; i += NT) fin += order_key(X[i]) != 0u;
+    uint32_t n_fin;
+    block_excl_scan_u32(fin, &n_fin, sm.rs);
+    const uint32_t want = a.tp_cand < n_fin ? a.tp_cand : n_fin;   // >= 1: the row has a finite maximum
+    const uint32_t kk = radix_select_kth([&](int i) { return order_key(X[i]); }, (int)V, want, sm.sel, sm.rs);
+    if (tid == 0) *ln = 0;
+    __syncthreads();
+    for (uint32_t i = tid; i < V; i += NT) {   // strictly above the threshold: fewer than `want`
+        if (order_key(X[i]) > kk) {
+            const uint32_t at = atomicAdd(ln, 1u);
+            lx[at] = X[i]; lid[at] = i;
+        }
+    }
+    __syncthreads();
+    uint32_t filled = *ln;
+    for (uint32_t base = 0; base < V && filled < want; base += NT) {   // ties, lowest ids first
+        const uint32_t i = base + tid;
+        const uint32_t tie = (i < V && order_key(X[i]) == kk) ? 1u : 0u;
+        uint32_t tot;
+        const uint32_t at = filled + block_excl_scan_u32(tie, &tot, sm.rs);
+        if (tie && at < want) { lx[at] = X[i]; lid[at] = i; }
+        filled = min(want, filled + tot);
+    }
+    __syncthreads();
+    for (uint32_t j = tid; j < want; j += NT) {   // rank-sort the `want` entries
+        const float v = lx[j];
+        const uint32_t id = lid[j];
+        uint32_t r = 0;
+        for (uint32_t o = 0; o < want; o++) r += (lx[o] > v) || (lx[o] == v && lid[o] < id);
+        rx[r] = v;
+        rid[r] = a.id_base + id;
+    }
+    const float t = fmaxf(temp, 1e-9f);
+    const float s = seq_scan([&](int i) { return softmax_num(X[i], m, t, tab); }, (int)V, 0.0f, SEQ_SUM, 0.0f, nullptr,
+                             sm.seq, sm.rs);
+    if (tid == 0) tp_write_head(a, row, m, s, want, ROW_OK, amax);
+}
+
 __global__ void __launch_bounds__(NT, 1) general_row_kernel(const RowArgs a) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     GeneralSmem& sm = *reinterpret_cast<GeneralSmem*>(smem_raw);
@@ -87,8 +142,12 @@ __global__ void __launch_bounds__(NT, 1) general_row_kernel(const RowArgs a) {
             const uint32_t h1 = a.hist_offsets[row + 1];
             if (h1 < h0 || h1 - h0 > a.max_history) bad = true; else nh = h1 - h0;
         }
+        const bool tp = a.tp_records != nullptr;
         if (bad) {
-            if (tid == 0) write_row(a, row, 0u, ROW_BAD_PARAM, 0, 0u, -INFINITY, 0.0f, 0.0f, 0u);
+            if (tid == 0) {
+                if (tp) tp_write_head(a, row, -INFINITY, 0.0f, 0u, ROW_BAD_PARAM, 0u);
+                else write_row(a, row, 0u, ROW_BAD_PARAM, 0, 0u, -INFINITY, 0.0f, 0.0f, 0u);
+            }
             continue;
         }
 
@@ -121,13 +180,17 @@ __global__ void __launch_bounds__(NT, 1) general_row_kernel(const RowArgs a) {
         nonfinite = __syncthreads_or(nonfinite);
         if (nonfinite) {
             if (tid == 0) {
-                write_row(a, row, 0u, ROW_NONFINITE, 0, 0u, -INFINITY, 0.0f, 0.0f, 0u);
+                if (tp) tp_write_head(a, row, NAN, 0.0f, 0u, ROW_NONFINITE, 0u);
+                else write_row(a, row, 0u, ROW_NONFINITE, 0, 0u, -INFINITY, 0.0f, 0.0f, 0u);
                 if (a.faulted) atomicAdd(a.faulted, 1ull);
             }
             continue;
         }
         if (gflags & 2u) {
-            if (tid == 0) write_row(a, row, 0u, ROW_DEAD, 0, 0u, -INFINITY, 0.0f, 0.0f, 0u);
+            if (tid == 0) {
+                if (tp) tp_write_head(a, row, -INFINITY, 0.0f, 0u, ROW_DEAD, 0u);
+                else write_row(a, row, 0u, ROW_DEAD, 0, 0u, -INFINITY, 0.0f, 0.0f, 0u);
+            }
             continue;
         }
 
@@ -143,7 +206,7 @@ __global__ void __launch_bounds__(NT, 1) general_row_kernel(const RowArgs a) {
             for (uint32_t s = tid; s < cap; s += NT) { hk[s] = 0xffffffffu; hc[s] = 0u; }
             __syncthreads();
             for (uint32_t j = tid; j < nh; j += NT) {
-                const uint32_t id = a.hist_ids[h0 + j];
+                const uint32_t id = a.hist_ids[h0 + j] - a.id_base;   // ids below the shard wrap around
                 if (id >= V) continue;
                 uint32_t s = (id * 2654435761u) & (cap - 1);
                 for (uint32_t probe = 0; probe < cap; probe++) {
@@ -186,6 +249,10 @@ __global__ void __launch_bounds__(NT, 1) general_row_kernel(const RowArgs a) {
         const float m = any ? key_to_float((uint32_t)(best >> 32)) : -INFINITY;
         const uint32_t amax = any ? 0xffffffffu - (uint32_t)best : 0u;
         const int status = any ? ROW_OK : ROW_EMPTY;
+        if (tp) {   // vocabulary-sharded mode: the row ends as this shard's record
+            tp_emit_row(a, sm, row, X, V, any, m, amax, temp, tab);
+            continue;
+        }
         if (temp < 1e-5f) {
             if (tid == 0) write_row(a, row, amax, status, 0, amax, m, 0.0f, 0.0f, 0u);
             continue;
@@ -346,6 +413,8 @@ cudaError_t launch_general(const RowArgs& a, uint32_t grid, cudaStream_t stream)
 #include <stdio.h>
 #include <string.h>
 
+#include <mutex>
+
 #include "../../include/pagoda_sampler.h"
 
 namespace pgs {
@@ -361,6 +430,7 @@ constexpr size_t STATIC_BYTES = (size_t)STATIC_SLOTS * STATIC_MAX_VOCAB * (4 + 4
 static __device__ __align__(256) unsigned char g_static_scratch[STATIC_BYTES];
 
 static void* g_static_addr[64];                 // device address of the array, per device ordinal
+static std::mutex g_static_setup;               // two threads making their first call on a device at once
 static thread_local char g_static_error[256] = "";
 
 static int static_fail(int code, const char* what, cudaError_t e) {
@@ -391,6 +461,8 @@ extern "C" int pgs_sample_batch_static(int device, const pgs_batch_desc* desc_pt
     if (d->mask_table || d->mask_state)
         return static_fail(-1, "pgs_sample_batch_static: grammar tables belong to a handle and are not supported here",
                            cudaSuccess);
+    if ((d->hist_offsets == nullptr) != (d->hist_ids == nullptr))
+        return static_fail(-1, "pgs_sample_batch_static: hist_offsets and hist_ids must be given together", cudaSuccess);
     if ((d->dump_ids || d->dump_probs) && d->dump_cap == 0)
         return static_fail(-1, "pgs_sample_batch_static: dump arrays given with dump_cap == 0", cudaSuccess);
     int prev = -1;
@@ -398,15 +470,21 @@ extern "C" int pgs_sample_batch_static(int device, const pgs_batch_desc* desc_pt
     if (e != cudaSuccess) return static_fail(-2, "cudaGetDevice", e);
     if (prev != device && (e = cudaSetDevice(device)) != cudaSuccess) return static_fail(-2, "cudaSetDevice", e);
     int rc = 0;
-    if (!g_static_addr[device]) {   // set-up, once per device, with that device current
+    void* scratch = nullptr;
+    {   // set-up, once per device, with that device current
+        std::lock_guard<std::mutex> lk(g_static_setup);
+        scratch = g_static_addr[device];
+    }
+    if (!scratch) {
+        std::lock_guard<std::mutex> lk(g_static_setup);
         void* p = nullptr;
         e = cudaGetSymbolAddress(&p, g_static_scratch);
         if (e == cudaSuccess) e = configure_general();
         if (e != cudaSuccess) rc = static_fail(-2, "pgs_sample_batch_static set-up", e);
-        else g_static_addr[device] = p;
+        else g_static_addr[device] = scratch = p;
     }
     if (rc == 0) {
-        unsigned char* base = static_cast<unsigned char*>(g_static_addr[device]);
+        unsigned char* base = static_cast<unsigned char*>(scratch);
         const size_t per = (size_t)STATIC_SLOTS * STATIC_MAX_VOCAB;
         RowArgs a;
         memset(&a, 0, sizeof a);

@@ -124,6 +124,7 @@ struct StreamSmem {
         uint32_t hash[2 * S_MAX_HASH];
         float stage[SNW * S_REGION];
         FinishScratch fin;
+        unsigned long long tpkey[SNT];   // vocabulary-sharded mode: one candidate per thread while a record is ranked
     } u;
 };
 
@@ -223,7 +224,8 @@ template <bool BF16>
 __device__ __forceinline__ void sprepare_row(const RowArgs& a, const StreamLaunch& sl, uint32_t row, SRowCtl& c) {
     const uint32_t V = a.vocab;
     const float temp = a.temperature ? a.temperature[row] : 0.0f;
-    const uint32_t top_k = a.top_k ? a.top_k[row] : 0u;
+    // (vocabulary-sharded mode: the record's length takes the place of top-k; top-p and the draw belong to the merge)
+    const uint32_t top_k = a.tp_records ? a.tp_cand : a.top_k ? a.top_k[row] : 0u;
     const float top_p = a.top_p ? a.top_p[row] : 1.0f;
     const float freq = a.freq ? a.freq[row] : 0.0f;
     const float pres = a.pres ? a.pres[row] : 0.0f;
@@ -344,6 +346,29 @@ __device__ __forceinline__ void sfinish_row(StreamSmem& sm, const RowArgs& a, ui
         }
         if (lane == 0 && a.n_kept) a.n_kept[row] = done;
     }
+}
+
+// Vocabulary-sharded mode: the candidates of one row (n <= SNT, one per thread) -> this shard's record: the
+// tp_cand largest by (logit descending, id ascending) behind the head.  Called by every thread; the caller has a
+// barrier in front.
+__device__ __forceinline__ void semit_tp(StreamSmem& sm, const RowArgs& a, uint32_t row, uint32_t n, float m, float S,
+                                         uint32_t amax) {
+    const int tid = threadIdx.x;
+    TpRecHead* head = reinterpret_cast<TpRecHead*>(a.tp_records + (size_t)row * a.tp_rec_bytes);
+    float* rx = reinterpret_cast<float*>(head + 1);
+    uint32_t* rid = reinterpret_cast<uint32_t*>(rx + a.tp_cand);
+    const uint32_t want = a.tp_cand < n ? a.tp_cand : n;
+    if ((uint32_t)tid < n)
+        sm.u.tpkey[tid] = ((unsigned long long)order_key(sm.cand_x[tid]) << 32) | (unsigned long long)(0xffffffffu - sm.cand_id[tid]);
+    __syncthreads();
+    if ((uint32_t)tid < n) {
+        const unsigned long long kj = sm.u.tpkey[tid];
+        uint32_t r = 0;
+#pragma unroll 8
+        for (uint32_t o = 0; o < n; o++) r += sm.u.tpkey[o] > kj;
+        if (r < want) { rx[r] = sm.cand_x[tid]; rid[r] = a.id_base + sm.cand_id[tid]; }
+    }
+    if (tid == 0) tp_write_head(a, row, m, S, want, ROW_OK, amax);
 }
 
 // ------------------------------------------------------------------------------------------------------------
@@ -675,8 +700,10 @@ __global__ void __launch_bounds__(SNT, 2) stream_row_kernel(const RowArgs a, con
         const bool writer = tid == 0;
         if (ctl.kind != 0u) {
             if (writer) {
-                if (ctl.kind == 1u) { a.token[row] = 0; a.status[row] = ROW_BAD_PARAM; if (a.drew) a.drew[row] = 0; }
-                else sl.work_rows[atomicAdd(sl.work_count, 1u)] = row;
+                if (ctl.kind == 1u) {
+                    if (a.tp_records) tp_write_head(a, row, -INFINITY, 0.0f, 0u, ROW_BAD_PARAM, 0u);
+                    else { a.token[row] = 0; a.status[row] = ROW_BAD_PARAM; if (a.drew) a.drew[row] = 0; }
+                } else sl.work_rows[atomicAdd(sl.work_count, 1u)] = row;
                 atomicAdd(sl.p1_done, 1u);
             }
             continue;
@@ -721,7 +748,7 @@ __global__ void __launch_bounds__(SNT, 2) stream_row_kernel(const RowArgs a, con
             int spilled = 0;
 #pragma unroll 1
             for (uint32_t j = tid; j < nh; j += SNT) {
-                const uint32_t id = j == (uint32_t)tid ? hid0 : __ldg(a.hist_ids + h0 + j);
+                const uint32_t id = (j == (uint32_t)tid ? hid0 : __ldg(a.hist_ids + h0 + j)) - a.id_base;   // ids below a shard wrap around
                 if (id >= V) continue;   // engine.rs:1562
                 uint32_t s = (id * 2654435761u) & (H - 1u);
                 bool placed = false;
@@ -850,7 +877,13 @@ __global__ void __launch_bounds__(SNT, 2) stream_row_kernel(const RowArgs a, con
         }
         const uint32_t amax = any ? sm.amax : 0u;
         if (nonfinite || (gflags & 2u) || greedy || !any) {
-            if (writer) {
+            if (writer && a.tp_records) {
+                if (nonfinite) {
+                    tp_write_head(a, row, NAN, 0.0f, 0u, ROW_NONFINITE, 0u);
+                    if (a.faulted) atomicAdd(a.faulted, 1ull);
+                } else if (gflags & 2u) tp_write_head(a, row, -INFINITY, 0.0f, 0u, ROW_DEAD, 0u);
+                else tp_write_head(a, row, m, 0.0f, 0u, ROW_OK, amax);   // greedy or empty: maximum + argmax alone
+            } else if (writer) {
                 if (nonfinite) {
                     a.token[row] = 0; a.status[row] = ROW_NONFINITE; if (a.drew) a.drew[row] = 0;
                     if (a.faulted) atomicAdd(a.faulted, 1ull);
@@ -976,7 +1009,13 @@ __global__ void __launch_bounds__(SNT, 2) stream_row_kernel(const RowArgs a, con
             if (writer) { sl.work_rows[atomicAdd(sl.work_count, 1u)] = row; }
             continue;
         }
-        if (n_cand <= (uint32_t)S_FCAP) {
+        if (a.tp_records) {   // CTA-uniform
+            if (n_cand > (uint32_t)SNT) {
+                if (writer) { sl.work_rows[atomicAdd(sl.work_count, 1u)] = row; }
+                continue;
+            }
+            semit_tp(sm, a, row, n_cand, m, S, amax);
+        } else if (n_cand <= (uint32_t)S_FCAP) {
             sfinish_row(sm, a, row, n_cand, m, t, S, top_k, ctl.top_p, ctl.u01, amax, status);
         } else {
             // long lists: the finish kernel takes the row from here

@@ -14,6 +14,7 @@ struct TpArgs {
     const float* temperature;
     const float* top_p;
     const float* uniform;
+    const uint32_t* top_k;          // merge: per row, 0 = off; must not exceed cand
     unsigned char* records;         // partial: out [rows x rec_bytes]; merge: in [n_shards x rows x rec_bytes]
     uint32_t rec_bytes;
     // peer-store exchange (all zero for the plain calls)
@@ -23,6 +24,8 @@ struct TpArgs {
     uint32_t* done;                 // partial: CTAs finished in this launch
     uint32_t epoch;                 // step number the flags are raised to / waited for
     uint32_t shard_rank;
+    uint32_t wait_polls;            // merge: bound of the flag wait, in polls of about half a microsecond each
+    unsigned long long* timeouts;   // merge: rows that gave up waiting, counted over all launches
 };
 
 

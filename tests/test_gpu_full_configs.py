@@ -88,11 +88,10 @@ def test_headline_batch_properties(sampler, oracle, synth):
     kw["hist_offsets"], kw["hist_ids"] = offs, ids
     p = sampler.sample_batch(np.ascontiguousarray(w.logits[perm]), **kw)
     np.testing.assert_array_equal(p.token, a.token[perm])
-    # against the oracle on a slice of the batch
-    sub = w.head(32)
-    want = oracle.sample_batch(sub.logits, n_threads=16, **sub.oracle_kwargs())
-    clear = want["margin"] > 1e-5
-    np.testing.assert_array_equal(a.token[:32][clear], want["token"][clear])
+    # against the oracle, all 256 rows, with everything the parity helper checks
+    got, want = run_both(sampler, oracle, w, n_threads=16)
+    np.testing.assert_array_equal(got.token, a.token)
+    assert_same(got, want, w, exact=False)
 
 
 def test_config5_full_width_rows(sampler, oracle, synth):
@@ -117,7 +116,7 @@ def test_config5_full_width_rows(sampler, oracle, synth):
         tok, am = out["token"].cpu().numpy(), out["argmax"].cpu().numpy()
         for r in range(w.rows):
             want = oracle.tp_sample_row(w.logits[r], n, 64, 1.0, 0.95, float(w.uniform[r]))
-            assert tok[r] == want.token and am[r] == want.argmax, (n, r)
+            assert am[r] == want.argmax and (tok[r] == want.token or want.margin <= 1e-5), (n, r)
         np.testing.assert_array_equal(am, w.logits.argmax(axis=1))
         for s in range(16):
             na, nx = oracle.draft_accept(am[4 * s:4 * s + 4], w.extra["draft"][s])

@@ -40,7 +40,7 @@ def main():
         from oracle import oracle
         for r in range(rows):
             want = oracle.tp_sample_row(x[r], world, cand, float(temp[r]), float(top_p[r]), float(u[r]))
-            assert tok[r] == want.token, (r, tok[r], want.token)
+            assert tok[r] == want.token or want.margin <= 1e-5, (r, tok[r], want.token)
     # every rank must have produced the same tokens
     ref = out["token"].clone()
     dist.broadcast(ref, 0)

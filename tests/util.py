@@ -3,16 +3,27 @@ oracle and compare everything the chain decides."""
 import numpy as np
 
 
-def run_both(sampler, oracle, w, dump_cap=0, n_threads=8):
+def run_both(sampler, oracle, w, dump_cap=None, n_threads=8):
     table_id = None
     if w.mask_words is not None:
         table_id = sampler.upload_mask_table(w.mask_words, w.state_flags)
+    if dump_cap is None:   # room for every top-k set plus ties; rows over the whole vocabulary are not dumped
+        k = w.top_k[(w.top_k > 0) & (w.temperature >= 1e-5)] if w.top_k is not None else np.zeros(0)
+        dump_cap = int(min(w.vocab, k.max() + 64)) if k.size else 0
     try:
         got = sampler.sample_batch(w.logits, diagnostics=True, dump_cap=dump_cap, **w.sampler_kwargs(table_id))
     finally:
         if table_id is not None:
             sampler.free_mask_table(table_id)
     want = oracle.sample_batch(w.logits_f32(), n_threads=n_threads, **w.oracle_kwargs())
+    # the oracle once more with top-p off: what it keeps is the top-k set every row starts top-p from
+    if (w.top_p < 1.0).any():
+        kw = w.oracle_kwargs()
+        kw["top_p"] = np.ones_like(w.top_p)
+        got.want_topk = oracle.sample_batch(w.logits_f32(), n_threads=n_threads, **kw)
+    else:
+        got.want_topk = want
+    got.workload, got.oracle = w, oracle
     return got, want
 
 
@@ -44,7 +55,7 @@ def assert_same(got, want, w=None, check_floats=True, exact=True, min_clear=0.9)
     np.testing.assert_array_equal(got.n_kept[live], want["n_kept"][live], err_msg=f"{name}: n_kept")
 
 
-def oracle_probs(oracle, w, row):
+def oracle_probs(oracle, w, row, logits_row=None, **over):
     """Final probability vector of one row from the oracle (for kept-set comparisons)."""
     kw = dict(temperature=float(w.temperature[row]), top_k=int(w.top_k[row]), top_p=float(w.top_p[row]),
               freq=float(w.frequency_penalty[row]), pres=float(w.presence_penalty[row]),
@@ -56,11 +67,17 @@ def oracle_probs(oracle, w, row):
         kw["mask_words"] = w.mask_words[s]
         kw["complete"] = bool(w.state_flags[s] & 1)
         kw["dead"] = bool(w.state_flags[s] & 2)
-    out, probs = oracle.sample_row(w.logits_f32()[row], want_probs=True, **kw)
+    kw.update(over)
+    out, probs = oracle.sample_row(w.logits_f32()[row] if logits_row is None else logits_row, want_probs=True, **kw)
     return out, probs
 
 
 def assert_close(got, want, name="", min_clear=0.9):
+    """The default (streaming) kernel against the oracle.  Bit-exact, on every row: status, argmax, row maximum,
+    whether a uniform was consumed, and the top-k kept set (which does not depend on the sum).  Within TOL: the
+    f32 left-fold sum and the total.  The top-p cut and the drawn token are compared on every row whose own
+    margin (distance of that decision from flipping, reported by the oracle) exceeds TOL; the rows left out are
+    counted, printed and bounded."""
     np.testing.assert_array_equal(got.status, want["status"], err_msg=f"{name}: status")
     live = (want["status"] == 0) | (want["status"] == 3)
     np.testing.assert_array_equal(got.argmax[live], want["argmax"][live], err_msg=f"{name}: argmax")
@@ -68,14 +85,42 @@ def assert_close(got, want, name="", min_clear=0.9):
                                   err_msg=f"{name}: row_max")
     with np.errstate(divide="ignore", invalid="ignore"):
         rel = np.abs(got.sumexp[live] - want["sumexp"][live]) / np.abs(want["sumexp"][live])
-    print(f"[{name}] fused sumexp max relative error {np.nanmax(rel) if rel.size else 0:.3g}")
+    print(f"[{name}] sumexp max relative error {np.nanmax(rel) if rel.size else 0:.3g}")
     np.testing.assert_allclose(got.sumexp[live], want["sumexp"][live], rtol=TOL, atol=0, err_msg=f"{name}: sumexp")
     np.testing.assert_allclose(got.total[live], want["total"][live], rtol=TOL, atol=0, err_msg=f"{name}: total")
     np.testing.assert_array_equal(got.drew.astype(np.int32), want["drew"], err_msg=f"{name}: drew")
-    clear = want["margin"] > TOL
-    bad = np.flatnonzero((got.token != want["token"]) & clear)
-    assert bad.size == 0, f"{name}: token mismatch on rows {bad[:8]} with margins {want['margin'][bad[:8]]}"
-    badk = np.flatnonzero((got.n_kept != want["n_kept"]) & clear & live)
+    w = getattr(got, "workload", None)
+    stoch = live & (want["drew"] == 1)
+    # ---- top-k kept set: unconditional
+    if w is not None:
+        want_k = got.want_topk
+        no_p = stoch & (w.top_p >= 1.0)
+        np.testing.assert_array_equal(got.n_kept[no_p], want["n_kept"][no_p], err_msg=f"{name}: top-k kept count")
+        with_p = stoch & (w.top_p < 1.0)
+        assert (got.n_kept[with_p] <= want_k["n_kept"][with_p]).all(), f"{name}: top-p kept more than top-k left"
+        if got.dump_ids is not None and got.dump_ids.shape[1] > 0:
+            order = np.argsort(np.where(stoch, want["margin"], np.inf))[:48]   # the rows closest to a boundary first
+            lf = w.logits_f32()
+            for r in order:
+                if not stoch[r] or got.n_kept[r] > got.dump_ids.shape[1]:
+                    continue
+                ids, _ = got.kept(int(r))
+                kw_row = dict(top_p=1.0) if w.top_p[r] < 1.0 else {}
+                _, probs = oracle_probs(got.oracle, w, int(r), logits_row=lf[r], **kw_row)
+                topk_ids = np.flatnonzero(probs > 0)
+                if w.top_p[r] >= 1.0:
+                    np.testing.assert_array_equal(ids, topk_ids, err_msg=f"{name}: top-k kept ids, row {r}")
+                else:
+                    assert np.isin(ids, topk_ids).all(), f"{name}: row {r} keeps ids outside of its top-k set"
+    # ---- top-p cut and drawn token: on rows whose own decision is clear
+    clear_p = want["margin_p"] > TOL
+    clear_tok = clear_p & (want["margin_cdf"] > TOL)
+    badk = np.flatnonzero((got.n_kept != want["n_kept"]) & clear_p & live)
     assert badk.size == 0, f"{name}: n_kept mismatch on rows {badk[:8]}"
-    # rows that sit on a boundary are rare; make sure the check is not vacuous
-    assert clear.mean() >= min_clear or len(clear) < 8, f"{name}: too many rows within tolerance of a boundary"
+    bad = np.flatnonzero((got.token != want["token"]) & clear_tok)
+    assert bad.size == 0, f"{name}: token mismatch on rows {bad[:8]} with margins {want['margin'][bad[:8]]}"
+    skipped = int((~clear_tok & stoch).sum())
+    print(f"[{name}] rows left out of the token comparison (decision within {TOL} of a boundary): "
+          f"{skipped} of {int(stoch.sum())} stochastic rows")
+    limit = max(1, int((1.0 - min_clear) * len(clear_tok))) if min_clear < 0.9 else max(1, len(clear_tok) // 100)
+    assert skipped <= limit, f"{name}: {skipped} rows within tolerance of a boundary (limit {limit})"
