@@ -119,8 +119,12 @@ def assert_close(got, want, name="", min_clear=0.9):
     assert badk.size == 0, f"{name}: n_kept mismatch on rows {badk[:8]}"
     bad = np.flatnonzero((got.token != want["token"]) & clear_tok)
     assert bad.size == 0, f"{name}: token mismatch on rows {bad[:8]} with margins {want['margin'][bad[:8]]}"
-    skipped = int((~clear_tok & stoch).sum())
-    print(f"[{name}] rows left out of the token comparison (decision within {TOL} of a boundary): "
-          f"{skipped} of {int(stoch.sum())} stochastic rows")
-    limit = max(1, int((1.0 - min_clear) * len(clear_tok))) if min_clear < 0.9 else max(1, len(clear_tok) // 100)
-    assert skipped <= limit, f"{name}: {skipped} rows within tolerance of a boundary (limit {limit})"
+    # Rows whose decision sits within TOL of a boundary may legitimately differ.  With hundreds of kept candidates a
+    # uniform lands that close to one of their CDF steps on a percent or two of the rows, so what is bounded is the
+    # number of rows that actually differ there, and the number that sit there is printed beside it.
+    near = ~clear_tok & stoch
+    differ = int(((got.token != want["token"]) & near).sum()) + int(((got.n_kept != want["n_kept"]) & ~clear_p & live).sum())
+    print(f"[{name}] stochastic rows with a decision within {TOL} of a boundary: {int(near.sum())} of {int(stoch.sum())}; "
+          f"of those, rows whose token or kept count differs from the oracle's: {differ}")
+    assert differ <= max(1, len(clear_tok) // 100), f"{name}: {differ} rows differ from the oracle inside the tolerance band"
+    assert near.mean() <= 1.0 - min_clear or len(near) < 8, f"{name}: {int(near.sum())} rows within tolerance of a boundary"
