@@ -621,6 +621,19 @@ __device__ __forceinline__ void p2_piece(StreamSmem& sm, const Raw<BF16>& raw, u
     }
 }
 
+// The loops below wait for their loads with nothing else to do (there are no registers for a second piece), so the
+// pieces they will need next are requested ahead of time as plain L2 prefetches: memory stays busy while the warps
+// compute, and the loads that follow find their lines in L2.  One 128-byte line per lane of the lower half-warp.
+#ifndef PGS_PF_DIST
+#define PGS_PF_DIST 2
+#endif
+template <bool BF16>
+__device__ __forceinline__ void prefetch_piece(const char* warp_piece) {
+    constexpr int LINES = S_REGION * (BF16 ? 2 : 4) / 128;   // 16 (f32) or 8 (bf16)
+    const int lane = threadIdx.x & 31;
+    if (lane < LINES) asm volatile("prefetch.global.L2 [%0];" ::"l"(warp_piece + lane * 128));
+}
+
 // pass 1 over the whole pieces n_full-1 .. 0; the thread's results go to sm.t_*[tid]
 template <bool BF16, bool MASK, bool STOCH>
 __device__ __noinline__ void pass1_whole(StreamSmem& sm) {
@@ -630,8 +643,12 @@ __device__ __noinline__ void pass1_whole(StreamSmem& sm) {
     const char* p = sm.pa.rowp + (size_t)lane_e0 * (BF16 ? 2 : 4) + (size_t)(n - 1u) * PB;
     float am = 0.0f, tmx = -INFINITY;
     uint32_t tqx = 0u;
+    const char* wp = sm.pa.rowp + (size_t)((threadIdx.x >> 5) * S_REGION) * (BF16 ? 2 : 4) + (size_t)(n - 1u) * PB;   // the warp's 512 logits of a piece
 #pragma unroll 1
-    for (uint32_t q = n; q-- > 0u; p -= PB) {
+    for (uint32_t d = 1; d < (uint32_t)PGS_PF_DIST && d < n; d++) prefetch_piece<BF16>(wp - (size_t)d * PB);
+#pragma unroll 1
+    for (uint32_t q = n; q-- > 0u; p -= PB, wp -= PB) {
+        if (q >= (uint32_t)PGS_PF_DIST) prefetch_piece<BF16>(wp - (size_t)PGS_PF_DIST * PB);
         Raw<BF16> b;
         raw_load<BF16>(b, p);
         p1_piece<BF16, MASK, false, STOCH>(sm, b, q, am, tmx, tqx);
@@ -648,8 +665,12 @@ __device__ __noinline__ void pass2_whole(StreamSmem& sm) {
     const char* p = sm.pa.rowp + (size_t)lane_e0 * (BF16 ? 2 : 4);
     FoldAcc fa;
     fa.accd = 0.0; fa.cur_n = 0ull; fa.cur_bb = 0u;
+    const char* wp = sm.pa.rowp + (size_t)((threadIdx.x >> 5) * S_REGION) * (BF16 ? 2 : 4);
 #pragma unroll 1
-    for (uint32_t q = 0u; q < n; q++, p += PB) {
+    for (uint32_t d = 1; d < (uint32_t)PGS_PF_DIST && d < n; d++) prefetch_piece<BF16>(wp + (size_t)d * PB);
+#pragma unroll 1
+    for (uint32_t q = 0u; q < n; q++, p += PB, wp += PB) {
+        if (q + (uint32_t)PGS_PF_DIST < n) prefetch_piece<BF16>(wp + (size_t)PGS_PF_DIST * PB);
         Raw<BF16> b;
         raw_load<BF16>(b, p);
         p2_piece<BF16, MASK, false>(sm, b, q, fa);
