@@ -330,8 +330,12 @@ def bench_tp(torch, dist, world, rank, dev, threads, steps=50):
     rec = {"rows": rows, "vocab": vocab, "n_shards": n_shards, "cand": cand, "steps": steps,
            "record_bytes": sampler.tp_record_bytes(cand)}
 
+    outs = sampler.tp_outputs(rows, dev)   # reused by every step: no allocation inside the timed loops
+
+    acc_out = (torch.zeros(seqs, dtype=torch.int32, device=dev), torch.zeros(seqs, dtype=torch.int32, device=dev))
+
     def finish(out):
-        return sampler.draft_accept(out["argmax"].view(seqs, pos), draft, stream_ptr=st)
+        return sampler.draft_accept(out["argmax"].view(seqs, pos), draft, stream_ptr=st, out=acc_out)
 
     if world > 1:
         lo, hi = column_shard(vocab, world, rank)
@@ -343,7 +347,7 @@ def bench_tp(torch, dist, world, rank, dev, threads, steps=50):
         def step_nccl(i):
             r = sampler.tp_partial(shards[i % len(shards)], vocab, world, rank, cand, temperature=t, stream_ptr=st)
             state["out"] = sampler.tp_merge(all_gather_records(r), vocab, world, rank, cand, temperature=t, top_p=tp_,
-                                            uniform=tu, stream_ptr=st)
+                                            uniform=tu, stream_ptr=st, out=outs)
             state["acc"] = finish(state["out"])
 
         def step_peer(i):
@@ -351,7 +355,7 @@ def bench_tp(torch, dist, world, rank, dev, threads, steps=50):
             sampler.tp_partial_push(shards[i % len(shards)], vocab, world, rank, cand, rec_ptrs, flag_ptrs, epoch,
                                     temperature=t, stream_ptr=st)
             state["out"] = sampler.tp_merge_wait(px.buf[par], px.flags[par], epoch, vocab, world, rank, cand, temperature=t,
-                                                 top_p=tp_, uniform=tu, stream_ptr=st)
+                                                 top_p=tp_, uniform=tu, stream_ptr=st, out=outs)
             state["acc"] = finish(state["out"])
 
         step_nccl(0); torch.cuda.synchronize()
@@ -379,7 +383,8 @@ def bench_tp(torch, dist, world, rank, dev, threads, steps=50):
                                stream_ptr=st)
 
         def merge(i):
-            state["out"] = sampler.tp_merge(recs, vocab, n_shards, 0, cand, temperature=t, top_p=tp_, uniform=tu, stream_ptr=st)
+            state["out"] = sampler.tp_merge(recs, vocab, n_shards, 0, cand, temperature=t, top_p=tp_, uniform=tu, stream_ptr=st,
+                                            out=outs)
             state["acc"] = finish(state["out"])
 
         for r in range(n_shards):

@@ -487,21 +487,27 @@ class Sampler:
         self._check(self._lib.pgs_tp_partial(self._h, C.byref(d), records.data_ptr(), self._stream(stream_ptr)))
         return records
 
+    @staticmethod
+    def tp_outputs(rows, dev):
+        """Output tensors of tp_merge / tp_merge_wait (pass them back in as `out` to reuse them)."""
+        import torch
+        return dict(token=torch.zeros(rows, dtype=torch.int32, device=dev),
+                    status=torch.full((rows,), -1, dtype=torch.int32, device=dev),
+                    drew=torch.zeros(rows, dtype=torch.uint8, device=dev),
+                    argmax=torch.zeros(rows, dtype=torch.int32, device=dev),
+                    gmax=torch.zeros(rows, dtype=torch.float32, device=dev),
+                    gsum=torch.zeros(rows, dtype=torch.float32, device=dev),
+                    total=torch.zeros(rows, dtype=torch.float32, device=dev),
+                    n_kept=torch.zeros(rows, dtype=torch.int32, device=dev))
+
     def tp_merge(self, records_all, vocab, n_shards, rank, cand, temperature=None, top_p=None, uniform=None,
-                 stream_ptr=None, top_k=None):
+                 stream_ptr=None, top_k=None, out=None):
         """Merge the all-gathered records [n_shards, rows, record_bytes] into tokens; returns a dict of
         CUDA tensors (token, status, drew, argmax, gmax, gsum, total, n_kept)."""
         import torch
         rows = records_all.shape[1]
         dev = records_all.device
-        out = dict(token=torch.zeros(rows, dtype=torch.int32, device=dev),
-                   status=torch.full((rows,), -1, dtype=torch.int32, device=dev),
-                   drew=torch.zeros(rows, dtype=torch.uint8, device=dev),
-                   argmax=torch.zeros(rows, dtype=torch.int32, device=dev),
-                   gmax=torch.zeros(rows, dtype=torch.float32, device=dev),
-                   gsum=torch.zeros(rows, dtype=torch.float32, device=dev),
-                   total=torch.zeros(rows, dtype=torch.float32, device=dev),
-                   n_kept=torch.zeros(rows, dtype=torch.int32, device=dev))
+        out = self.tp_outputs(rows, dev) if out is None else out
         o = TpOut(**{k: v.data_ptr() for k, v in out.items()})
         d = self._tp_desc(rows, vocab, n_shards, rank, cand, None, temperature, top_p, uniform, top_k=top_k)
         self._check(self._lib.pgs_tp_merge(self._h, C.byref(d), records_all.data_ptr(), C.byref(o),
@@ -548,20 +554,13 @@ class Sampler:
         self._check(self._lib.pgs_tp_exchange_status(self._h))
 
     def tp_merge_wait(self, records_all, flags, epoch, vocab, n_shards, rank, cand, temperature=None, top_p=None,
-                      uniform=None, stream_ptr=None, top_k=None):
+                      uniform=None, stream_ptr=None, top_k=None, out=None):
         """tp_merge preceded, on the device, by a bounded wait until all n_shards flags of this rank have
         reached `epoch`.  records_all [n_shards, rows, record_bytes] uint8, flags [n_shards] int32/uint32."""
         import torch
         rows = records_all.shape[1]
         dev = records_all.device
-        out = dict(token=torch.zeros(rows, dtype=torch.int32, device=dev),
-                   status=torch.full((rows,), -1, dtype=torch.int32, device=dev),
-                   drew=torch.zeros(rows, dtype=torch.uint8, device=dev),
-                   argmax=torch.zeros(rows, dtype=torch.int32, device=dev),
-                   gmax=torch.zeros(rows, dtype=torch.float32, device=dev),
-                   gsum=torch.zeros(rows, dtype=torch.float32, device=dev),
-                   total=torch.zeros(rows, dtype=torch.float32, device=dev),
-                   n_kept=torch.zeros(rows, dtype=torch.int32, device=dev))
+        out = self.tp_outputs(rows, dev) if out is None else out
         o = TpOut(**{k: v.data_ptr() for k, v in out.items()})
         d = self._tp_desc(rows, vocab, n_shards, rank, cand, None, temperature, top_p, uniform, top_k=top_k)
         self._check(self._lib.pgs_tp_merge_wait(self._h, C.byref(d), C.c_void_p(records_all.data_ptr()),
@@ -569,12 +568,15 @@ class Sampler:
                                                 self._stream(stream_ptr)))
         return out
 
-    def draft_accept(self, row_argmax, draft, stream_ptr=None):
-        """row_argmax, draft: int32 CUDA tensors [sequences, positions] -> (accepted, next)."""
+    def draft_accept(self, row_argmax, draft, stream_ptr=None, out=None):
+        """row_argmax, draft: int32 CUDA tensors [sequences, positions] -> (accepted, next); `out`: a pair of
+        int32 tensors [sequences] to write into instead of new ones."""
         import torch
         seqs, pos = row_argmax.shape
-        acc = torch.zeros(seqs, dtype=torch.int32, device=row_argmax.device)
-        nxt = torch.zeros(seqs, dtype=torch.int32, device=row_argmax.device)
+        if out is None:
+            out = (torch.zeros(seqs, dtype=torch.int32, device=row_argmax.device),
+                   torch.zeros(seqs, dtype=torch.int32, device=row_argmax.device))
+        acc, nxt = out
         self._check(self._lib.pgs_draft_accept(self._h, row_argmax.contiguous().data_ptr(),
                                                draft.contiguous().data_ptr(), seqs, pos, acc.data_ptr(),
                                                nxt.data_ptr(), self._stream(stream_ptr)))

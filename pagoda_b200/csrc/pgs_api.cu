@@ -13,7 +13,6 @@
 #include <vector>
 
 #include "pgs_args.cuh"
-#include "pgs_fused.cuh"
 #include "pgs_stream.cuh"
 #include "pgs_tp.cuh"
 
@@ -42,8 +41,6 @@ cudaError_t launch_tp_push(const TpArgs& a, cudaStream_t stream);
 cudaError_t launch_tp_merge(const TpArgs& a, const TpOut& o, cudaStream_t stream);
 cudaError_t launch_draft_accept(const uint32_t* row_argmax, const uint32_t* draft, uint32_t sequences,
                                 uint32_t positions, uint32_t* accepted, uint32_t* next, cudaStream_t stream);
-cudaError_t configure_finish();
-cudaError_t launch_finish(const RowArgs& a, const Handoff& ho, cudaStream_t stream);
 }  // namespace pgs
 
 static thread_local char g_create_error[256] = "";
@@ -72,15 +69,10 @@ struct pgs_handle {
     unsigned char* aux_host = nullptr;   // pinned
     unsigned char* aux_dev = nullptr;
     size_t aux_bytes = 0;
-    // rows the row kernel hands on: to the general kernel (work list), to the finish kernel (long candidate lists)
+    // rows the row kernel hands on to the general kernel (work list)
     uint32_t* work_rows = nullptr;
     uint32_t* work_count = nullptr;   // [2]
     uint32_t* tp_done = nullptr;      // CTAs finished in the current peer-store push
-    uint32_t* long_rows = nullptr;
-    uint32_t* long_count = nullptr;   // [2]
-    pgs::RowRec* recs = nullptr;      // [max_rows]
-    uint32_t* cand_id = nullptr;      // [max_rows x F_MCAP]
-    float* cand_x = nullptr;
     int exact = 0;
     // streaming row kernel: id -> count slots, shared memory and CTAs per SM, the gate's counter
     uint32_t stream_hash = 0, stream_cohort = 0;
@@ -152,7 +144,7 @@ static int destroy_impl(pgs_handle* h) {
     cudaFree(h->sx); cudaFree(h->sl_id); cudaFree(h->sl_p); cudaFree(h->sl_key);
     cudaFree(h->sh_key); cudaFree(h->sh_cnt); cudaFree(h->tables_dev);
     cudaFree(h->logits_stage); cudaFree(h->aux_dev); cudaFree(h->work_rows); cudaFree(h->work_count); cudaFree(h->tp_done); cudaFree(h->prof);
-    cudaFree(h->recs); cudaFree(h->cand_id); cudaFree(h->cand_x); cudaFree(h->p1_done); cudaFree(h->faulted); cudaFree(h->long_rows); cudaFree(h->long_count);
+    cudaFree(h->p1_done); cudaFree(h->faulted);
     if (h->aux_host) cudaFreeHost(h->aux_host);
     if (h->ev_step) cudaEventDestroy(h->ev_step);
     if (h->stream) cudaStreamDestroy(h->stream);
@@ -190,17 +182,9 @@ extern "C" int pgs_create(int device, uint32_t max_rows, uint32_t max_vocab, uin
         PGS_CUDA(nullptr, cudaEventCreateWithFlags(&h->ev_step, cudaEventDisableTiming));
         h->last_stream = h->stream;
         PGS_CUDA(nullptr, pgs::configure_general());
-        PGS_CUDA(nullptr, pgs::configure_finish());
         PGS_CUDA(nullptr, pgs::configure_tp());
         PGS_CUDA(nullptr, pgs::configure_score());
-        PGS_CUDA(nullptr, cudaMalloc(&h->recs, (size_t)max_rows * sizeof(pgs::RowRec)));
-        PGS_CUDA(nullptr, cudaMemsetAsync(h->recs, 0, (size_t)max_rows * sizeof(pgs::RowRec), h->stream));
-        PGS_CUDA(nullptr, cudaMalloc(&h->cand_id, (size_t)max_rows * pgs::F_MCAP * sizeof(uint32_t)));
-        PGS_CUDA(nullptr, cudaMalloc(&h->cand_x, (size_t)max_rows * pgs::F_MCAP * sizeof(float)));
         PGS_CUDA(nullptr, cudaMalloc(&h->work_rows, (size_t)max_rows * sizeof(uint32_t)));
-        PGS_CUDA(nullptr, cudaMalloc(&h->long_rows, (size_t)max_rows * sizeof(uint32_t)));
-        PGS_CUDA(nullptr, cudaMalloc(&h->long_count, 2 * sizeof(uint32_t)));
-        PGS_CUDA(nullptr, cudaMemsetAsync(h->long_count, 0, 2 * sizeof(uint32_t), h->stream));
         PGS_CUDA(nullptr, cudaMalloc(&h->work_count, 2 * sizeof(uint32_t)));
         PGS_CUDA(nullptr, cudaMemsetAsync(h->work_count, 0, 2 * sizeof(uint32_t), h->stream));
         PGS_CUDA(nullptr, cudaMalloc(&h->tp_done, sizeof(uint32_t)));
@@ -333,7 +317,7 @@ extern "C" int pgs_mask_table_free(pgs_handle* h, int32_t table_id) {
 namespace {
 
 // One step: the streaming row kernel serves every row it can and lists the others, which the general kernel then
-// processes; rows with long candidate lists are finished by the finish kernel.  In exact mode every row takes the
+// processes.  In exact mode every row takes the
 // general kernel.
 int launch_step(pgs_handle* h, pgs::RowArgs& a, cudaStream_t stream) {
     const uint32_t rows = a.rows;
@@ -356,20 +340,17 @@ int launch_step(pgs_handle* h, pgs::RowArgs& a, cudaStream_t stream) {
     sl.done_base = h->done_total; sl.gate_polls = 1u << 16;   // x 200 ns: gives up after about 13 ms
     sl.p1_done = h->p1_done;
     sl.work_rows = h->work_rows; sl.work_count = h->work_count;
-    sl.ho.recs = h->recs; sl.ho.cand_id = h->cand_id; sl.ho.cand_x = h->cand_x;
-    sl.ho.long_rows = h->long_rows; sl.ho.long_count = h->long_count;
     sl.prof = h->prof;
     const uint32_t resident = (uint32_t)h->stream_ctas * (uint32_t)h->sm_count;
     PGS_CUDA(h, pgs::launch_stream(a, sl, rows < resident ? rows : resident, stream));
     h->done_total += rows;
-    // Both lists are usually empty.  The two passes are set up while the row kernel still runs (programmatic stream
-    // serialization) and return at once when they find nothing listed.
-    if (!a.tp_records) PGS_CUDA(h, pgs::launch_finish(a, sl.ho, stream));   // (records are always written by the row's own CTA)
+    // The list is usually empty.  The pass over it is set up while the row kernel still runs (programmatic stream
+    // serialization) and returns at once when it finds nothing listed.
     pgs::RowArgs wl = a;
     wl.work_rows = h->work_rows;
     wl.work_count = h->work_count;
     PGS_CUDA(h, pgs::launch_general(wl, grid < 32u ? grid : 32u, stream));
-    h->counters.kernel_launches += a.tp_records ? 2 : 3;
+    h->counters.kernel_launches += 2;
     return PGS_OK;
 }
 

@@ -1,8 +1,8 @@
-// The reference's rule applied to a row's short candidate list: exact probabilities
+// The reference's rule applied to a row's candidate list by one CTA of any size: exact probabilities
 // exp((x - max) / t) / sum (sampler.rs:92-114), top-k threshold with every tie kept
 // (sampler.rs:116-128), top-p walk by probability descending / id ascending (sampler.rs:130-150),
-// then the total and the inverse-CDF walk in id order (sampler.rs:40-55).  Shared by the finish
-// kernel of the fused path and by the merge kernel of the vocabulary-sharded path.
+// then the total and the inverse-CDF walk in id order (sampler.rs:40-55).  Used by the streaming row
+// kernel for its own rows and by the merge kernel of the vocabulary-sharded path.
 #pragma once
 
 #include <cuda_runtime.h>
@@ -10,24 +10,25 @@
 
 #include "pgs_args.cuh"
 #include "pgs_block.cuh"
-#include "pgs_fused.cuh"
 
 namespace pgs {
 
-struct FinishSmem {
-    ReduceSmem rs;
-    unsigned long long exp_tab[32];
-    uint32_t m_id[F_MCAP];          // candidate ids, arrival order
-    float p[F_MCAP];                // probabilities, arrival order
-    uint32_t sid[F_MCAP];           // ids ascending
-    float sp[F_MCAP];               // probabilities in id order (zeroed when dropped)
-    float rp[F_MCAP];               // probabilities descending (ties: id ascending)
-    uint32_t rpos[F_MCAP];          // position in the id-ordered list of the entry at each rank
-    SeqSmem seq;
+constexpr int F_MCAP = 2048;       // longest candidate list (a power of two)
+constexpr int F_QUAD = 256;        // lists up to this length are ranked by counting, longer ones by sorting
+
+// Working arrays of the finish, in shared memory: each holds CAP entries (CAP a power of two >= 512, the
+// longest list the owner hands in).
+template <int CAP>
+struct FinishArraysT {
+    unsigned long long key[CAP];   // sort keys
+    uint32_t sid[CAP];             // ids ascending
+    float sp[CAP];                 // probabilities in id order (zeroed when dropped)
+    float rp[CAP];                 // probabilities descending (ties: id ascending)
+    uint32_t rpos[CAP];            // position in the id-ordered list of the entry at each rank
+    float fp[CAP];                 // running sums of the serial folds
     uint32_t n_live;
-    float bcast_f;
-    int bcast_i;
 };
+using FinishArrays = FinishArraysT<F_MCAP>;
 
 // Exact left fold of n shared-memory floats, called by one warp: returns the total and leaves every
 // running value in pre[0..n).  One lane does the additions: the loads do not depend on the running value, so
@@ -67,121 +68,59 @@ __device__ __forceinline__ int warp_find(const float* pre, int n, int mode, floa
     return -1;
 }
 
-
-// Called by every thread of a 1024-thread CTA.  cand_id / cand_x: the row's n <= F_MCAP candidates
-// (any order); V: the full vocabulary size (the CDF walk falls through to V - 1, sampler.rs:54).
-__device__ __forceinline__ void finish_row(FinishSmem& sm, const RowArgs& a, uint32_t row, uint32_t V,
-                                           const uint32_t* cand_id, const float* cand_x, uint32_t n, float m,
-                                           float t, float S, uint32_t top_k, float top_p, float u01,
-                                           uint32_t amax, int status) {
-    const int tid = threadIdx.x;
-    if (tid < 32) sm.exp_tab[tid] = kExp2TableDev[tid];
-    const bool use_p = !(top_p >= 1.0f);
-    const bool norm = S > 1e-9f;
+// Ascending bitonic sort of n_pad (a power of two) 64-bit keys in shared memory by a CTA of T threads.
+template <int T>
+__device__ __forceinline__ void cta_bitonic_sort(unsigned long long* keys, uint32_t n_pad) {
+    const uint32_t tid = threadIdx.x;
     __syncthreads();
-    for (uint32_t j = tid; j < n; j += NT) {
-        sm.m_id[j] = cand_id[j];
-        const float e = softmax_num(cand_x[j], m, t, sm.exp_tab);   // exact expf
-        sm.p[j] = norm ? fdiv(e, S) : e;
-    }
-    __syncthreads();
-    // rank every candidate by id and by (probability descending, id ascending)
-    if (n <= 256u) {
-        for (uint32_t j = tid; j < n; j += NT) {
-            const uint32_t idj = sm.m_id[j];
-            const float pj = sm.p[j];
-            uint32_t r_id = 0, r_p = 0;
-#pragma unroll 8
-            for (uint32_t o = 0; o < n; o++) {   // broadcast loads, independent of one another: requested in batches
-                const uint32_t ido = sm.m_id[o];
-                const float po = sm.p[o];
-                r_id += ido < idj;
-                r_p += (po > pj) || (po == pj && ido < idj);
+    for (uint32_t k = 2; k <= n_pad; k <<= 1) {
+        for (uint32_t j = k >> 1; j > 0; j >>= 1) {
+            for (uint32_t i = tid; i < n_pad / 2; i += T) {   // the i-th pair of this step
+                const uint32_t lo = ((i & ~(j - 1u)) << 1) | (i & (j - 1u)), hi = lo | j;
+                const unsigned long long a = keys[lo], b = keys[hi];
+                const bool up = (lo & k) == 0u;
+                if ((a > b) == up) { keys[lo] = b; keys[hi] = a; }
             }
-            sm.sid[r_id] = idj;
-            sm.sp[r_id] = pj;
-            sm.rp[r_p] = pj;
-            sm.rpos[r_p] = r_id;
+            __syncthreads();
         }
-    } else {
-        // long lists: two bitonic sorts of 64-bit keys in place of the quadratic counting.  m_id and p are
-        // adjacent and together hold F_MCAP keys.
-        static_assert(offsetof(FinishSmem, p) == offsetof(FinishSmem, m_id) + sizeof(uint32_t) * F_MCAP, "key space");
-        unsigned long long* keys = reinterpret_cast<unsigned long long*>(sm.m_id);
-        uint32_t npad = 512;
-        while (npad < n) npad <<= 1;
-        uint32_t idr[F_MCAP / NT];
-        float pr[F_MCAP / NT];
-#pragma unroll
-        for (int u = 0; u < F_MCAP / NT; u++) {
-            const uint32_t j = tid + u * NT;
-            idr[u] = j < n ? sm.m_id[j] : 0u;
-            pr[u] = j < n ? sm.p[j] : 0.0f;
-        }
-        __syncthreads();
-#pragma unroll
-        for (int u = 0; u < F_MCAP / NT; u++) {   // by id ascending; the padding sorts to the end
-            const uint32_t j = tid + u * NT;
-            if (j < npad) keys[j] = j < n ? ((unsigned long long)idr[u] << 32) | f2u(pr[u]) : ~0ull;
-        }
-        bitonic_sort(keys, (int)npad, keys);
-        for (uint32_t j = tid; j < n; j += NT) { sm.sid[j] = (uint32_t)(keys[j] >> 32); sm.sp[j] = u2f((uint32_t)keys[j]); }
-        __syncthreads();
-        for (uint32_t j = tid; j < npad; j += NT)   // by (p, position descending) ascending = rank descending; padding first
-            keys[j] = j < n ? ((unsigned long long)f2u(sm.sp[j]) << 32) | (0xffffffffu - j) : 0ull;
-        bitonic_sort(keys, (int)npad, keys);
-        for (uint32_t r = tid; r < n; r += NT) {
-            const unsigned long long k = keys[npad - 1u - r];
-            sm.rp[r] = u2f((uint32_t)(k >> 32));
-            sm.rpos[r] = 0xffffffffu - (uint32_t)k;
-        }
-        __syncthreads();
     }
-    if (tid == 0) sm.n_live = 0;
+}
+
+// Second half of the finish, from ranked candidates: f.sid / f.sp hold the n candidates in id order, f.rp / f.rpos
+// the same by (probability descending, id ascending), f.n_live is zero.  Called by every thread; ends with the row's
+// outputs written.
+template <int T, class FA>
+__device__ __forceinline__ void cta_finish_ranked(FA& f, const RowArgs& a, uint32_t row, uint32_t V, uint32_t n, float m,
+                                                  float S, uint32_t top_k, float top_p, float u01, uint32_t amax, int status) {
+    const int tid = threadIdx.x, lane = tid & 31;
     __syncthreads();
-    // top-k: every tie at the k-th probability survives; entries with zero probability never matter
-    {
-        const float thr = (top_k != 0u && top_k <= n) ? sm.rp[top_k - 1] : 0.0f;
-        for (uint32_t j = tid; j < n; j += NT) {
-            const bool live = sm.rp[j] >= thr && sm.rp[j] > 0.0f;
-            const bool next_live = j + 1 < n && sm.rp[j + 1] >= thr && sm.rp[j + 1] > 0.0f;
-            if (live && !next_live) sm.n_live = j + 1;
+    {   // top-k: every tie at the k-th probability survives; entries with zero probability never matter
+        const float thr = (top_k != 0u && top_k <= n) ? f.rp[top_k - 1] : 0.0f;
+        for (uint32_t j = tid; j < n; j += T) {
+            const bool live = f.rp[j] >= thr && f.rp[j] > 0.0f;
+            const bool next_live = j + 1 < n && f.rp[j + 1] >= thr && f.rp[j + 1] > 0.0f;
+            if (live && !next_live) f.n_live = j + 1;
         }
     }
     __syncthreads();
-    const uint32_t n_live = sm.n_live;
-    // top-p walk in ranked order
+    if (tid >= 32) return;
+    // one warp: top-p walk in ranked order, then total and inverse-CDF pick in id order
+    const uint32_t n_live = f.n_live;
     uint32_t keep = n_live;
-    if (use_p && n_live > 0) {
-        int found = -1;
-        if (tid < 32) {   // one lane folds, at four cycles per term; the parallel emulation only pays beyond this size
-            warp_prefix(sm.rp, (int)n_live, sm.p);   // sm.p is free once the candidates are ranked
-            found = warp_find(sm.p, (int)n_live, SEQ_FIND_GE, top_p);
-            if (tid == 0) sm.bcast_i = found;
-        }
-        __syncthreads();
-        found = sm.bcast_i;
+    if (!(top_p >= 1.0f) && n_live > 0) {
+        warp_prefix(f.rp, (int)n_live, f.fp);
+        const int found = warp_find(f.fp, (int)n_live, SEQ_FIND_GE, top_p);
         if (found >= 0) keep = (uint32_t)found + 1;
     }
-    __syncthreads();
-    for (uint32_t j = keep + tid; j < n; j += NT) sm.sp[sm.rpos[j]] = 0.0f;
-    __syncthreads();
-    // total and inverse-CDF pick in id order
-    float total;
+    for (uint32_t j = keep + lane; j < n; j += 32) f.sp[f.rpos[j]] = 0.0f;
+    __syncwarp();
+    const float total = warp_prefix(f.sp, (int)n, f.fp);
     int pick = -1;
-    if (tid < 32) {
-        const float tt = warp_prefix(sm.sp, (int)n, sm.p);
-        int f = -1;
-        if (tt > 1e-9f) f = warp_find(sm.p, (int)n, SEQ_FIND_GT, fmul(u01, tt));
-        if (tid == 0) { sm.bcast_f = tt; sm.bcast_i = f; }
-    }
-    __syncthreads();
-    total = sm.bcast_f;
-    pick = sm.bcast_i;
-    if (tid == 0) {
+    if (total > 1e-9f) pick = warp_find(f.fp, (int)n, SEQ_FIND_GT, fmul(u01, total));
+    if (lane == 0) {
         uint32_t token = amax;
         int drew = 0;
-        if (total > 1e-9f) { token = pick >= 0 ? sm.sid[pick] : V - 1; drew = 1; }
+        if (total > 1e-9f) { token = pick >= 0 ? f.sid[pick] : V - 1; drew = 1; }
         a.token[row] = token; a.status[row] = status;
         if (a.drew) a.drew[row] = (uint8_t)drew;
         if (a.argmax) a.argmax[row] = amax;
@@ -191,20 +130,82 @@ __device__ __forceinline__ void finish_row(FinishSmem& sm, const RowArgs& a, uin
     }
     if (a.n_kept || a.dump_ids || a.dump_probs) {   // diagnostics: the kept set in id order
         uint32_t done = 0;
-        for (uint32_t base = 0; base < n; base += NT) {
-            const uint32_t j = base + tid;
-            const uint32_t kept = (j < n && sm.sp[j] > 0.0f) ? 1u : 0u;
-            uint32_t tot;
-            const uint32_t at = done + block_excl_scan_u32(kept, &tot, sm.rs);
+        for (uint32_t base = 0; base < n; base += 32) {
+            const uint32_t j = base + lane;
+            const bool kept = j < n && f.sp[j] > 0.0f;
+            const unsigned mask = __ballot_sync(FULL, kept);
+            const uint32_t at = done + __popc(mask & ((1u << lane) - 1u));
             if (kept && at < a.dump_cap) {
-                if (a.dump_ids) a.dump_ids[(size_t)row * a.dump_cap + at] = sm.sid[j];
-                if (a.dump_probs) a.dump_probs[(size_t)row * a.dump_cap + at] = sm.sp[j];
+                if (a.dump_ids) a.dump_ids[(size_t)row * a.dump_cap + at] = f.sid[j];
+                if (a.dump_probs) a.dump_probs[(size_t)row * a.dump_cap + at] = f.sp[j];
             }
-            done += tot;
+            done += __popc(mask);
         }
-        if (tid == 0 && a.n_kept) a.n_kept[row] = done;
+        if (lane == 0 && a.n_kept) a.n_kept[row] = done;
     }
 }
 
+
+// Candidates of one row -> token.  Called by every thread of a CTA of T threads (T >= F_QUAD, a multiple of 32)
+// with a barrier in front; cand_id / cand_x: the row's n <= F_MCAP candidates in any order (shared memory outside
+// of `f`); V: the full vocabulary size (the CDF walk falls through to V - 1, sampler.rs:54).  Ends with the row's
+// outputs written; the caller needs a barrier before it reuses `f` or the candidate arrays.
+template <int T, class FA>
+__device__ __forceinline__ void cta_finish(FA& f, const unsigned long long* exp_tab, const RowArgs& a, uint32_t row,
+                                           uint32_t V, const uint32_t* cand_id, const float* cand_x, uint32_t n, float m, float t,
+                                           float S, uint32_t top_k, float top_p, float u01, uint32_t amax, int status) {
+    static_assert(T >= F_QUAD && T % 32 == 0, "one thread per candidate of a short list");
+    const int tid = threadIdx.x;
+    const bool norm = S > 1e-9f;
+    if (tid == 0) f.n_live = 0u;
+    if (n <= (uint32_t)F_QUAD) {
+        // short list: every candidate counts the candidates in front of it, by id and by (probability descending,
+        // id ascending)
+        uint32_t my_id = 0u;
+        float my_p = 0.0f;
+        if ((uint32_t)tid < n) {
+            my_id = cand_id[tid];
+            const float e = softmax_num(cand_x[tid], m, t, exp_tab);   // exact expf
+            my_p = norm ? fdiv(e, S) : e;
+            f.key[tid] = ((unsigned long long)f2u(my_p) << 32) | (unsigned long long)(0xffffffffu - my_id);   // p >= 0
+        }
+        __syncthreads();
+        if ((uint32_t)tid < n) {
+            const unsigned long long kj = f.key[tid];
+            uint32_t r_id = 0, r_p = 0;
+#pragma unroll 8
+            for (uint32_t o = 0; o < n; o++) {   // broadcast loads, independent of one another
+                const unsigned long long ko = f.key[o];
+                r_p += ko > kj;
+                r_id += (uint32_t)ko > (uint32_t)kj;   // larger ~id = smaller id
+            }
+            f.sid[r_id] = my_id; f.sp[r_id] = my_p; f.rp[r_p] = my_p; f.rpos[r_p] = r_id;
+        }
+    } else {
+        // long list: sorted by id, then by (probability, position) -- two sorts of 64-bit keys
+        uint32_t npad = 512;
+        while (npad < n) npad <<= 1;
+        for (uint32_t j = tid; j < npad; j += T) {
+            unsigned long long k = ~0ull;   // the padding sorts to the end
+            if (j < n) {
+                const float e = softmax_num(cand_x[j], m, t, exp_tab);
+                k = ((unsigned long long)cand_id[j] << 32) | f2u(norm ? fdiv(e, S) : e);
+            }
+            f.key[j] = k;
+        }
+        cta_bitonic_sort<T>(f.key, npad);
+        for (uint32_t j = tid; j < n; j += T) { f.sid[j] = (uint32_t)(f.key[j] >> 32); f.sp[j] = u2f((uint32_t)f.key[j]); }
+        __syncthreads();
+        for (uint32_t j = tid; j < npad; j += T)   // ascending by (p, position descending) = rank descending; padding first
+            f.key[j] = j < n ? ((unsigned long long)f2u(f.sp[j]) << 32) | (0xffffffffu - j) : 0ull;
+        cta_bitonic_sort<T>(f.key, npad);
+        for (uint32_t r = tid; r < n; r += T) {
+            const unsigned long long k = f.key[npad - 1u - r];
+            f.rp[r] = u2f((uint32_t)(k >> 32));
+            f.rpos[r] = 0xffffffffu - (uint32_t)k;
+        }
+    }
+    cta_finish_ranked<T, FA>(f, a, row, V, n, m, S, top_k, top_p, u01, amax, status);
+}
 
 }  // namespace pgs

@@ -58,10 +58,8 @@ constexpr int S_NCELL = 4;               // running maxima per thread (piece num
 constexpr int S_CELLS = S_NCELL * SNT;   // per-thread maxima that bound the top-k threshold
 constexpr int S_NB = 1024;               // buckets of their histogram
 constexpr int S_BPT = S_NB / SNT;        // buckets per thread
-constexpr int S_FCAP = 256;              // candidates finished inside this kernel
 constexpr int S_RPT = S_MAX_REGIONS / SNT;   // regions per thread in the CTA-wide walks over regions
 constexpr uint32_t S_NIL = 0xffffffffu;
-static_assert(S_FCAP <= SNT, "one thread per candidate in the finish");
 static_assert(SNW <= 32, "warp slots are combined by one warp");
 
 // Everything the kernel needs to know about a row, read and validated by one thread while the CTA still works
@@ -85,12 +83,6 @@ struct PassArgs {
     uint32_t eos_piece, eos_tid, eos_sub;
 };
 
-struct FinishScratch {   // at most S_FCAP candidates
-    unsigned long long fkey[S_FCAP];
-    float fp[S_FCAP], fsp[S_FCAP], frp[S_FCAP];
-    uint32_t fsid[S_FCAP], frpos[S_FCAP];
-};
-
 struct StreamSmem {
     SRowCtl ctl[2];
     PassArgs pa;
@@ -99,33 +91,39 @@ struct StreamSmem {
     uint32_t scan_u[SNW];
     float scan_f[SNW];
     double wacc[SNW];               // per-warp share of the fold
-    uint32_t cand_n, sel_bucket, n_live, amax;
-    uint32_t hist[S_NB];
-    float cell[S_CELLS];             // [S_NCELL][SNT]
-    float t_am[SNT], t_max[SNT];     // per-thread results of pass 1 over the whole pieces
-    uint32_t t_q[SNT];
+    uint32_t cand_n, sel_bucket, amax;
     uint32_t cand_id[F_MCAP];
     float cand_x[F_MCAP];
-    // per warp region of the row (512 consecutive logits): pass 1 leaves the warp's maximum and the plain sum of
-    // its numerators relative to it; then the binade's lower end the fold has there (0 = fold this region the
-    // careful way) and the estimate of the running value at its start.  While the history is indexed, reg_a
-    // counts the distinct history ids per region.
-    float reg_a[S_MAX_REGIONS], reg_b[S_MAX_REGIONS];
-    float reg_t[S_MAX_REGIONS];      // a logit below this adds exactly nothing to the fold in this region
-    // distinct history ids grouped by region: those of region r are the entries rs[r] .. rs[r + 1]
-    uint16_t rs[S_MAX_REGIONS + 2];
-    uint32_t pmask[S_MAX_REGIONS / 32];   // bit r: region r holds history ids
-    uint16_t pid[S_MAX_HASH / 2];    // position inside the region
-    uint32_t pval[S_MAX_HASH / 2];   // count, then (after pass 1) the bits of the penalised logit
     long long prof_acc[16];
-    // one area, three uses: id -> count table while the history is indexed (hkey[H], hcnt[H]); per-warp staging of
-    // a piece while penalties are applied to it (SNW x S_REGION floats); scratch of the finish
-    union alignas(16) {
-        uint32_t hash[2 * S_MAX_HASH];
-        float stage[SNW * S_REGION];
-        FinishScratch fin;
+    // Two lives of one area: the tables of a row while it streams, and the arrays of the finish once its
+    // candidates are known (nothing of the first is needed by then).
+    union {
+        struct {
+            uint32_t hist[S_NB];
+            float cell[S_CELLS];             // [S_NCELL][SNT]
+            float t_am[SNT], t_max[SNT];     // per-thread results of pass 1 over the whole pieces
+            uint32_t t_q[SNT];
+            // per warp region of the row (512 consecutive logits): pass 1 leaves the warp's maximum and the plain sum
+            // of its numerators relative to it; then the binade's lower end the fold has there (0 = fold this region the
+            // careful way) and the estimate of the running value at its start.  While the history is indexed, reg_a
+            // counts the distinct history ids per region.
+            float reg_a[S_MAX_REGIONS], reg_b[S_MAX_REGIONS];
+            float reg_t[S_MAX_REGIONS];      // a logit below this adds exactly nothing to the fold in this region
+            // distinct history ids grouped by region: those of region r are the entries rs[r] .. rs[r + 1]
+            uint16_t rs[S_MAX_REGIONS + 2];
+            uint32_t pmask[S_MAX_REGIONS / 32];   // bit r: region r holds history ids
+            uint16_t pid[S_MAX_HASH / 2];    // position inside the region
+            uint32_t pval[S_MAX_HASH / 2];   // count, then (after pass 1) the bits of the penalised logit
+            // id -> count table while the history is indexed (hkey[H], hcnt[H]), then per-warp staging of a piece
+            // while penalties are applied to it (SNW x S_REGION floats)
+            union alignas(16) {
+                uint32_t hash[2 * S_MAX_HASH];
+                float stage[SNW * S_REGION];
+            } u;
+        };
+        FinishArrays fin;
         unsigned long long tpkey[SNT];   // vocabulary-sharded mode: one candidate per thread while a record is ranked
-    } u;
+    };
 };
 
 static_assert(sizeof(StreamSmem) <= 113 * 1024, "two CTAs per SM");
@@ -269,85 +267,6 @@ __device__ __forceinline__ void sprepare_row(const RowArgs& a, const StreamLaunc
     c.kind = bad ? 1u : defer ? 2u : 0u;
 }
 
-// Candidates of one row -> token, by the threads 0..n-1 of the CTA and then its first warp (n <= S_FCAP).
-// Called by every thread; the caller has a barrier in front.
-__device__ __forceinline__ void sfinish_row(StreamSmem& sm, const RowArgs& a, uint32_t row, uint32_t n, float m, float t,
-                                            float S, uint32_t top_k, float top_p, float u01, uint32_t amax, int status) {
-    FinishScratch& fs = sm.u.fin;
-    const int tid = threadIdx.x, lane = tid & 31;
-    const uint32_t V = a.vocab;
-    const bool norm = S > 1e-9f;
-    uint32_t my_id = 0u;
-    float my_p = 0.0f;
-    if (tid == 0) sm.n_live = 0u;
-    if ((uint32_t)tid < n) {
-        my_id = sm.cand_id[tid];
-        const float e = softmax_num(sm.cand_x[tid], m, t, sm.exp_tab);   // exact expf
-        my_p = norm ? fdiv(e, S) : e;
-        fs.fkey[tid] = ((unsigned long long)f2u(my_p) << 32) | (unsigned long long)(0xffffffffu - my_id);   // p >= 0
-    }
-    __syncthreads();
-    if ((uint32_t)tid < n) {   // rank by id and by (probability descending, id ascending)
-        const unsigned long long kj = fs.fkey[tid];
-        uint32_t r_id = 0, r_p = 0;
-#pragma unroll 8
-        for (uint32_t o = 0; o < n; o++) {   // broadcast loads, independent of one another
-            const unsigned long long ko = fs.fkey[o];
-            r_p += ko > kj;
-            r_id += (uint32_t)ko > (uint32_t)kj;   // larger ~id = smaller id
-        }
-        fs.fsid[r_id] = my_id; fs.fsp[r_id] = my_p; fs.frp[r_p] = my_p; fs.frpos[r_p] = r_id;
-    }
-    __syncthreads();
-    if ((uint32_t)tid < n) {   // top-k: every tie at the k-th probability survives; zeros never matter
-        const float thr = (top_k != 0u && top_k <= n) ? fs.frp[top_k - 1] : 0.0f;
-        const bool live = fs.frp[tid] >= thr && fs.frp[tid] > 0.0f;
-        const bool next_live = (uint32_t)tid + 1 < n && fs.frp[tid + 1] >= thr && fs.frp[tid + 1] > 0.0f;
-        if (live && !next_live) sm.n_live = tid + 1;
-    }
-    __syncthreads();
-    if (tid >= 32) return;
-    // one warp: top-p walk in ranked order, then total and inverse-CDF pick in id order
-    const uint32_t n_live = sm.n_live;
-    uint32_t keep = n_live;
-    if (!(top_p >= 1.0f) && n_live > 0) {
-        warp_prefix(fs.frp, (int)n_live, fs.fp);
-        const int found = warp_find(fs.fp, (int)n_live, SEQ_FIND_GE, top_p);
-        if (found >= 0) keep = (uint32_t)found + 1;
-    }
-    for (uint32_t j = keep + lane; j < n; j += 32) fs.fsp[fs.frpos[j]] = 0.0f;
-    __syncwarp();
-    const float total = warp_prefix(fs.fsp, (int)n, fs.fp);
-    int pick = -1;
-    if (total > 1e-9f) pick = warp_find(fs.fp, (int)n, SEQ_FIND_GT, fmul(u01, total));
-    if (lane == 0) {
-        uint32_t token = amax;
-        int drew = 0;
-        if (total > 1e-9f) { token = pick >= 0 ? fs.fsid[pick] : V - 1; drew = 1; }
-        a.token[row] = token; a.status[row] = status;
-        if (a.drew) a.drew[row] = (uint8_t)drew;
-        if (a.argmax) a.argmax[row] = amax;
-        if (a.row_max) a.row_max[row] = m;
-        if (a.sumexp) a.sumexp[row] = S;
-        if (a.total) a.total[row] = total;
-    }
-    if (a.n_kept || a.dump_ids || a.dump_probs) {   // diagnostics: the kept set in id order
-        uint32_t done = 0;
-        for (uint32_t base = 0; base < n; base += 32) {
-            const uint32_t j = base + lane;
-            const bool kept = j < n && fs.fsp[j] > 0.0f;
-            const unsigned mask = __ballot_sync(FULL, kept);
-            const uint32_t at = done + __popc(mask & ((1u << lane) - 1u));
-            if (kept && at < a.dump_cap) {
-                if (a.dump_ids) a.dump_ids[(size_t)row * a.dump_cap + at] = fs.fsid[j];
-                if (a.dump_probs) a.dump_probs[(size_t)row * a.dump_cap + at] = fs.fsp[j];
-            }
-            done += __popc(mask);
-        }
-        if (lane == 0 && a.n_kept) a.n_kept[row] = done;
-    }
-}
-
 // Vocabulary-sharded mode: the candidates of one row (n <= SNT, one per thread) -> this shard's record: the
 // tp_cand largest by (logit descending, id ascending) behind the head.  Called by every thread; the caller has a
 // barrier in front.
@@ -359,13 +278,13 @@ __device__ __forceinline__ void semit_tp(StreamSmem& sm, const RowArgs& a, uint3
     uint32_t* rid = reinterpret_cast<uint32_t*>(rx + a.tp_cand);
     const uint32_t want = a.tp_cand < n ? a.tp_cand : n;
     if ((uint32_t)tid < n)
-        sm.u.tpkey[tid] = ((unsigned long long)order_key(sm.cand_x[tid]) << 32) | (unsigned long long)(0xffffffffu - sm.cand_id[tid]);
+        sm.tpkey[tid] = ((unsigned long long)order_key(sm.cand_x[tid]) << 32) | (unsigned long long)(0xffffffffu - sm.cand_id[tid]);
     __syncthreads();
     if ((uint32_t)tid < n) {
-        const unsigned long long kj = sm.u.tpkey[tid];
+        const unsigned long long kj = sm.tpkey[tid];
         uint32_t r = 0;
 #pragma unroll 8
-        for (uint32_t o = 0; o < n; o++) r += sm.u.tpkey[o] > kj;
+        for (uint32_t o = 0; o < n; o++) r += sm.tpkey[o] > kj;
         if (r < want) { rx[r] = sm.cand_x[tid]; rid[r] = a.id_base + sm.cand_id[tid]; }
     }
     if (tid == 0) tp_write_head(a, row, m, S, want, ROW_OK, amax);
@@ -1036,21 +955,9 @@ __global__ void __launch_bounds__(SNT, 2) stream_row_kernel(const RowArgs a, con
                 continue;
             }
             semit_tp(sm, a, row, n_cand, m, S, amax);
-        } else if (n_cand <= (uint32_t)S_FCAP) {
-            sfinish_row(sm, a, row, n_cand, m, t, S, top_k, ctl.top_p, ctl.u01, amax, status);
         } else {
-            // long lists: the finish kernel takes the row from here
-#pragma unroll 1
-            for (uint32_t j = tid; j < n_cand; j += SNT) {
-                sl.ho.cand_id[(size_t)row * F_MCAP + j] = sm.cand_id[j];
-                sl.ho.cand_x[(size_t)row * F_MCAP + j] = sm.cand_x[j];
-            }
-            if (writer) {
-                RowRec& rec = sl.ho.recs[row];
-                rec.n_cand = n_cand; rec.amax = amax; rec.status = status; rec.m = m; rec.t = t; rec.S = S;
-                __threadfence();   // the record and the candidates before the list entry
-                sl.ho.long_rows[atomicAdd(sl.ho.long_count, 1u)] = row;
-            }
+            cta_finish<SNT>(sm.fin, sm.exp_tab, a, row, V, sm.cand_id, sm.cand_x, n_cand, m, t, S, top_k, ctl.top_p, ctl.u01, amax,
+                            status);
         }
         PGS_STICK(5);   // finish
     }

@@ -3,7 +3,6 @@
 
 #include <stdint.h>
 
-#include "pgs_fused.cuh"
 
 namespace pgs {
 
@@ -19,7 +18,6 @@ struct StreamLaunch {
     uint32_t* p1_done;          // rows that have finished their first pass, counted over all launches
     uint32_t* work_rows;        // rows handed to the general kernel
     uint32_t* work_count;
-    Handoff ho;                 // rows with long candidate lists go to the finish kernel
     long long* prof;            // optional phase timers, [gridDim.x x 16]
 };
 

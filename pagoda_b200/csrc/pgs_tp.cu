@@ -64,24 +64,31 @@ __global__ void __launch_bounds__(256) tp_push_kernel(const TpArgs a) {
     }
 }
 
+constexpr int TP_MT = 256;    // threads of the merge kernel
+constexpr int TP_MCAP = TP_MAX_SHARDS * 128;   // candidates of all shards together (cand <= 128)
+
 struct TpMergeSmem {
-    FinishSmem fin;
-    uint32_t cid[F_MCAP];
-    float cx[F_MCAP];
+    FinishArraysT<TP_MCAP> fin;
+    unsigned long long exp_tab[32];
+    uint32_t cid[TP_MCAP];
+    float cx[TP_MCAP];
     float M, S;
     uint32_t amax, n;
     int fault;   // the row's status when it is not ROW_OK
+    uint32_t start[TP_MAX_SHARDS + 1];   // where each shard's candidates begin in cid / cx
+    TpRecHead hd[TP_MAX_SHARDS];
+    int unsorted;
 };
 
 
-__global__ void __launch_bounds__(NT, 1) tp_merge_kernel(const TpArgs a, const TpOut o) {
+__global__ void __launch_bounds__(TP_MT, 4) tp_merge_kernel(const TpArgs a, const TpOut o) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     TpMergeSmem& sm = *reinterpret_cast<TpMergeSmem*>(smem_raw);
     const int tid = threadIdx.x;
     const uint32_t row = blockIdx.x;
     const float temp = a.temperature ? a.temperature[row] : 0.0f;
     const float t = fmaxf(temp, 1e-9f);
-    if (tid < 32) sm.fin.exp_tab[tid] = kExp2TableDev[tid];
+    if (tid < 32) sm.exp_tab[tid] = kExp2TableDev[tid];
     if (a.flags) {   // peer-store exchange: wait (bounded, about a second) until every shard has raised its flag
         if (tid == 0) {
             int late = 0;
@@ -108,13 +115,30 @@ __global__ void __launch_bounds__(NT, 1) tp_merge_kernel(const TpArgs a, const T
         return reinterpret_cast<const TpRecHead*>(a.records + ((size_t)r * a.rows + row) * a.rec_bytes);
     };
     const uint32_t top_k = a.top_k ? a.top_k[row] : 0u;
+    // every record slot of the row is requested at once (one trip to memory): the heads by the first threads, the
+    // candidate slots one or two per thread; which of the slots are filled is known once the heads are in
+    if ((uint32_t)tid < a.n_shards) sm.hd[tid] = *rec(tid);
+    constexpr int SLOTS = (TP_MCAP + TP_MT - 1) / TP_MT;
+    float gx[SLOTS];
+    uint32_t gid[SLOTS];
+#pragma unroll
+    for (int u = 0; u < SLOTS; u++) {
+        const uint32_t c = (uint32_t)tid + u * TP_MT;
+        gx[u] = 0.0f; gid[u] = 0u;
+        if (c < a.n_shards * a.cand) {
+            const float* rx = reinterpret_cast<const float*>(rec(c / a.cand) + 1);
+            gx[u] = rx[c % a.cand];
+            gid[u] = reinterpret_cast<const uint32_t*>(rx + a.cand)[c % a.cand];
+        }
+    }
+    __syncthreads();
     if (tid == 0) {
         float M = -INFINITY;
         int fault = (top_k > a.cand) ? ROW_BAD_PARAM : ROW_OK;   // a record holds the shard's `cand` largest, no more
         bool nonfinite = false, dead = false;
         for (uint32_t r = 0; r < a.n_shards; r++) {
-            const float mr = rec(r)->m;
-            const uint32_t st = rec(r)->n_status >> 24;
+            const float mr = sm.hd[r].m;
+            const uint32_t st = sm.hd[r].n_status >> 24;
             if (st == (uint32_t)ROW_BAD_PARAM) fault = ROW_BAD_PARAM;
             nonfinite |= st == (uint32_t)ROW_NONFINITE || mr != mr;
             dead |= st == (uint32_t)ROW_DEAD;
@@ -126,31 +150,33 @@ __global__ void __launch_bounds__(NT, 1) tp_merge_kernel(const TpArgs a, const T
         uint32_t n = 0, amax = 0;
         float best = -INFINITY;
         bool have = false;
-        for (uint32_t r = 0; r < a.n_shards && fault == ROW_OK; r++) {
-            const TpRecHead* h = rec(r);
-            if (finite_f(h->m)) {
+        for (uint32_t r = 0; r < a.n_shards; r++) {
+            const TpRecHead& h = sm.hd[r];
+            if (fault == ROW_OK && finite_f(h.m)) {
                 // shards are in id order, so strict > keeps the lowest id on ties
-                if (!have || h->m > best) { best = h->m; amax = h->argmax; have = true; }
-                S = fadd(S, fmul(h->s, pgs_expf_tab(fdiv(fsub(h->m, M), t), sm.fin.exp_tab)));
+                if (!have || h.m > best) { best = h.m; amax = h.argmax; have = true; }
+                S = fadd(S, fmul(h.s, pgs_expf_tab(fdiv(fsub(h.m, M), t), sm.exp_tab)));
             }
-            n += min(h->n_status & 0xffffffu, a.cand);   // a record can never hold more than `cand` entries
+            sm.start[r] = n;
+            n += min(h.n_status & 0xffffffu, a.cand);   // a record can never hold more than `cand` entries
         }
+        sm.start[a.n_shards] = n;
         sm.M = M; sm.S = S; sm.amax = amax; sm.n = n; sm.fault = fault;
+        sm.unsorted = 0; sm.fin.n_live = 0u;
     }
     __syncthreads();
     if (sm.fault) {
         if (tid == 0) { o.token[row] = 0; o.status[row] = sm.fault; if (o.drew) o.drew[row] = 0; }
         return;
     }
-    // gather the union of the candidates
-    uint32_t off = 0;
-    for (uint32_t r = 0; r < a.n_shards; r++) {
-        const TpRecHead* h = rec(r);
-        const float* rx = reinterpret_cast<const float*>(h + 1);
-        const uint32_t* rid = reinterpret_cast<const uint32_t*>(rx + a.cand);
-        const uint32_t hn = min(h->n_status & 0xffffffu, a.cand);
-        for (uint32_t j = tid; j < hn; j += NT) { sm.cx[off + j] = rx[j]; sm.cid[off + j] = rid[j]; }
-        off += hn;
+    // the union of the candidates, shard after shard
+#pragma unroll
+    for (int u = 0; u < SLOTS; u++) {
+        const uint32_t c = (uint32_t)tid + u * TP_MT;
+        if (c < a.n_shards * a.cand) {
+            const uint32_t r = c / a.cand, j = c % a.cand;
+            if (j < sm.start[r + 1] - sm.start[r]) { sm.cx[sm.start[r] + j] = gx[u]; sm.cid[sm.start[r] + j] = gid[u]; }
+        }
     }
     __syncthreads();
     const bool any = finite_f(sm.M);
@@ -170,8 +196,51 @@ __global__ void __launch_bounds__(NT, 1) tp_merge_kernel(const TpArgs a, const T
     memset(&ra, 0, sizeof ra);
     ra.token = o.token; ra.status = o.status; ra.drew = o.drew; ra.argmax = o.argmax; ra.sumexp = o.gsum;
     ra.total = o.total; ra.n_kept = o.n_kept;
-    finish_row(sm.fin, ra, row, a.vocab, sm.cid, sm.cx, sm.n, sm.M, t, sm.S, top_k, a.top_p ? a.top_p[row] : 1.0f,
-               a.uniform ? a.uniform[row] : 0.0f, sm.amax, ROW_OK);
+    ra.row_max = nullptr;
+    const float top_p = a.top_p ? a.top_p[row] : 1.0f, u01 = a.uniform ? a.uniform[row] : 0.0f;
+    // Every shard's candidates arrive sorted by (logit descending, id ascending), and shards follow one another in id
+    // order.  So a candidate's rank among all of them is a sum of binary searches, one per shard, and its place in id
+    // order needs a count inside its own shard only: no sort.  The searches are by (probability, id); two different
+    // logits can round to one probability, which may leave a shard's list out of that order: such a row (looked for
+    // below) takes the general ranking instead.
+    const uint32_t n = sm.n;
+    const bool norm = sm.S > 1e-9f;
+    for (uint32_t c = tid; c < n; c += TP_MT) {
+        const float e = softmax_num(sm.cx[c], sm.M, t, sm.exp_tab);   // exact expf
+        sm.fin.key[c] = ((unsigned long long)f2u(norm ? fdiv(e, sm.S) : e) << 32) | (unsigned long long)(0xffffffffu - sm.cid[c]);
+    }
+    __syncthreads();
+    for (uint32_t c = tid; c + 1 < n; c += TP_MT) {
+        uint32_t r = 0;
+        while (sm.start[r + 1] <= c) r++;
+        if (c + 1 < sm.start[r + 1] && !(sm.fin.key[c] > sm.fin.key[c + 1])) sm.unsorted = 1;
+    }
+    __syncthreads();
+    if (sm.unsorted) {   // CTA-uniform
+        cta_finish<TP_MT>(sm.fin, sm.exp_tab, ra, row, a.vocab, sm.cid, sm.cx, n, sm.M, t, sm.S, top_k, top_p, u01, sm.amax, ROW_OK);
+        return;
+    }
+    for (uint32_t c = tid; c < n; c += TP_MT) {
+        const unsigned long long kc = sm.fin.key[c];
+        uint32_t own = 0;
+        while (sm.start[own + 1] <= c) own++;
+        uint32_t r_p = 0;
+        for (uint32_t r = 0; r < a.n_shards; r++) {   // keys of shard r that come before kc: the list is descending
+            uint32_t lo = sm.start[r], hi = sm.start[r + 1];
+            const uint32_t base = lo;
+            while (lo < hi) {
+                const uint32_t mid = (lo + hi) >> 1;
+                if (sm.fin.key[mid] > kc) lo = mid + 1; else hi = mid;
+            }
+            r_p += lo - base;
+        }
+        uint32_t r_id = sm.start[own];
+        const uint32_t idc = sm.cid[c];
+        for (uint32_t o2 = sm.start[own]; o2 < sm.start[own + 1]; o2++) r_id += sm.cid[o2] < idc;
+        const float pc = u2f((uint32_t)(kc >> 32));
+        sm.fin.sid[r_id] = idc; sm.fin.sp[r_id] = pc; sm.fin.rp[r_p] = pc; sm.fin.rpos[r_p] = r_id;
+    }
+    cta_finish_ranked<TP_MT>(sm.fin, ra, row, a.vocab, n, sm.M, sm.S, top_k, top_p, u01, sm.amax, ROW_OK);
 }
 
 __global__ void draft_accept_kernel(const uint32_t* row_argmax, const uint32_t* draft, uint32_t sequences,
@@ -185,7 +254,10 @@ __global__ void draft_accept_kernel(const uint32_t* row_argmax, const uint32_t* 
 }
 
 cudaError_t configure_tp() {
-    return cudaFuncSetAttribute(tp_merge_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(TpMergeSmem));
+    cudaError_t e = cudaFuncSetAttribute(tp_merge_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(TpMergeSmem));
+    if (e != cudaSuccess) return e;
+    // several rows per SM: most of a row's time is one warp's serial walk
+    return cudaFuncSetAttribute(tp_merge_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
 }
 
 cudaError_t launch_tp_push(const TpArgs& a, cudaStream_t stream) {
@@ -202,7 +274,7 @@ cudaError_t launch_tp_push(const TpArgs& a, cudaStream_t stream) {
 }
 
 cudaError_t launch_tp_merge(const TpArgs& a, const TpOut& o, cudaStream_t stream) {
-    tp_merge_kernel<<<a.rows, NT, sizeof(TpMergeSmem), stream>>>(a, o);
+    tp_merge_kernel<<<a.rows, TP_MT, sizeof(TpMergeSmem), stream>>>(a, o);
     return cudaGetLastError();
 }
 
