@@ -123,8 +123,8 @@ class Sampler {   // sampler.rs:11-37, bound to one device
 
     // The batched form of Engine::advance_with_logits (engine.rs:1286-1314) for the pending sequences of
     // one step, in `pending` order: sanity, penalties over `outputs[i]` (the generated ids), grammar mask
-    // for the decoded output `partials[i]`, EOS fix, sample.  One uniform is drawn per stochastic row, and
-    // handed back when the chain reports that it did not consume it.
+    // for the decoded output `partials[i]`, EOS fix, sample.  The rows see the generator's stream exactly as the
+    // reference's serial loop would hand it out.
     std::vector<Advance> advance_batch(const std::vector<const std::vector<float>*>& logits,
                                        const std::vector<const SamplingParams*>& params,
                                        const std::vector<const std::vector<TokenId>*>& outputs,
@@ -159,27 +159,42 @@ class Sampler {   // sampler.rs:11-37, bound to one device
                 mst[r] = (int32_t)p.grammar->state_of(partials[r]);
             }
         }
-        // one draw per stochastic row, in order (sampler.rs:43-46); greedy rows draw nothing
-        std::vector<int> drawn(rows, 0);
-        for (uint32_t r = 0; r < rows; r++)
-            if (!(temp[r] < 1e-5f)) { uni[r] = rng_.next_f32(); drawn[r] = 1; }
+        // One draw per stochastic row, in `pending` order (sampler.rs:43-46); greedy rows draw nothing.  A stochastic
+        // row that ends without sampling (faulted, grammar dead end, nothing finite left) consumes no draw in the
+        // reference (engine.rs:1292-1303, sampler.rs:43-46), so the rows behind it must see the stream one draw
+        // earlier: the generator is put back to where it stood before that row's draw and the rows behind it are run
+        // again with fresh draws.  Such rows are rare, and every pass makes at least one more row final.
         pgs_batch_desc d{};
-        d.struct_size = sizeof d; d.rows = rows; d.vocab = vocab; d.logits_dtype = PGS_F32; d.row_stride = vocab;
-        d.logits = x.data(); d.logits_mem = PGS_MEM_HOST; d.aux_mem = PGS_MEM_HOST;
-        d.temperature = temp.data(); d.top_k = top_k.data(); d.top_p = top_p.data();
-        d.frequency_penalty = freq.data(); d.presence_penalty = pres.data(); d.repetition_penalty = rep.data();
-        d.hist_offsets = ho.data(); d.hist_ids = hi.empty() ? ho.data() : hi.data();
-        d.mask_table = mtab.data(); d.mask_state = mst.data(); d.eos_token_id = eos; d.uniform = uni.data();
-        d.token = token.data(); d.status = status.data(); d.drew = drew.data();
-        const int rc = pgs_sample_batch(h_, &d);
+        d.struct_size = sizeof d; d.vocab = vocab; d.logits_dtype = PGS_F32; d.row_stride = vocab;
+        d.logits_mem = PGS_MEM_HOST; d.aux_mem = PGS_MEM_HOST; d.eos_token_id = eos;
+        std::vector<Rng> before(rows, rng_);
+        uint32_t start = 0;
+        int rc = PGS_OK;
+        while (start < rows) {
+            for (uint32_t r = start; r < rows; r++) {
+                before[r] = rng_;
+                uni[r] = (temp[r] < 1e-5f) ? 0.0f : rng_.next_f32();
+            }
+            d.rows = rows - start;
+            d.logits = x.data() + (size_t)start * vocab;
+            d.temperature = temp.data() + start; d.top_k = top_k.data() + start; d.top_p = top_p.data() + start;
+            d.frequency_penalty = freq.data() + start; d.presence_penalty = pres.data() + start;
+            d.repetition_penalty = rep.data() + start;
+            d.hist_offsets = ho.data() + start;   // offsets stay absolute
+            d.hist_ids = hi.empty() ? ho.data() : hi.data();
+            d.mask_table = mtab.data() + start; d.mask_state = mst.data() + start; d.uniform = uni.data() + start;
+            d.token = token.data() + start; d.status = status.data() + start; d.drew = drew.data() + start;
+            rc = pgs_sample_batch(h_, &d);
+            if (rc != PGS_OK) break;
+            uint32_t stop = rows;
+            for (uint32_t r = start; r < rows; r++)
+                if (!(temp[r] < 1e-5f) && !drew[r]) { stop = r; break; }
+            if (stop == rows) break;
+            rng_ = before[stop];   // row `stop` keeps its result; it used nothing of the stream
+            start = stop + 1;
+        }
         for (int32_t id : uploaded) pgs_mask_table_free(h_, id);
         if (rc != PGS_OK) throw std::runtime_error(pgs_last_error(h_));
-        // a stochastic row that did not draw (nothing finite, or faulted) shifts the stream of the rows
-        // after it in the reference; that only happens on degenerate rows, which are reported, and the
-        // last unconsumed draw is handed back so that the next step starts where the reference would
-        for (uint32_t r = rows; r-- > 0;) {
-            if (drawn[r] && !drew[r]) rng_.unread(); else if (drawn[r]) break;
-        }
         std::vector<Advance> out(rows);
         for (uint32_t r = 0; r < rows; r++) out[r] = {token[r], (RowStatus)status[r]};
         return out;

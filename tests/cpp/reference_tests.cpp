@@ -111,6 +111,42 @@ static void grammar_walk_and_fault_isolation() {   // pagoda/tests/grammar_tests
     CHECK(text.size() == 5 && text.front() == '"' && text.back() == '"');
 }
 
+// The draw-order rule of the serial loop (pagoda/src/engine.rs:511-544, sampler.rs:43-46): one next_f32() per row that
+// really samples, in `pending` order; a faulted row and a grammar dead end take nothing from the stream.  The batch
+// below has both in the middle.  Its tokens must equal those of the same rows advanced one by one (a single-row batch
+// is trivially in order), and the line printed at the end is compared with the CPU oracle's Sampler stream by the
+// Python side of this test.
+static void draw_order_matches_the_serial_loop() {
+    const uint32_t vocab = 64;
+    std::vector<std::vector<float>> rows(6, std::vector<float>(vocab));
+    for (int r = 0; r < 6; r++)
+        for (uint32_t i = 0; i < vocab; i++) rows[r][i] = (float)((i * 37u + (uint32_t)r * 11u) % 17u) * 0.25f;
+    rows[1][5] = NAN;                         // row 1 faults
+    Grammar g = Grammar::regex("abc");
+    SamplingParams p;
+    p.temperature = 0.8f; p.top_k = 10; p.top_p = 0.9f;
+    SamplingParams dead = p;
+    dead.grammar = g;                          // row 3: the partial output "z" is a dead end
+    std::vector<const std::vector<float>*> lp;
+    for (auto& r : rows) lp.push_back(&r);
+    std::vector<const SamplingParams*> pp = {&p, &p, &p, &dead, &p, &p};
+    std::vector<const std::vector<TokenId>*> outs(6, nullptr);
+    std::vector<std::string> partials = {"", "", "", "z", "", ""};
+    Sampler batched(1234), serial(1234);
+    auto b = batched.advance_batch(lp, pp, outs, partials, vocab, -1);
+    CHECK(b[1].status == RowStatus::Fault && b[3].status == RowStatus::Stop);
+    printf("DRAW_ORDER");
+    for (int r = 0; r < 6; r++) {
+        auto one = serial.advance_batch({lp[r]}, {pp[r]}, {nullptr}, {partials[r]}, vocab, -1);
+        CHECK(one[0].token == b[r].token && one[0].status == b[r].status);
+        printf(" %u:%d", b[r].token, (int)b[r].status);
+    }
+    // both generators stand where the reference's would: the next sample agrees too
+    const TokenId nb = batched.sample(rows[0], p), ns = serial.sample(rows[0], p);
+    CHECK(nb == ns);
+    printf(" next %u\n", nb);
+}
+
 int main() {
     greedy_is_argmax();
     sampler_is_reproducible();
@@ -120,6 +156,7 @@ int main() {
     regex_grammar();
     json_grammar();
     grammar_walk_and_fault_isolation();
+    draw_order_matches_the_serial_loop();
     printf("%s (%d failures)\n", failures ? "FAILED" : "CPP_OK", failures);
     return failures != 0;
 }

@@ -30,3 +30,28 @@ def test_reference_unit_tests_through_the_cpp_mirror():
         _build(exe)
         out = subprocess.run([exe], capture_output=True, text=True, timeout=300)
         assert out.returncode == 0 and "CPP_OK" in out.stdout, out.stdout + out.stderr
+        _check_draw_order(out.stdout)
+
+
+def _check_draw_order(stdout):
+    """The DRAW_ORDER line of the C++ test against the oracle's Sampler run over the same rows one after the other,
+    as the reference's loop does (engine.rs:511-544): a faulted row and a grammar dead end draw nothing."""
+    import numpy as np
+    from oracle import oracle
+    line = [l for l in stdout.splitlines() if l.startswith("DRAW_ORDER")][0].split()
+    got = [tuple(map(int, w.split(":"))) for w in line[1:7]]
+    nxt = int(line[8])
+    vocab = 64
+    rows = np.array([[((i * 37 + r * 11) % 17) * 0.25 for i in range(vocab)] for r in range(6)], np.float32)
+    rows[1, 5] = np.nan
+    s = oracle.Sampler(1234)
+    want = []
+    for r in range(6):
+        if r == 1:
+            want.append((0, 1))        # logits_sane fails: Fault, nothing sampled (engine.rs:1292-1295)
+        elif r == 3:
+            want.append((0, 2))        # allowed_bytes is None: Stop, nothing sampled (engine.rs:1299-1303)
+        else:
+            want.append((s.sample(rows[r], temperature=0.8, top_k=10, top_p=0.9), 0))
+    assert got == want, (got, want)
+    assert nxt == s.sample(rows[0], temperature=0.8, top_k=10, top_p=0.9)
