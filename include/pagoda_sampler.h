@@ -179,7 +179,7 @@ PGS_API int pgs_sample_batch_async(pgs_handle *h, const pgs_batch_desc *desc, vo
 PGS_API int pgs_sample_batch_static(int device_ordinal, const pgs_batch_desc *desc, void *cuda_stream);
 PGS_API const char *pgs_static_last_error(void);
 
-/* Fidelity switch.  By default rows run in the fused kernel: every decision follows the
+/* Fidelity switch.  By default rows run in the streaming row kernel: every decision follows the
  * reference, candidate probabilities use the exact expf, and the f32 left-fold sum of
  * temperature_softmax (sampler.rs:99-113) agrees with the reference's to about 1e-6 relative,
  * so a top-p or CDF decision can differ only when it sits that close to its boundary.  With
@@ -289,12 +289,11 @@ typedef struct pgs_counters {
 } pgs_counters;
 PGS_API int pgs_get_counters(const pgs_handle *h, pgs_counters *out);
 
-/* Phase timers of the fused kernel, a diagnostic: only handles created with PGS_PROFILE=1 in the environment
- * keep them.  out[cta * 16 + slot] receives the cycles thread 0 of CTA `cta` spent in each phase since the last
- * read (summed over its rows), then the timers are cleared.  Slots: 12 row barrier, 11 parameters + copy issue +
- * history table, 0 slice check (14: of which waiting for the copy), 1 penalties, 2 argmax, 3 exchange #1,
- * 13 + 15 + 4 top-k bound, 5 candidates + exponent pass, 6 scan, 7 exchange #2, 8 fold, 9 exchange #3 + refinement.
- * n_ctas <= 1024.  Synchronises the handle's stream. */
+/* Phase timers of the streaming row kernel, a diagnostic: only handles created with PGS_PROFILE=1 in the
+ * environment keep them.  out[cta * 16 + slot] receives the cycles thread 0 of CTA `cta` spent in each phase since
+ * the last read (summed over its rows), then the timers are cleared.  Slots: 0 gate + row barrier, 1 history
+ * indexed, 2 first pass, 3 reductions + top-k bound + fold table, 4 second pass, 5 finish.  n_ctas <= 1024.
+ * Synchronises the handle's stream. */
 PGS_API int pgs_debug_read_profile(pgs_handle *h, long long *out, uint32_t n_ctas);
 
 /* The handle's stream as a cudaStream_t, for callers that time or order work on it. */

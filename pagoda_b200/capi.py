@@ -299,7 +299,7 @@ class Sampler:
         return {k: getattr(c, k) for k, _ in Counters._fields_}
 
     def read_phase_timers(self, n_ctas: int = 1024):
-        """Cycles per CTA and phase of the fused kernel since the last read ([n_ctas, 16] int64; needs
+        """Cycles per CTA and phase of the streaming row kernel since the last read ([n_ctas, 16] int64; needs
         PGS_PROFILE=1 in the environment when the sampler is created)."""
         out = np.zeros((n_ctas, 16), dtype=np.int64)
         self._check(self._lib.pgs_debug_read_profile(self._h, out.ctypes.data_as(C.c_void_p), C.c_uint32(n_ctas)))

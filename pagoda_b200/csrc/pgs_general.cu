@@ -2,7 +2,7 @@
 // Engine::advance_with_logits (pagoda/src/engine.rs:1286-1314) with its working copy of the row
 // in a global-memory scratch slot.  It accepts every shape and parameter combination (any vocab
 // size or alignment, top-k off, top-p without top-k, thousands of tied candidates, long
-// histories) and is the path rows take when the fused cluster kernel cannot hold them.
+// histories) and is the path rows take when the streaming row kernel cannot serve them.
 //
 // Order of operations per row, as the reference runs them:
 //   sanity (engine.rs:1278-1295) -> repetition* / frequency / presence penalties

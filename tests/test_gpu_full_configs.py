@@ -1,5 +1,5 @@
 """The benchmark configurations at their full sizes, through the C ABI, against the CPU oracle (run on
-all host threads) and through size-independent properties.  Fused mode is the default path; the
+all host threads) and through size-independent properties.  The streaming row kernel is the default path; the
 general kernel (exact mode) must reproduce every token bit for bit."""
 import numpy as np
 import pytest

@@ -14,10 +14,10 @@ pytestmark = pytest.mark.gpu
 NEG_INF = float("-inf")
 
 
-@pytest.fixture(scope="module", params=["exact", "fused"])
+@pytest.fixture(scope="module", params=["exact", "stream"])
 def sampler(request):
     """Both kernels behind the same ABI: `exact` routes every row through the general kernel
-    (bit-exact token ids), `fused` is the default fast path with its stated tolerance."""
+    (bit-exact token ids), `stream` is the default fast path with its stated tolerance."""
     import pagoda_b200
     s = pagoda_b200.Sampler(device=0, max_rows=256, max_vocab=262144, max_history=4096)
     s.set_exact(request.param == "exact")

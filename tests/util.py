@@ -32,7 +32,7 @@ TOL = 1e-5   # the stated tolerance on softmax probabilities (relative)
 
 def assert_same(got, want, w=None, check_floats=True, exact=True, min_clear=0.9):
     """exact=True (general kernel): bit-exact agreement on every decision and on the f32 quantities
-    behind them.  exact=False (fused kernel): statuses, argmax and row max bit-exact; the f32
+    behind them.  exact=False (streaming row kernel): statuses, argmax and row max bit-exact; the f32
     left-fold sum and the probabilities within TOL relative; token ids and kept counts equal on
     every row whose closest decision is further than TOL from its boundary (the oracle reports
     that margin per row)."""
