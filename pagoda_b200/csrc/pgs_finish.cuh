@@ -38,11 +38,15 @@ using FinishArrays = FinishArraysT<F_MCAP>;
 __device__ __forceinline__ float warp_prefix(const float* v, int n, float* pre) {
     const int lane = threadIdx.x & 31;
     float acc = 0.0f;
-    if (lane == 0) {
+    if (lane == 0 && n > 0) {
+        float4 lo4 = *reinterpret_cast<const float4*>(v), hi4 = *reinterpret_cast<const float4*>(v + 4);
 #pragma unroll 1
         for (int j0 = 0; j0 < n; j0 += 8) {
-            const float4 lo4 = *reinterpret_cast<const float4*>(v + j0), hi4 = *reinterpret_cast<const float4*>(v + j0 + 4);
             float x[8] = {lo4.x, lo4.y, lo4.z, lo4.w, hi4.x, hi4.y, hi4.z, hi4.w};
+            if (j0 + 8 < n) {   // the next eight are on their way while these are added
+                lo4 = *reinterpret_cast<const float4*>(v + j0 + 8);
+                hi4 = *reinterpret_cast<const float4*>(v + j0 + 12);
+            }
 #pragma unroll
             for (int u = 0; u < 8; u++) {
                 acc = fadd(acc, j0 + u < n ? x[u] : 0.0f);
