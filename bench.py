@@ -486,8 +486,8 @@ def main():
             step(i)
         t = sampler.read_phase_timers()
         act = t[t.sum(1) > 0]
-        names = {0: "gate + row barrier", 1: "history indexed", 2: "pass 1 (HBM)", 3: "reductions, top-k bound, fold table",
-                 4: "pass 2 (L2)", 5: "finish"}
+        names = {0: "gate + row barrier", 1: "history indexed", 2: "pass 1 (HBM)", 6: "reductions + argmax", 7: "top-k bound",
+                 3: "fold table", 4: "pass 2 (L2)", 5: "finish"}
         per_step = act.mean(0) / n
         print(f"{len(act)} CTAs active, {ROWS} rows per step; cycles per step and CTA (thread 0), mean over CTAs:", file=sys.stderr)
         for slot, name in names.items():

@@ -292,7 +292,8 @@ PGS_API int pgs_get_counters(const pgs_handle *h, pgs_counters *out);
 /* Phase timers of the streaming row kernel, a diagnostic: only handles created with PGS_PROFILE=1 in the
  * environment keep them.  out[cta * 16 + slot] receives the cycles thread 0 of CTA `cta` spent in each phase since
  * the last read (summed over its rows), then the timers are cleared.  Slots: 0 gate + row barrier, 1 history
- * indexed, 2 first pass, 3 reductions + top-k bound + fold table, 4 second pass, 5 finish.  n_ctas <= 1024.
+ * indexed, 2 first pass, 6 reductions + argmax, 7 top-k bound, 3 fold table, 4 second pass, 5 finish.
+ * n_ctas <= 1024.
  * Synchronises the handle's stream. */
 PGS_API int pgs_debug_read_profile(pgs_handle *h, long long *out, uint32_t n_ctas);
 

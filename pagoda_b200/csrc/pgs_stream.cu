@@ -843,6 +843,7 @@ __global__ void __launch_bounds__(SNT, 2) stream_row_kernel(const RowArgs a, con
             continue;
         }
 
+        PGS_STICK(6);   // reductions + argmax
         // ---- top-k bound.  The per-thread maxima are spread over S_NB equal-width buckets between their
         // smallest finite value and the row maximum (a monotone map); with b the highest bucket such that the
         // buckets b.. hold at least top_k maxima, every logit of bucket b - 1 or higher is a candidate.
@@ -875,6 +876,7 @@ __global__ void __launch_bounds__(SNT, 2) stream_row_kernel(const RowArgs a, con
             const float delta = 4.8e-7f * (fabsf(m - bound) + 4.0f * t) + 4.8e-7f * (fabsf(bound) + fabsf(m));
             cut = bound - delta;
         }
+        PGS_STICK(7);   // top-k bound
         // numerator = 2^(x * sc + c): c = -m * sc as c_hi + c_lo (c_lo only when it matters: the numerators then keep
         // the reference's scale to 1e-7, which the fold needs where many logits are equal); what is left of c scales
         // the final sum
@@ -923,7 +925,7 @@ __global__ void __launch_bounds__(SNT, 2) stream_row_kernel(const RowArgs a, con
                 __syncthreads();   // scan_f is reused by the next round; after the last one the table and PassArgs are complete
             }
         }
-        PGS_STICK(3);   // reductions, bound, fold table
+        PGS_STICK(3);   // fold table
 
         // ================================================================ pass 2 (L2, first piece first)
         if (has_tail) {

@@ -48,6 +48,20 @@ def test_argmax_ties_take_the_lowest_id(sampler):  # sampler.rs:64 strict >
     assert r.status[0] == 1  # -inf from the model is a fault (engine.rs:1278-1280)
 
 
+def test_negative_zero_ties_with_positive_zero(sampler, oracle):
+    """The reference's argmax compares with `>` (sampler.rs:64), for which -0.0 and +0.0 are equal: when the row
+    maximum is a mix of the two, the lowest id wins whatever its sign bit."""
+    assert _row(sampler, [-1.0, -0.0, 0.0, -3.0]).token[0] == 1
+    assert _row(sampler, [-1.0, 0.0, -0.0, -3.0]).token[0] == 1
+    x = np.full(20000, -2.0, np.float32)           # long enough for several pieces of the streaming kernel
+    x[5] = -0.0
+    x[15000] = 0.0
+    got = _row(sampler, x)
+    assert got.token[0] == 5 == oracle.argmax(x) and got.argmax[0] == 5
+    got = _row(sampler, x, temperature=1.0, top_k=4, uniform=0.0)   # stochastic rows report the same argmax
+    assert got.argmax[0] == 5
+
+
 def test_sampler_is_reproducible_and_matches_the_oracle_stream(sampler, oracle):  # sampler.rs:165-176
     logits = np.ones(100, dtype=np.float32)
     rng = oracle.Rng(99)
