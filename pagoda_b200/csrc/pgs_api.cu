@@ -24,7 +24,8 @@ size_t general_smem_bytes();
 size_t stream_smem_bytes();
 cudaError_t configure_stream();
 cudaError_t stream_ctas_per_sm(int* out);
-cudaError_t launch_stream(const RowArgs& a, const StreamLaunch& sl, uint32_t grid, cudaStream_t stream);
+cudaError_t launch_stream(const RowArgs& a, const StreamLaunch& sl, uint32_t grid, uint32_t csize, cudaStream_t stream);
+cudaError_t stream_max_clusters(int csize, int* out);
 struct ScoreArgs {
     const float* logits;
     unsigned long long row_stride;
@@ -76,6 +77,8 @@ struct pgs_handle {
     int exact = 0;
     // streaming row kernel: id -> count slots, shared memory and CTAs per SM, the gate's counter
     uint32_t stream_hash = 0, stream_cohort = 0;
+    int max_clusters[4] = {0, 0, 0, 0};   // resident clusters of 1 (unused), 2, 4, 8 CTAs of the row kernel
+    int cluster_mode = 1;                 // PGS_CLUSTER=0 turns row sharing off
     size_t stream_smem = 0;
     int stream_ctas = 0;
     uint32_t* p1_done = nullptr;      // device counter: rows that finished their first pass, over all launches
@@ -204,6 +207,10 @@ extern "C" int pgs_create(int device, uint32_t max_rows, uint32_t max_vocab, uin
         // about an SM count keeps pass 2 in L2 but leaves half the threads of every SM waiting at the gate)
         h->stream_cohort = 0xffffffffu;
         if (const char* ev = getenv("PGS_COHORT")) { if (atoi(ev) > 0) h->stream_cohort = (uint32_t)atoi(ev); }
+        if (const char* ev = getenv("PGS_CLUSTER")) h->cluster_mode = atoi(ev);
+        for (int i = 1; i < 4; i++) {
+            if (pgs::stream_max_clusters(1 << i, &h->max_clusters[i]) != cudaSuccess) { cudaGetLastError(); h->max_clusters[i] = 0; }
+        }
         if (const char* ev = getenv("PGS_EXACT")) h->exact = atoi(ev);
         if (const char* ev = getenv("PGS_PROFILE")) {
             if (atoi(ev)) {
@@ -342,7 +349,13 @@ int launch_step(pgs_handle* h, pgs::RowArgs& a, cudaStream_t stream) {
     sl.work_rows = h->work_rows; sl.work_count = h->work_count;
     sl.prof = h->prof;
     const uint32_t resident = (uint32_t)h->stream_ctas * (uint32_t)h->sm_count;
-    PGS_CUDA(h, pgs::launch_stream(a, sl, rows < resident ? rows : resident, stream));
+    // Small batches: the CTAs of a cluster share every row, with the largest cluster size that still has all rows
+    // resident at once (a row alone on one CTA is bound by latency, not by bandwidth).
+    uint32_t csize = 1;
+    if (h->cluster_mode && !a.tp_records)
+        for (int i = 3; i >= 2; i--)   // (pairs do not pay: two CTAs per row with half the rows' CTAs measured slower)
+            if (h->max_clusters[i] > 0 && rows <= (uint32_t)h->max_clusters[i]) { csize = 1u << i; break; }
+    PGS_CUDA(h, pgs::launch_stream(a, sl, csize > 1 ? rows : (rows < resident ? rows : resident), csize, stream));
     h->done_total += rows;
     // The list is usually empty.  The pass over it is set up while the row kernel still runs (programmatic stream
     // serialization) and returns at once when it finds nothing listed.

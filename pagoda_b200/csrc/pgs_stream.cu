@@ -41,6 +41,8 @@
 
 #include <type_traits>
 
+#include <cooperative_groups.h>
+
 #include "pgs_args.cuh"
 #include "pgs_block.cuh"
 #include "pgs_finish.cuh"
@@ -81,6 +83,12 @@ struct PassArgs {
     float sc, sc_lo, c_hi, c_lo, cut_f, freq, pres, rep;
     uint32_t V, n_full, n_regions, flags;
     uint32_t eos_piece, eos_tid, eos_sub;
+    // a row shared by the CTAs of a cluster: this CTA works on the pieces q0, q0 + qstep, ...; the candidates of all of
+    // them are collected by the first CTA (pointers into its shared memory)
+    uint32_t q0, qstep;
+    uint32_t* cand_n_p;
+    uint32_t* cand_id_p;
+    float* cand_x_p;
 };
 
 struct StreamSmem {
@@ -92,6 +100,10 @@ struct StreamSmem {
     float scan_f[SNW];
     double wacc[SNW];               // per-warp share of the fold
     uint32_t cand_n, sel_bucket, amax;
+    // cluster mode: one slot per CTA of the cluster, written by that CTA into every CTA's copy (xk .. xflag) or into
+    // the first CTA's copy (xs, xam)
+    uint32_t xk[8], xlo[8], xfin[8], xflag[8], xam[8];
+    double xs[8];
     uint32_t cand_id[F_MCAP];
     float cand_x[F_MCAP];
     long long prof_acc[16];
@@ -451,7 +463,7 @@ struct FoldAcc {
 };
 
 // pass 2 on one piece
-template <bool BF16, bool MASK, bool TAIL>
+template <bool BF16, bool MASK, bool TAIL, bool CL = false>
 __device__ __forceinline__ void p2_piece(StreamSmem& sm, const Raw<BF16>& raw, uint32_t q, FoldAcc& fa) {
     constexpr int G = Geo<BF16>::G, GE = Geo<BF16>::GE;
     const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
@@ -465,8 +477,13 @@ __device__ __forceinline__ void p2_piece(StreamSmem& sm, const Raw<BF16>& raw, u
 #pragma unroll
         for (int j = 0; j < S_EPT; j++)
             if (x[j] >= cut_f) {
-                const uint32_t at = atomicAdd(&sm.cand_n, 1u);
-                if (at < (uint32_t)F_MCAP) { sm.cand_id[at] = elem_id<BF16>(e0, j); sm.cand_x[at] = x[j]; }
+                if (CL) {
+                    const uint32_t at = atomicAdd(sm.pa.cand_n_p, 1u);
+                    if (at < (uint32_t)F_MCAP) { sm.pa.cand_id_p[at] = elem_id<BF16>(e0, j); sm.pa.cand_x_p[at] = x[j]; }
+                } else {
+                    const uint32_t at = atomicAdd(&sm.cand_n, 1u);
+                    if (at < (uint32_t)F_MCAP) { sm.cand_id[at] = elem_id<BF16>(e0, j); sm.cand_x[at] = x[j]; }
+                }
             }
     }
     const uint32_t region = q * SNW + (uint32_t)w;
@@ -554,11 +571,32 @@ __device__ __forceinline__ void prefetch_piece(const char* warp_piece) {
 }
 
 // pass 1 over the whole pieces n_full-1 .. 0; the thread's results go to sm.t_*[tid]
-template <bool BF16, bool MASK, bool STOCH>
+template <bool BF16, bool MASK, bool STOCH, bool CL>
 __device__ __noinline__ void pass1_whole(StreamSmem& sm) {
     constexpr int PB = S_PIECE * (BF16 ? 2 : 4);
     const uint32_t lane_e0 = (threadIdx.x >> 5) * S_REGION + (threadIdx.x & 31) * Geo<BF16>::GE;
     const uint32_t n = sm.pa.n_full;   // >= 1
+    if (CL) {   // the pieces q0, q0 + qstep, ... of the row, last one first
+        float am = 0.0f, tmx = -INFINITY;
+        uint32_t tqx = 0u;
+        const int q0 = (int)sm.pa.q0, qs = (int)sm.pa.qstep;
+        if (q0 < (int)n) {
+            int q = q0 + (((int)n - 1 - q0) / qs) * qs;
+            const size_t step = (size_t)qs * PB;
+            const char* p = sm.pa.rowp + (size_t)lane_e0 * (BF16 ? 2 : 4) + (size_t)q * PB;
+            const char* wp = sm.pa.rowp + (size_t)((threadIdx.x >> 5) * S_REGION) * (BF16 ? 2 : 4) + (size_t)q * PB;
+            if (q - qs >= q0) prefetch_piece<BF16>(wp - step);
+#pragma unroll 1
+            for (; q >= q0; q -= qs, p -= step, wp -= step) {
+                if (q - 2 * qs >= q0) prefetch_piece<BF16>(wp - 2 * step);
+                Raw<BF16> b;
+                raw_load<BF16>(b, p);
+                p1_piece<BF16, MASK, false, STOCH>(sm, b, (uint32_t)q, am, tmx, tqx);
+            }
+        }
+        sm.t_am[threadIdx.x] = am; sm.t_max[threadIdx.x] = tmx; sm.t_q[threadIdx.x] = tqx;
+        return;
+    }
     const char* p = sm.pa.rowp + (size_t)lane_e0 * (BF16 ? 2 : 4) + (size_t)(n - 1u) * PB;
     float am = 0.0f, tmx = -INFINITY;
     uint32_t tqx = 0u;
@@ -576,7 +614,7 @@ __device__ __noinline__ void pass1_whole(StreamSmem& sm) {
 }
 
 // pass 2 over the whole pieces 0 .. n_full-1; the warp's share of the fold is added to sm.wacc[w]
-template <bool BF16, bool MASK>
+template <bool BF16, bool MASK, bool CL>
 __device__ __noinline__ void pass2_whole(StreamSmem& sm) {
     constexpr int PB = S_PIECE * (BF16 ? 2 : 4);
     const uint32_t lane_e0 = (threadIdx.x >> 5) * S_REGION + (threadIdx.x & 31) * Geo<BF16>::GE;
@@ -584,6 +622,23 @@ __device__ __noinline__ void pass2_whole(StreamSmem& sm) {
     const char* p = sm.pa.rowp + (size_t)lane_e0 * (BF16 ? 2 : 4);
     FoldAcc fa;
     fa.accd = 0.0; fa.cur_n = 0ull; fa.cur_bb = 0u;
+    if (CL) {   // the pieces q0, q0 + qstep, ... of the row, first one first
+        const uint32_t q0 = sm.pa.q0, qs = sm.pa.qstep;
+        const size_t step = (size_t)qs * PB;
+        p += (size_t)q0 * PB;
+        const char* wp = sm.pa.rowp + (size_t)((threadIdx.x >> 5) * S_REGION) * (BF16 ? 2 : 4) + (size_t)q0 * PB;
+        if (q0 + qs < n) prefetch_piece<BF16>(wp + step);
+#pragma unroll 1
+        for (uint32_t q = q0; q < n; q += qs, p += step, wp += step) {
+            if (q + 2u * qs < n) prefetch_piece<BF16>(wp + 2 * step);
+            Raw<BF16> b;
+            raw_load<BF16>(b, p);
+            p2_piece<BF16, MASK, false, true>(sm, b, q, fa);
+        }
+        fa.flush();
+        if ((threadIdx.x & 31) == 0) sm.wacc[threadIdx.x >> 5] += fa.accd;
+        return;
+    }
     const char* wp = sm.pa.rowp + (size_t)((threadIdx.x >> 5) * S_REGION) * (BF16 ? 2 : 4);
 #pragma unroll 1
     for (uint32_t d = 1; d < (uint32_t)PGS_PF_DIST && d < n; d++) prefetch_piece<BF16>(wp + (size_t)d * PB);
@@ -598,8 +653,14 @@ __device__ __noinline__ void pass2_whole(StreamSmem& sm) {
     if ((threadIdx.x & 31) == 0) sm.wacc[threadIdx.x >> 5] += fa.accd;
 }
 
-template <bool BF16>
+// CL: a thread-block cluster of 2, 4 or 8 CTAs shares every row (small batches: a row alone on one CTA is bound by
+// the latency of its own loads and dependent instructions).  CTA k of the cluster takes the pieces k, k + size, ...;
+// the CTAs exchange their maxima, region tables, histograms, candidates and fold shares through distributed shared
+// memory around four cluster barriers per row, and the first CTA finishes the row.  Every decision that ends a row
+// early is taken from values all CTAs of the cluster hold alike, so they always meet at the same barriers.
+template <bool BF16, bool CL>
 __global__ void __launch_bounds__(SNT, 2) stream_row_kernel(const RowArgs a, const StreamLaunch sl) {
+    namespace cg = cooperative_groups;
     constexpr int GE = Geo<BF16>::GE, GS = Geo<BF16>::GS;
     constexpr int ESZ = BF16 ? 2 : 4;
     extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -618,12 +679,16 @@ __global__ void __launch_bounds__(SNT, 2) stream_row_kernel(const RowArgs a, con
 #pragma unroll 1
         for (int i = 0; i < 16; i++) sm.prof_acc[i] = 0;
     constexpr int PREP_TID = SNT - 32;   // lane 0 of the last warp
-    if (tid == PREP_TID && blockIdx.x < a.rows) sprepare_row<BF16>(a, sl, blockIdx.x, sm.ctl[0]);
+    uint32_t crank = 0u, csize = 1u;
+    if (CL) { crank = cg::this_cluster().block_rank(); csize = cg::this_cluster().num_blocks(); }
+    const uint32_t first_row = CL ? blockIdx.x / csize : blockIdx.x, row_step = CL ? gridDim.x / csize : gridDim.x;
+    const uint32_t tail_owner = n_full % csize;   // the CTA that takes the ragged piece
+    if (tid == PREP_TID && first_row < a.rows) sprepare_row<BF16>(a, sl, first_row, sm.ctl[0]);
     long long tick_ = clock64();
     uint32_t it = 0;
-    for (uint32_t row = blockIdx.x; row < a.rows; row += gridDim.x, it++) {
+    for (uint32_t row = first_row; row < a.rows; row += row_step, it++) {
         // ---- gate: at most `cohort` rows ahead of the rows that have left their first pass
-        if (tid == 0 && row >= sl.cohort) {
+        if (!CL && tid == 0 && row >= sl.cohort) {
             const uint32_t need = row - sl.cohort + 1u;
             const volatile uint32_t* done = sl.p1_done;
 #pragma unroll 1
@@ -636,8 +701,8 @@ __global__ void __launch_bounds__(SNT, 2) stream_row_kernel(const RowArgs a, con
         __syncthreads();
         PGS_STICK(0);   // gate + row barrier
         const SRowCtl& ctl = sm.ctl[it & 1];
-        if (tid == PREP_TID && row + gridDim.x < a.rows) sprepare_row<BF16>(a, sl, row + gridDim.x, sm.ctl[(it + 1) & 1]);
-        const bool writer = tid == 0;
+        if (tid == PREP_TID && row + row_step < a.rows) sprepare_row<BF16>(a, sl, row + row_step, sm.ctl[(it + 1) & 1]);
+        const bool writer = tid == 0 && crank == 0u;   // one thread of the row's (first) CTA
         if (ctl.kind != 0u) {
             if (writer) {
                 if (ctl.kind == 1u) {
@@ -662,6 +727,14 @@ __global__ void __launch_bounds__(SNT, 2) stream_row_kernel(const RowArgs a, con
             pa.rowp = rowp; pa.mw = ctl.mw; pa.sc = sc; pa.sc_lo = ctl.sc_lo; pa.c_hi = 0.0f; pa.c_lo = 0.0f; pa.cut_f = 0.0f;
             pa.freq = ctl.freq; pa.pres = ctl.pres; pa.rep = ctl.rep;
             pa.V = V; pa.n_full = n_full; pa.n_regions = n_regions;
+            pa.q0 = crank; pa.qstep = csize;
+            pa.cand_n_p = &sm.cand_n; pa.cand_id_p = sm.cand_id; pa.cand_x_p = sm.cand_x;
+            if (CL) {
+                cg::cluster_group cluster = cg::this_cluster();
+                pa.cand_n_p = cluster.map_shared_rank(&sm.cand_n, 0);
+                pa.cand_id_p = cluster.map_shared_rank(sm.cand_id, 0);
+                pa.cand_x_p = cluster.map_shared_rank(sm.cand_x, 0);
+            }
             pa.flags = (pen ? PF_PEN : 0u) | (do_rep ? PF_REP : 0u) | (do_fp ? PF_FP : 0u) | (fabsf(ctl.pres) > 1e-6f ? PF_PRES : 0u);
             // the EOS fix touches one logit: where it sits in the piece / thread / register layout
             pa.eos_piece = 0xffffffffu; pa.eos_tid = 0u; pa.eos_sub = 0u;
@@ -674,6 +747,7 @@ __global__ void __launch_bounds__(SNT, 2) stream_row_kernel(const RowArgs a, con
         }
 
         // ---- history: distinct ids with their counts, grouped by the warp region they fall into
+        bool defer_row = false;
         if (pen) {
             uint32_t* rcnt = reinterpret_cast<uint32_t*>(sm.reg_a);   // distinct ids per region, then the scatter cursor
             // the first id of every thread is requested before the tables are cleared
@@ -705,10 +779,14 @@ __global__ void __launch_bounds__(SNT, 2) stream_row_kernel(const RowArgs a, con
                 if (!placed) spilled = 1;
             }
             spilled = __syncthreads_or(spilled);
-            if (spilled) {   // CTA-uniform
+            if (spilled && !CL) {   // CTA-uniform
                 if (writer) { sl.work_rows[atomicAdd(sl.work_count, 1u)] = row; atomicAdd(sl.p1_done, 1u); }
                 continue;
             }
+            // (A cluster must meet at its barriers whatever one of its CTAs finds here: the CTA goes through the first
+            // pass without penalties and says so in the exchange behind it, where all CTAs give the row up together.)
+            if (CL && spilled) { defer_row = true; if (tid == 0) sm.pa.flags = 0u; }
+            if (!spilled) {
             // exclusive scan of the counts in region order; thread t owns the regions t * rpt ..
             const uint32_t rpt = (n_regions + SNT - 1) / SNT;   // <= S_RPT
             uint32_t cnt[S_RPT], own = 0u;
@@ -736,6 +814,7 @@ __global__ void __launch_bounds__(SNT, 2) stream_row_kernel(const RowArgs a, con
                 sm.pid[at] = (uint16_t)(id % S_REGION);
                 sm.pval[at] = hcnt[s];
             }
+            }
         }
 #pragma unroll
         for (int c = 0; c < S_NCELL; c++) sm.cell[c * SNT + tid] = -INFINITY;
@@ -746,15 +825,16 @@ __global__ void __launch_bounds__(SNT, 2) stream_row_kernel(const RowArgs a, con
         float am = 0.0f;            // max |raw logit|
         float tmx = -INFINITY;      // the thread's running maximum, and the lowest piece that holds it
         uint32_t tqx = 0u;
-        if (has_tail) {
+        const bool my_tail = has_tail && (!CL || tail_owner == crank);
+        if (my_tail) {
             Raw<BF16> raw;
             raw_load_tail<BF16>(raw, rowp + ((size_t)n_full * S_PIECE + lane_e0) * ESZ, n_full * S_PIECE + lane_e0, V);
             if (has_mask) { if (greedy) p1_piece<BF16, true, true, false>(sm, raw, n_full, am, tmx, tqx); else p1_piece<BF16, true, true, true>(sm, raw, n_full, am, tmx, tqx); }
             else { if (greedy) p1_piece<BF16, false, true, false>(sm, raw, n_full, am, tmx, tqx); else p1_piece<BF16, false, true, true>(sm, raw, n_full, am, tmx, tqx); }
         }
         if (n_full > 0u) {
-            if (has_mask) { if (greedy) pass1_whole<BF16, true, false>(sm); else pass1_whole<BF16, true, true>(sm); }
-            else { if (greedy) pass1_whole<BF16, false, false>(sm); else pass1_whole<BF16, false, true>(sm); }
+            if (has_mask) { if (greedy) pass1_whole<BF16, true, false, CL>(sm); else pass1_whole<BF16, true, true, CL>(sm); }
+            else { if (greedy) pass1_whole<BF16, false, false, CL>(sm); else pass1_whole<BF16, false, true, CL>(sm); }
             am = absmax3_nan(am, sm.t_am[tid], 0.0f);
             if (sm.t_max[tid] >= tmx) { tmx = sm.t_max[tid]; tqx = sm.t_q[tid]; }   // the whole pieces come before the ragged one
         }
@@ -782,10 +862,42 @@ __global__ void __launch_bounds__(SNT, 2) stream_row_kernel(const RowArgs a, con
             if (tid == 0) { sm.cand_n = 0u; sm.sel_bucket = 0u; sm.amax = 0xffffffffu; }
         }
         __syncthreads();
-        const uint32_t gkey = __reduce_max_sync(FULL, lane < SNW ? sm.red_key[lane] : 0u);
-        const uint32_t lo_key = __reduce_min_sync(FULL, lane < SNW ? sm.red_lo[lane] : 0xffffffffu);
-        const uint32_t n_fin = __reduce_add_sync(FULL, lane < SNW ? sm.red_fin[lane] : 0u);
-        const bool nonfinite = __any_sync(FULL, lane < SNW && sm.red_flag[lane] != 0u);
+        uint32_t gkey = __reduce_max_sync(FULL, lane < SNW ? sm.red_key[lane] : 0u);
+        uint32_t lo_key = __reduce_min_sync(FULL, lane < SNW ? sm.red_lo[lane] : 0xffffffffu);
+        uint32_t n_fin = __reduce_add_sync(FULL, lane < SNW ? sm.red_fin[lane] : 0u);
+        bool nonfinite = __any_sync(FULL, lane < SNW && sm.red_flag[lane] != 0u);
+        if (CL) {
+            // First barrier: every CTA of the cluster is through its first pass, so nobody still uses the space of the
+            // region table for its history counts, and everybody is done with the row before.  Then every CTA hands its
+            // part of the region table and its four numbers to all the others; second barrier; combine.
+            cg::cluster_group cluster = cg::this_cluster();
+            cluster.sync();
+            if (!greedy) {
+#pragma unroll 1
+                for (uint32_t r = tid; r < n_regions; r += SNT) {
+                    const uint32_t q = r / SNW;
+                    if ((q < n_full ? q % csize : tail_owner) != crank) continue;
+                    const float ra = sm.reg_a[r], rb = sm.reg_b[r];
+                    for (uint32_t k = 0; k < csize; k++) {
+                        if (k == crank) continue;
+                        *cluster.map_shared_rank(&sm.reg_a[r], k) = ra;
+                        *cluster.map_shared_rank(&sm.reg_b[r], k) = rb;
+                    }
+                }
+            }
+            if ((uint32_t)tid < csize) {
+                *cluster.map_shared_rank(&sm.xk[crank], tid) = gkey;
+                *cluster.map_shared_rank(&sm.xlo[crank], tid) = lo_key;
+                *cluster.map_shared_rank(&sm.xfin[crank], tid) = n_fin;
+                *cluster.map_shared_rank(&sm.xflag[crank], tid) = (nonfinite ? 1u : 0u) | (defer_row ? 2u : 0u);
+            }
+            cluster.sync();
+            gkey = 0u; lo_key = 0xffffffffu; n_fin = 0u; nonfinite = false; defer_row = false;
+            for (uint32_t k = 0; k < csize; k++) {
+                gkey = umax(gkey, sm.xk[k]); lo_key = umin(lo_key, sm.xlo[k]); n_fin += sm.xfin[k];
+                nonfinite |= (sm.xflag[k] & 1u) != 0u; defer_row |= (sm.xflag[k] & 2u) != 0u;
+            }
+        }
         const bool any = gkey != 0u;
         const float m = any ? key_to_float(gkey) : -INFINITY;
         const int status = any ? ROW_OK : ROW_EMPTY;
@@ -815,8 +927,21 @@ __global__ void __launch_bounds__(SNT, 2) stream_row_kernel(const RowArgs a, con
             }
             __syncthreads();
         }
-        const uint32_t amax = any ? sm.amax : 0u;
-        if (nonfinite || (gflags & 2u) || greedy || !any) {
+        uint32_t amax = any ? sm.amax : 0u;
+        if (defer_row || nonfinite || (gflags & 2u) || greedy || !any) {
+            if (CL) {   // the lowest id over all CTAs; the first CTA writes the row
+                cg::cluster_group cluster = cg::this_cluster();
+                if (tid == 0) *cluster.map_shared_rank(&sm.xam[crank], 0) = sm.amax;
+                cluster.sync();
+                if (crank != 0u) continue;
+                uint32_t am_all = 0xffffffffu;
+                for (uint32_t k = 0; k < csize; k++) am_all = umin(am_all, sm.xam[k]);
+                amax = any ? am_all : 0u;
+            }
+            if (defer_row) {   // (cluster mode only) a CTA could not index the history: the general kernel takes the row
+                if (writer) sl.work_rows[atomicAdd(sl.work_count, 1u)] = row;
+                continue;
+            }
             if (writer && a.tp_records) {
                 if (nonfinite) {
                     tp_write_head(a, row, NAN, 0.0f, 0u, ROW_NONFINITE, 0u);
@@ -860,6 +985,16 @@ __global__ void __launch_bounds__(SNT, 2) stream_row_kernel(const RowArgs a, con
             __syncthreads();
             // thread j owns the S_BPT buckets S_NB-1 - j*S_BPT - u; `above` = maxima in higher buckets
             uint32_t hv[S_BPT], own = 0u;
+            if (CL) {   // third barrier: the histograms of all CTAs stand; every CTA adds them up for itself
+                cg::cluster_group cluster = cg::this_cluster();
+                cluster.sync();
+#pragma unroll
+                for (int u = 0; u < S_BPT; u++) {
+                    hv[u] = 0u;
+                    for (uint32_t k = 0; k < csize; k++) hv[u] += *cluster.map_shared_rank(&sm.hist[(S_NB - 1) - tid * S_BPT - u], k);
+                    own += hv[u];
+                }
+            } else
 #pragma unroll
             for (int u = 0; u < S_BPT; u++) { hv[u] = sm.hist[(S_NB - 1) - tid * S_BPT - u]; own += hv[u]; }
             uint32_t total;
@@ -928,23 +1063,33 @@ __global__ void __launch_bounds__(SNT, 2) stream_row_kernel(const RowArgs a, con
         PGS_STICK(3);   // fold table
 
         // ================================================================ pass 2 (L2, first piece first)
-        if (has_tail) {
+        if (my_tail) {
             Raw<BF16> raw;
             raw_load_tail<BF16>(raw, rowp + ((size_t)n_full * S_PIECE + lane_e0) * ESZ, n_full * S_PIECE + lane_e0, V);
             FoldAcc fa;
             fa.accd = 0.0; fa.cur_n = 0ull; fa.cur_bb = 0u;
-            if (has_mask) p2_piece<BF16, true, true>(sm, raw, n_full, fa); else p2_piece<BF16, false, true>(sm, raw, n_full, fa);
+            if (has_mask) p2_piece<BF16, true, true, CL>(sm, raw, n_full, fa); else p2_piece<BF16, false, true, CL>(sm, raw, n_full, fa);
             fa.flush();
             if (lane == 0) sm.wacc[w] += fa.accd;
         }
         if (n_full > 0u) {
-            if (has_mask) pass2_whole<BF16, true>(sm); else pass2_whole<BF16, false>(sm);
+            if (has_mask) pass2_whole<BF16, true, CL>(sm); else pass2_whole<BF16, false, CL>(sm);
         }
         __syncthreads();   // the candidate list and the warps' shares are complete
         PGS_STICK(4);   // pass 2
         double s_d = lane < SNW ? sm.wacc[lane] : 0.0;
 #pragma unroll
         for (int o = 16; o; o >>= 1) s_d += __shfl_xor_sync(FULL, s_d, o);
+        if (CL) {   // the fold shares and the argmax candidates of all CTAs meet in the first one
+            cg::cluster_group cluster = cg::this_cluster();
+            if (tid == 0) { *cluster.map_shared_rank(&sm.xs[crank], 0) = s_d; *cluster.map_shared_rank(&sm.xam[crank], 0) = sm.amax; }
+            cluster.sync();
+            if (crank != 0u) continue;
+            s_d = 0.0;
+            uint32_t am_all = 0xffffffffu;
+            for (uint32_t k = 0; k < csize; k++) { s_d += sm.xs[k]; am_all = umin(am_all, sm.xam[k]); }
+            amax = am_all;
+        }
         const float S = (float)(s_d * exp2(c_rest));
         const uint32_t n_cand = sm.cand_n;
         if (n_cand > (uint32_t)F_MCAP) {   // CTA-uniform
@@ -971,25 +1116,57 @@ __global__ void __launch_bounds__(SNT, 2) stream_row_kernel(const RowArgs a, con
 size_t stream_smem_bytes() { return sizeof(StreamSmem); }
 uint32_t stream_threads() { return SNT; }
 
+template <bool BF16, bool CL>
+static cudaError_t configure_one() {
+    cudaError_t e = cudaFuncSetAttribute(stream_row_kernel<BF16, CL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(StreamSmem));
+    if (e != cudaSuccess) return e;
+    return cudaFuncSetAttribute(stream_row_kernel<BF16, CL>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+}
+
 cudaError_t configure_stream() {
-    cudaError_t e = cudaFuncSetAttribute(stream_row_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(StreamSmem));
-    if (e != cudaSuccess) return e;
-    e = cudaFuncSetAttribute(stream_row_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(StreamSmem));
-    if (e != cudaSuccess) return e;
-    e = cudaFuncSetAttribute(stream_row_kernel<false>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
-    if (e != cudaSuccess) return e;
-    return cudaFuncSetAttribute(stream_row_kernel<true>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+    cudaError_t e = configure_one<false, false>();
+    if (e == cudaSuccess) e = configure_one<true, false>();
+    if (e == cudaSuccess) e = configure_one<false, true>();
+    if (e == cudaSuccess) e = configure_one<true, true>();
+    return e;
 }
 
 // CTAs of this kernel that one SM holds
 cudaError_t stream_ctas_per_sm(int* out) {
-    return cudaOccupancyMaxActiveBlocksPerMultiprocessor(out, stream_row_kernel<false>, SNT, sizeof(StreamSmem));
+    return cudaOccupancyMaxActiveBlocksPerMultiprocessor(out, stream_row_kernel<false, false>, SNT, sizeof(StreamSmem));
 }
 
-cudaError_t launch_stream(const RowArgs& a, const StreamLaunch& sl, uint32_t grid, cudaStream_t stream) {
-    if (a.dtype == 0) stream_row_kernel<false><<<grid, SNT, sizeof(StreamSmem), stream>>>(a, sl);
-    else stream_row_kernel<true><<<grid, SNT, sizeof(StreamSmem), stream>>>(a, sl);
-    return cudaGetLastError();
+// Clusters of `csize` CTAs of this kernel that the device holds at once (csize 2, 4 or 8)
+cudaError_t stream_max_clusters(int csize, int* out) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)csize, 1, 1);
+    cfg.blockDim = dim3(SNT, 1, 1);
+    cfg.dynamicSmemBytes = sizeof(StreamSmem);
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = (unsigned)csize; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr; cfg.numAttrs = 1;
+    return cudaOccupancyMaxActiveClusters(out, stream_row_kernel<false, true>, &cfg);
+}
+
+// csize == 1: one CTA per row, `grid` CTAs.  csize > 1: `grid` clusters of csize CTAs, one cluster per row at a time.
+cudaError_t launch_stream(const RowArgs& a, const StreamLaunch& sl, uint32_t grid, uint32_t csize, cudaStream_t stream) {
+    if (csize <= 1u) {
+        if (a.dtype == 0) stream_row_kernel<false, false><<<grid, SNT, sizeof(StreamSmem), stream>>>(a, sl);
+        else stream_row_kernel<true, false><<<grid, SNT, sizeof(StreamSmem), stream>>>(a, sl);
+        return cudaGetLastError();
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid * csize, 1, 1);
+    cfg.blockDim = dim3(SNT, 1, 1);
+    cfg.dynamicSmemBytes = sizeof(StreamSmem);
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = csize; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr; cfg.numAttrs = 1;
+    if (a.dtype == 0) return cudaLaunchKernelEx(&cfg, stream_row_kernel<false, true>, a, sl);
+    return cudaLaunchKernelEx(&cfg, stream_row_kernel<true, true>, a, sl);
 }
 
 }  // namespace pgs
