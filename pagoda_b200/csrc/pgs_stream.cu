@@ -746,6 +746,17 @@ __global__ void __launch_bounds__(SNT, 2) stream_row_kernel(const RowArgs a, con
             }
         }
 
+        // the pieces the first pass starts with are requested now, so that they arrive while the history is indexed
+        if (n_full > 0u) {
+            constexpr int PB = S_PIECE * ESZ;
+            const uint32_t qs = CL ? csize : 1u;
+            if (n_full > crank) {
+                const uint32_t qlast = crank + ((n_full - 1u - crank) / qs) * qs;
+                const char* wp = rowp + (size_t)(w * S_REGION) * ESZ + (size_t)qlast * PB;
+                prefetch_piece<BF16>(wp);
+                if (qlast >= qs + crank) prefetch_piece<BF16>(wp - (size_t)qs * PB);
+            }
+        }
         // ---- history: distinct ids with their counts, grouped by the warp region they fall into
         bool defer_row = false;
         if (pen) {
