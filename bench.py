@@ -417,6 +417,42 @@ def bench_tp(torch, dist, world, rank, dev, threads, steps=50):
     return rec
 
 
+def run_sweep(args):
+    """Diagnostics, not the benchmark contract: plain text lines.  `--sweep variants`: the 256-row headline batch as
+    greedy rows without penalties (the first pass alone), as stochastic rows without penalties, and as it is.
+    `--sweep rows`: the headline recipe at other batch sizes.  With --sweep-steps 1 every case launches exactly once
+    (no warm-up), which is the form to put under ncu for instruction counts."""
+    import copy
+    import torch
+    import pagoda_b200
+    from pagoda_b200 import synth
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(0)
+    n = args.sweep_steps
+    cases = []
+    if args.sweep == "variants":
+        w = synth.headline(seed=7, rows=ROWS, vocab=VOCAB)
+        g = copy.copy(w)
+        g.temperature = np.zeros_like(w.temperature)
+        g.hist_offsets = g.hist_ids = None
+        st = copy.copy(w)
+        st.hist_offsets = st.hist_ids = None
+        cases = [("greedy rows, no penalties", g), ("stochastic rows, no penalties", st), ("headline rows", w)]
+    else:
+        for rows in (1, 8, 32, 64, 128, 148, 256, 296, 592, 1024, 2048):
+            cases.append((f"{rows} rows", synth.headline(seed=7, rows=rows, vocab=VOCAB)))
+    for name, w in cases:
+        sampler = pagoda_b200.Sampler(device=0, max_rows=w.rows, max_vocab=VOCAB, max_history=1024)
+        ext = torch.cuda.ExternalStream(sampler.stream_ptr, device=dev)
+        dw = DeviceWorkload(torch, sampler, w, dev, min_pool_bytes=400e6 if w.rows <= 512 else 1)
+        ms = timed_steps(torch, None, 1, ext, dev, dw.step, n, 0 if n == 1 else 20) / n
+        print(f"{name:32s} {ms * 1e3:9.1f} us/step {ms * 1e6 / w.rows:9.1f} ns/row "
+              f"{w.algorithmic_bytes() / (ms * 1e-3) / 1e9:8.0f} GB/s algorithmic", flush=True)
+        dw.close(); sampler.close()
+        del dw, sampler
+        torch.cuda.empty_cache()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -426,6 +462,8 @@ def main():
     ap.add_argument("--e2e-steps", type=int, default=10)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--headline-only", action="store_true", help="skip the configs / strong / tp records")
+    ap.add_argument("--sweep", choices=["variants", "rows"], help="diagnostic tables (plain text), see run_sweep")
+    ap.add_argument("--sweep-steps", type=int, default=100)
     ap.add_argument("--phases", action="store_true",
                     help="print the row kernel's in-kernel phase timers (cycles per step and CTA) and exit")
     args = ap.parse_args()
@@ -437,6 +475,9 @@ def main():
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     if args.impl == "reference":
         run_reference(args, rank, world)
+        return
+    if args.sweep:
+        run_sweep(args)
         return
 
     import torch
