@@ -503,18 +503,10 @@ def main():
     step = dw.step
 
     clocks = ClockSampler(local_rank) if rank == 0 else None
-    # warm-up: the W steps asked for, then untimed steps until the GPU has been busy long enough to have left its
-    # idle clocks (a 20-step timed region is under 2 ms)
     warm = max(args.warmup, 3)
     for i in range(warm):
         step(i)
     torch.cuda.synchronize()
-    ramp, t_ramp = 0, time.perf_counter()
-    while time.perf_counter() - t_ramp < 0.25:
-        for i in range(50):
-            step(ramp + i)
-        torch.cuda.synchronize()
-        ramp += 50
     # parity of the benchmarked path, all rows of pool 0, before timing
     step(0)
     torch.cuda.synchronize()
@@ -540,6 +532,16 @@ def main():
         assert ok, "parity check against the CPU oracle failed"
         parity = {"rows": checked, "rows_on_a_boundary": skipped, "ok": ok}
 
+    # untimed steps until the GPU has been busy long enough to have left its idle clocks (a 20-step timed region is
+    # under 2 ms, and the oracle check above left the GPU idle for a while), directly in front of the timed region
+    if world > 1:
+        dist.barrier()   # (rank 0 comes out of its oracle check: everybody ramps up together)
+    ramp, t_ramp = 0, time.perf_counter()
+    while time.perf_counter() - t_ramp < 0.25:
+        for i in range(50):
+            step(ramp + i)
+        torch.cuda.synchronize()
+        ramp += 50
     launches0 = sampler.counters()["kernel_launches"]
     if world > 1:
         dist.barrier()
