@@ -18,10 +18,15 @@
 //   finish: exact probabilities of the candidates, top-k with ties, top-p walk, inverse-CDF pick.
 //
 // A row is 600 KB, more than one SM holds, and its maximum must be known before the first numerator: the row
-// is therefore read a second time, from L2, which keeps the rows in flight as long as only about an SM count
-// of them are in their first pass at once.  The launch is one wave of CTAs for up to 2 x SM-count rows; a gate
-// (a counter of rows that finished pass 1, bounded polling) starts the later rows when the earlier ones leave
-// HBM to them, so that the second pass of one cohort runs under the first pass of the next.
+// is therefore read a second time.  What the second pass finds in L2 is what the first pass read last, which is
+// why the passes run in opposite directions; with a whole batch in flight that is about a third of the row.
+// The loops have no registers for a second piece in flight, so every warp asks for the piece it will read two
+// iterations later with an L2 prefetch.  An optional gate (a counter of rows that finished pass 1, bounded
+// polling, off unless the launch asks for a cohort) can hold rows back so that fewer are in their first pass at
+// once.
+//
+// Small batches: when all rows fit as resident clusters, a thread-block cluster of 4 or 8 CTAs shares every row
+// (see stream_row_kernel below): a row alone on one CTA is bound by the latency of its own instructions.
 //
 // The f32 left fold (pagoda/src/sampler.rs:99-113): while the running value stays inside one binade, adding a
 // non-negative term is an integer addition in units of that binade's ulp which depends on the running value only
@@ -38,8 +43,6 @@
 // Rows this kernel does not serve (top-k off or > 1024, more candidates than its buffers, histories beyond its
 // id -> count table, rows that are not 16-byte aligned) are appended to a work list for the general row kernel.
 #include <cuda_runtime.h>
-
-#include <type_traits>
 
 #include <cooperative_groups.h>
 

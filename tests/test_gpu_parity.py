@@ -62,6 +62,35 @@ def test_negative_zero_ties_with_positive_zero(sampler, oracle):
     assert got.argmax[0] == 5
 
 
+def test_rows_shared_by_a_cluster_agree_with_one_cta_per_row(oracle, synth, monkeypatch):
+    """Small batches run with a cluster of CTAs per row.  The same batch through a handle created with that
+    switched off (PGS_CLUSTER=0) must give the same decisions; both must agree with the oracle."""
+    import pagoda_b200
+    from tests.util import assert_same, run_both
+    w = synth.config2(seed=77, rows=12, vocab=151936)
+    w.temperature[::5] = 0.0                       # a few greedy rows
+    w.logits[7, 1234] = np.inf                     # and a faulted one
+    a = pagoda_b200.Sampler(device=0, max_rows=12, max_vocab=151936, max_history=1024)
+    monkeypatch.setenv("PGS_CLUSTER", "0")
+    b = pagoda_b200.Sampler(device=0, max_rows=12, max_vocab=151936, max_history=1024)
+    monkeypatch.delenv("PGS_CLUSTER")
+    try:
+        ra, want = run_both(a, oracle, w)
+        rb, _ = run_both(b, oracle, w)
+        assert_same(ra, want, w, exact=False)
+        assert_same(rb, want, w, exact=False)
+        live = ra.status == 0                         # (a faulted row has a token and a status, nothing else)
+        for k in ("token", "status", "drew"):
+            np.testing.assert_array_equal(getattr(ra, k), getattr(rb, k), err_msg=k)
+        for k in ("argmax", "n_kept"):
+            np.testing.assert_array_equal(getattr(ra, k)[live], getattr(rb, k)[live], err_msg=k)
+        np.testing.assert_array_equal(ra.row_max[live].view(np.uint32), rb.row_max[live].view(np.uint32))
+        np.testing.assert_allclose(ra.sumexp[live], rb.sumexp[live], rtol=2e-6, atol=0)
+    finally:
+        a.close()
+        b.close()
+
+
 def test_sampler_is_reproducible_and_matches_the_oracle_stream(sampler, oracle):  # sampler.rs:165-176
     logits = np.ones(100, dtype=np.float32)
     rng = oracle.Rng(99)
